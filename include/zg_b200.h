@@ -1,0 +1,186 @@
+/* Entry points that the reference's CUDA library does not have.
+ *
+ * The reference host backend implements these ops (or, for the loss and the
+ * Adam update, runs them as raw loops over host memory); its CUDA backend
+ * has no counterpart, so the Zig CudaDevice cannot run a training step on the
+ * device today.  Each declaration cites the HOST code whose semantics it
+ * follows; INTEGRATION.md shows the Zig-side method that binds it.
+ *
+ * All calls are asynchronous on the given stream and never exit the
+ * process: errors are recorded in a sticky per-process status.
+ */
+#ifndef ZG_B200_EXT_H
+#define ZG_B200_EXT_H
+
+#include "decls.h"
+
+/* ------------------------------------------------------------------ status
+ * Replaces the reference's print-and-exit error macros
+ * (src/cuda/cuda_helpers.cu:21-91). 0 = no error since the last clear. */
+EXTERN_C int zg_last_error(void);
+EXTERN_C const char* zg_last_error_message(void);
+EXTERN_C void zg_clear_error(void);
+/* 1 if a CUDA device is usable by this process, else 0 (never errors). */
+EXTERN_C int zg_device_available(void);
+/* Binds the calling thread to a device ordinal (multi-device processes). */
+EXTERN_C void zg_set_device(unsigned device_number);
+
+/* --------------------------------------------------------------- math mode
+ * How SINGLE-precision GEMMs use the tensor cores:
+ *   ZG_MATH_FP32X3  three TF32 passes on an error-compensated hi/lo split
+ *                   (fp32-level accuracy; default)
+ *   ZG_MATH_TF32    one TF32 pass (10-bit mantissa products)
+ *   ZG_MATH_FFMA    CUDA-core FFMA kernel, no tensor cores */
+enum { ZG_MATH_FP32X3 = 0, ZG_MATH_TF32 = 1, ZG_MATH_FFMA = 2 };
+EXTERN_C void zg_set_math_mode(int mode);
+EXTERN_C int zg_get_math_mode(void);
+
+/* -------------------------------------------------------------------- GEMM
+ * opspec.bmm_acc (src/device/opspec.zig:144-162) as HostDevice.bmm_acc runs
+ * it (src/device/host_device.zig:277-313): for b in [0,nC):
+ *   C[b] = epilogue(alpha * op(A[b % nA]) * op(B[b % nB]) + beta * C[b])
+ * A[.] is m x k (k x m when trans_a), B[.] is k x n (n x k when trans_b),
+ * row-major with leading dimensions lda/ldb/ldc; batches are contiguous
+ * (rows*ld elements apart).  id selects the A/B element type (SINGLE, DOUBLE
+ * or BF16); c_id the C element type (SINGLE/DOUBLE, or BF16 with BF16 inputs).
+ *
+ * Fused epilogues (the reference issues these as separate device calls):
+ *   ZG_EPI_NONE
+ *   ZG_EPI_BIAS       + bias[j]               (bias.add_(y), examples/mnist/src/model.zig:108)
+ *   ZG_EPI_BIAS_RELU  max(0, . + bias[j])     (+ nn.relu_, src/nn/nn.zig:39-62)
+ *   ZG_EPI_RELU_MASK  0 where mask_src[i,j] <= 0 (relu_inplace_bwd on the result,
+ *                     src/device/host_device.zig:543-547); mask_src has C's shape and ld
+ * bias is fp32 [n]; mask_src has C's element type. */
+enum { ZG_EPI_NONE = 0, ZG_EPI_BIAS = 1, ZG_EPI_BIAS_RELU = 2, ZG_EPI_RELU_MASK = 3 };
+EXTERN_C void zg_bmm(dtype id, dtype c_id, StreamWrapper stream,
+                     const void* A, const void* B, void* C,
+                     len_t nA, len_t nB, len_t nC, len_t m, len_t n, len_t k,
+                     bool trans_a, bool trans_b, len_t lda, len_t ldb, len_t ldc,
+                     double alpha, double beta,
+                     int epilogue, const void* bias, const void* mask_src);
+
+/* ------------------------------------------------------------- elementwise */
+/* opspec.relu_inplace_bwd (host_device.zig:543-547): if (x <= 0) x_g = 0 */
+EXTERN_C void zg_relu_inplace_bwd(dtype id, StreamWrapper stream, const void* x, void* x_g, len_t n);
+/* opspec.clamp_bwd (host_device.zig:594-598): if (lo < x && x < hi) x_g += y_g */
+EXTERN_C void zg_clamp_bwd(dtype id, StreamWrapper stream, const void* x, const void* y_g, void* x_g,
+                           len_t n, double lo, double hi);
+/* Unary maps y = f(x) (host_device.zig:383-387 sqrt, :480-482 rsqrt with
+ * p = eps, :497-510 exp, :549-551 tanh, :561-563 sigmoid) */
+enum { ZG_UN_EXP = 0, ZG_UN_SQRT = 1, ZG_UN_RSQRT = 2, ZG_UN_TANH = 3, ZG_UN_SIGM = 4 };
+EXTERN_C void zg_unary_fwd(dtype id, StreamWrapper stream, int op, const void* x, void* y, len_t n, double p);
+/* Their accumulating backward passes: x_g += f'(.) * y_g.  `v` is y for
+ * exp/tanh/sigm (host_device.zig:512-515,553-555,565-567) and x for
+ * sqrt/rsqrt, where entries with x < p (eps) receive no gradient
+ * (host_device.zig:396-408, 485-503). */
+EXTERN_C void zg_unary_bwd(dtype id, StreamWrapper stream, int op, const void* v, const void* y_g, void* x_g,
+                           len_t n, double p);
+/* opspec.transpose (host_device.zig:261-267): B[j,i] = A[i,j] + alpha*B[j,i] */
+EXTERN_C void zg_transpose(dtype id, StreamWrapper stream, const void* A, void* B, len_t m, len_t n, double alpha);
+
+/* -------------------------------------------------------------- reductions
+ * reduce.zig:49-164 and host_device.zig:709-874.  y = alpha*reduce + beta*y. */
+EXTERN_C void zg_fold_rows(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
+                           double alpha, double beta);               /* [row,col] -> [col] */
+EXTERN_C void zg_fold_cols(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
+                           double alpha, double beta);               /* [row,col] -> [row] */
+EXTERN_C void zg_sum_along(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t ndim,
+                           len_t dim, void* y, double alpha, double beta);
+/* max_along ignores alpha/beta, as the host does (host_device.zig:853-874) */
+EXTERN_C void zg_max_along(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t ndim,
+                           len_t dim, void* y);
+/* opspec.unbroadcast (host_device.zig:709-780); scratch sized by the caller
+ * as NDArray.unbroadcast_ does (src/ndarray.zig:697-715) */
+EXTERN_C void zg_unbroadcast(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t x_ndim,
+                             void* y, const len_t* y_shape, len_t y_ndim, void* scratch,
+                             double alpha, double beta);
+/* opspec.broadcast (host_device.zig:782-795): y[i] = alpha*x[i % |x|] + beta*y[i] */
+EXTERN_C void zg_broadcast(dtype id, StreamWrapper stream, const void* x, len_t x_len, void* y, len_t y_len,
+                           double alpha, double beta);
+
+/* ------------------------------------------------------------------ losses
+ * Fused row-softmax + cross-entropy, forward and backward in one pass
+ * (src/nn/loss.zig:130-215):
+ *   p = exp(x - (max + log sum exp(x - max)))
+ *   loss_out[0] = (sum_rows -sum_j t_j log(clamp(p_j, 1e-7, 1-1e-7))) / loss_div
+ *   dlogits (+)= (p - t) / loss_div           (when dlogits != NULL)
+ * labels: ZG_LABEL_ONEHOT = fp32 [rows,C] probability rows (what the
+ * reference feeds); ZG_LABEL_INDEX = u64 class index per row.
+ * loss_out is ONE device scalar (overwritten); probs_out (optional) receives
+ * p.  loss_div = the batch size; a data-parallel shard passes the GLOBAL
+ * batch and sums loss_out over the shards.  accumulate != 0 adds into dlogits
+ * (the reference's `+=` into a zero-filled gradient), 0 overwrites. */
+enum { ZG_LABEL_ONEHOT = 0, ZG_LABEL_INDEX = 1 };
+EXTERN_C void zg_softmax_ce_fwd_bwd(dtype id, StreamWrapper stream, const void* logits, const void* labels,
+                                    int label_kind, len_t rows, len_t C, double loss_div,
+                                    void* loss_out, void* dlogits, int accumulate, void* probs_out);
+/* Smooth-L1 / Huber, mean reduction (src/nn/loss.zig:259-305):
+ * loss_out[0] = mean(huber(pred - target)) (overwritten);
+ * grad += d/(beta*n) or sign(d)/n  (when grad != NULL) */
+EXTERN_C void zg_smooth_l1_fwd_bwd(dtype id, StreamWrapper stream, const void* pred, const void* target,
+                                   len_t n, double beta, void* loss_out, void* grad);
+
+/* -------------------------------------------------------------- optimizers
+ * One launch over a whole parameter set.  The tensors of a model live back to
+ * back (attach order) in one parameter buffer and one gradient buffer; seg
+ * describes them.  offset/len are in elements. */
+typedef struct {
+  len_t offset;
+  len_t len;
+} zg_segment;
+
+/* SGD.update over every segment (src/nn/optim.zig:100-122): per tensor
+ * [if clip: nrm = ||g||; if nrm > max_norm: g *= max_norm/(nrm+delta)] then
+ * p += (-lr)*g.  norms is a device scratch of n_seg floats (used when clip). */
+EXTERN_C void zg_sgd_step(dtype id, StreamWrapper stream, void* params, void* grads,
+                          const zg_segment* seg, len_t n_seg, double lr,
+                          int clip, double max_norm, double delta, void* norms);
+/* Adam.update over every segment (src/nn/optim.zig:177-234), all in fp32:
+ * the step counter advances once per TENSOR (optim.zig:189): segment j uses
+ * t = t_first + j.  m, v are laid out like params.  When bf16_copy != NULL
+ * the updated parameters are also written there as bfloat16. */
+EXTERN_C void zg_adam_step(dtype id, StreamWrapper stream, void* params, void* grads, void* m, void* v,
+                           const zg_segment* seg, len_t n_seg, len_t t_first,
+                           double lr, double beta1, double beta2, double eps,
+                           int clip, double max_norm, double delta, void* norms, void* bf16_copy);
+/* target[i] = tau*src[i] + (1-tau)*target[i] (examples/dqn/src/dqn_agent.zig:111-123) */
+EXTERN_C void zg_soft_update(dtype id, StreamWrapper stream, const void* src, void* target, len_t n, double tau);
+/* fp32 -> bf16 (round to nearest even) and back */
+EXTERN_C void zg_cast(dtype src_id, dtype dst_id, StreamWrapper stream, const void* src, void* dst, len_t n);
+
+/* ------------------------------------------------------------------- index
+ * opspec.scatter_add (host_device.zig:1039-1086): dst[offsets[i]] += src[i] */
+EXTERN_C void zg_scatter_add(dtype id, StreamWrapper stream, const void* src, const len_t* offsets, len_t n, void* dst);
+/* NDArray.gather along dim 1 of a [rows, cols] array with one index per row
+ * (src/ndarray.zig:593-633; offsets are computed on the host there):
+ * dst[r] = src[r*cols + idx[r]]; offsets_out (optional) receives r*cols+idx[r] */
+EXTERN_C void zg_gather_rows(dtype id, StreamWrapper stream, const void* src, const len_t* idx, len_t rows,
+                             len_t cols, void* dst, len_t* offsets_out);
+/* opspec.scatter_gcn_deg_scaled (+_bwd) (host_device.zig:1356-1403) */
+EXTERN_C void zg_scatter_gcn_deg_scaled(dtype id, StreamWrapper stream, void* dst, const void* h, const void* deg,
+                                        const len_t* src_idx, const len_t* tgt_idx, len_t stride, len_t n_edge);
+EXTERN_C void zg_scatter_gcn_deg_scaled_bwd(dtype id, StreamWrapper stream, const void* grad_out, const void* h,
+                                            const void* deg, const len_t* src_idx, const len_t* tgt_idx,
+                                            void* grad_h, void* grad_deg, len_t stride, len_t n_edge);
+
+/* --------------------------------------------- stream-ordered caching allocator
+ * Device-side replacement for the Zig CachingAllocator + BlockPool
+ * (src/allocators/caching_allocator.zig:15-162, block_pool.zig:103-412) behind
+ * mem_cache_alloc / mem_cache_free / mem_scratch
+ * (src/device/device_reference.zig:29-60).  A freed block is reusable at once
+ * by later work on the SAME stream; reuse from another stream waits on an event
+ * recorded at free time.  `ctx` is the opaque block handle that DeviceData.ctx
+ * carries (src/allocators/device_data.zig:32-40). */
+typedef struct { void* ptr; } CacheWrapper;
+typedef struct { void* ptr; len_t ctx; } zg_block;
+EXTERN_C CacheWrapper zg_cache_create(unsigned device_id, len_t max_bytes /* 0 = no limit */);
+EXTERN_C void zg_cache_destroy(CacheWrapper cache);
+EXTERN_C zg_block zg_cache_alloc(CacheWrapper cache, len_t nbytes, StreamWrapper stream); /* ptr NULL on OOM */
+EXTERN_C void zg_cache_free(CacheWrapper cache, zg_block block, StreamWrapper stream);
+EXTERN_C void* zg_cache_scratch(CacheWrapper cache, len_t nbytes, StreamWrapper stream);  /* valid until next call */
+EXTERN_C void zg_cache_clear(CacheWrapper cache);   /* returns cached (unused) blocks to the driver */
+/* stats: [0] bytes reserved from the driver, [1] bytes in live blocks,
+ * [2] allocations served from cache, [3] allocations that grew the arena */
+EXTERN_C void zg_cache_stats(CacheWrapper cache, len_t* out4);
+
+#endif

@@ -1,0 +1,117 @@
+// Shared helpers of the device library: status handling, stream casts,
+// vector access and warp/block reductions.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/decls.h"
+#include "../../include/zg_b200.h"
+
+namespace zg {
+
+// ---------------------------------------------------------------- status
+// The first error since the last zg_clear_error() is kept (sticky); later
+// ones are dropped so that the root cause is what the caller sees.
+enum Status : int {
+  kOk = 0,
+  kCudaError = 1,       // a CUDA runtime/driver call failed
+  kBadArgument = 2,     // shapes / dtype / alignment not supported
+  kOutOfMemory = 3,
+  kKernelTimeout = 4,   // a bounded device-side wait ran out
+  kUnsupported = 5,
+};
+
+void set_error(int code, const char* fmt, ...);
+bool check_cuda(cudaError_t e, const char* what, const char* file, int line);
+
+#define ZG_CUDA(expr) ::zg::check_cuda((expr), #expr, __FILE__, __LINE__)
+#define ZG_LAUNCH_CHECK() ::zg::check_cuda(cudaPeekAtLastError(), "kernel launch", __FILE__, __LINE__)
+
+// A stream-bound op context: what CublasWrapper / CudnnWrapper /
+// CutensorWrapper point to.
+struct OpContext {
+  cudaStream_t stream;
+  void* plans;  // plan cache (owned; see reduce_plan.cu)
+};
+
+static inline cudaStream_t as_stream(StreamWrapper w) { return static_cast<cudaStream_t>(w.ptr); }
+static inline cudaStream_t as_stream(CublasWrapper w) { return static_cast<OpContext*>(w.ptr)->stream; }
+static inline cudaStream_t as_stream(CudnnWrapper w) { return static_cast<OpContext*>(w.ptr)->stream; }
+static inline cudaStream_t as_stream(CutensorWrapper w) { return static_cast<OpContext*>(w.ptr)->stream; }
+
+int sm_count();  // SMs of the current device (cached)
+
+// Per-stream scratch owned by the library (runtime.cu).  Returns a 256-byte
+// aligned buffer of at least `bytes`; *counters points at 64 zero-initialised
+// unsigned counters that a kernel must leave at zero when it finishes.
+void* workspace(cudaStream_t s, size_t bytes, unsigned** counters);
+
+// gemm.cu: reads (and clears) the per-device flag that a tensor-core kernel
+// raises when one of its bounded waits runs out; allocates the flag on first use.
+void check_tc_errors();
+
+// Grid size for a grid-stride kernel: enough CTAs for `work_items` at
+// `per_cta` items each, capped at `waves` resident waves of the device.
+static inline unsigned grid_for(size_t work_items, size_t per_cta, int ctas_per_sm = 8) {
+  size_t want = (work_items + per_cta - 1) / per_cta;
+  size_t cap = (size_t)sm_count() * ctas_per_sm;
+  if (want < 1) want = 1;
+  return (unsigned)(want < cap ? want : cap);
+}
+
+#ifdef __CUDACC__
+// ------------------------------------------------------------- device side
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T warp_max(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    T u = __shfl_xor_sync(0xffffffffu, v, o);
+    v = u > v ? u : v;
+  }
+  return v;
+}
+
+// Block-wide sum; every thread receives the result.  `smem` needs 32 slots.
+template <typename T>
+__device__ __forceinline__ T block_sum(T v, T* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  T r = (threadIdx.x < nw) ? smem[threadIdx.x] : T(0);
+  if (warp == 0) {
+    r = warp_sum(r);
+    if (lane == 0) smem[0] = r;
+  }
+  __syncthreads();
+  return smem[0];
+}
+
+template <typename T>
+struct Vec4 {};
+template <>
+struct Vec4<float> {
+  using type = float4;
+};
+template <>
+struct Vec4<double> {
+  using type = double4;  // 32 bytes; split into two 16-byte accesses by the compiler
+};
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+#endif
+
+static inline bool host_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace zg

@@ -1,0 +1,399 @@
+// GEMM entry points: zg_bmm (include/zg_b200.h), gemm / gemv / ger
+// (include/blas_conflux.h).  Large, TMA-addressable problems go to the
+// tcgen05 kernel (gemm_tc.cuh); everything else (tiny shapes, rows whose byte
+// stride is not a multiple of 16, fp64) runs on a register-tiled FFMA kernel.
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "driver_api.h"
+#include "gemm_tc.cuh"
+#include "../../include/blas_conflux.h"
+
+namespace zg {
+
+static int g_math_mode = ZG_MATH_FP32X3;
+
+// =====================================================================
+// FFMA kernel: 64x64 tile, 16-deep k-slabs, 256 threads x (4x4) outputs.
+// Generic in element type (double / float / bf16 inputs with float math),
+// operand transposes and leading dimensions.  gridDim.z = batches * splits.
+// =====================================================================
+template <typename T> struct Acc { using type = float; };
+template <> struct Acc<double> { using type = double; };
+
+template <typename T> __device__ __forceinline__ typename Acc<T>::type to_acc(T v) { return (typename Acc<T>::type)v; }
+template <> __device__ __forceinline__ float to_acc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename TC, typename A> __device__ __forceinline__ TC from_acc(A v) { return (TC)v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, float>(float v) { return __float2bfloat16_rn(v); }
+
+struct SimtParams {
+  size_t nA, nB, m, n, k, lda, ldb, ldc, a_stride, b_stride, c_stride;
+  bool ta, tb;
+  double alpha, beta;
+  int epilogue;
+  const float* bias;
+  const void* mask;
+  unsigned splits;
+  size_t k_per_split;
+};
+
+template <typename TI, typename TC>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C, const SimtParams p) {
+  using AT = typename Acc<TI>::type;
+  constexpr int TM = 64, TN = 64, TK = 16;
+  __shared__ AT As[TK][TM + 1];
+  __shared__ AT Bs[TK][TN + 1];
+  const unsigned batch = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const TI* a = A + (batch % p.nA) * p.a_stride;
+  const TI* b = B + (batch % p.nB) * p.b_stride;
+  TC* c = C + (size_t)batch * p.c_stride;
+  const size_t m0 = (size_t)blockIdx.y * TM, n0 = (size_t)blockIdx.x * TN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  AT acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = AT(0);
+  const size_t kb = split * p.k_per_split;
+  size_t ke = kb + p.k_per_split;
+  if (ke > p.k) ke = p.k;
+  for (size_t k0 = kb; k0 < ke; k0 += TK) {
+    // cooperative loads: 1024 elements per operand slab, 4 per thread; the
+    // fastest-varying thread index follows the contiguous dimension in memory
+    for (int e = threadIdx.x; e < TM * TK; e += 256) {
+      int mm, kk;
+      if (p.ta) { mm = e % TM; kk = e / TM; } else { kk = e % TK; mm = e / TK; }
+      const size_t gm = m0 + mm, gk = k0 + kk;
+      AT v = AT(0);
+      if (gm < p.m && gk < ke) v = to_acc<TI>(p.ta ? a[gk * p.lda + gm] : a[gm * p.lda + gk]);
+      As[kk][mm] = v;
+    }
+    for (int e = threadIdx.x; e < TN * TK; e += 256) {
+      int nn, kk;
+      if (p.tb) { kk = e % TK; nn = e / TK; } else { nn = e % TN; kk = e / TN; }
+      const size_t gn = n0 + nn, gk = k0 + kk;
+      AT v = AT(0);
+      if (gn < p.n && gk < ke) v = to_acc<TI>(p.tb ? b[gn * p.ldb + gk] : b[gk * p.ldb + gn]);
+      Bs[kk][nn] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      AT av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+    }
+    __syncthreads();
+  }
+  const AT alpha = (AT)p.alpha, beta = (AT)p.beta;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const size_t gm = m0 + ty * 4 + i;
+    if (gm >= p.m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t gn = n0 + tx + 16 * j;
+      if (gn >= p.n) continue;
+      const size_t o = gm * p.ldc + gn;
+      AT v = alpha * acc[i][j];
+      if (p.splits > 1) {
+        if constexpr (sizeof(TC) == 4 || sizeof(TC) == 8) atomicAdd(reinterpret_cast<AT*>(c) + o, v);
+        continue;
+      }
+      if (beta != AT(0)) v += beta * to_acc<TC>(c[o]);
+      if (p.epilogue == ZG_EPI_BIAS) v += (AT)p.bias[gn];
+      else if (p.epilogue == ZG_EPI_BIAS_RELU) { v += (AT)p.bias[gn]; v = v > AT(0) ? v : AT(0); }
+      else if (p.epilogue == ZG_EPI_RELU_MASK) {
+        const TC* mk = static_cast<const TC*>(p.mask) + (size_t)batch * p.c_stride;
+        if (to_acc<TC>(mk[o]) <= AT(0)) v = AT(0);
+      }
+      c[o] = from_acc<TC, AT>(v);
+    }
+  }
+}
+
+// C[b][i][j] *= beta over an [m, n] window with leading dimension ldc
+template <typename T>
+__global__ void scale_c_kernel(T* C, size_t batches, size_t m, size_t n, size_t ldc, size_t c_stride, T beta) {
+  const size_t total = batches * m * n, nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nth) {
+    const size_t b = i / (m * n), r = (i % (m * n)) / n, cidx = i % n;
+    T* p = C + b * c_stride + r * ldc + cidx;
+    *p = (beta == T(0)) ? T(0) : beta * (*p);
+  }
+}
+
+template <typename T>
+static void prescale_c(cudaStream_t s, T* C, size_t batches, size_t m, size_t n, size_t ldc, size_t c_stride, double beta) {
+  if (beta == 1.0) return;
+  scale_c_kernel<T><<<grid_for(batches * m * n, 1024), 256, 0, s>>>(C, batches, m, n, ldc, c_stride, (T)beta);
+  ZG_LAUNCH_CHECK();
+}
+
+template <typename TI, typename TC>
+static void launch_simt(cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m, len_t n, len_t k,
+                        bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue, const void* bias,
+                        const void* mask) {
+  SimtParams p;
+  p.nA = nA; p.nB = nB; p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldb = ldb; p.ldc = ldc;
+  p.a_stride = (ta ? k : m) * lda; p.b_stride = (tb ? n : k) * ldb; p.c_stride = m * ldc;
+  p.ta = ta; p.tb = tb; p.alpha = alpha; p.beta = beta; p.epilogue = epilogue;
+  p.bias = static_cast<const float*>(bias); p.mask = mask;
+  const size_t tiles = ((m + 63) / 64) * ((n + 63) / 64) * nC;
+  unsigned splits = 1;
+  // deep-k, few-tile problems (weight gradients): split K over more CTAs
+  if (epilogue == ZG_EPI_NONE && sizeof(TC) >= 4 && k >= 1024 && tiles * 2 <= (size_t)sm_count()) {
+    size_t want = (size_t)sm_count() * 2 / tiles;
+    size_t maxs = k / 256;
+    splits = (unsigned)(want < maxs ? want : maxs);
+    if (splits < 1) splits = 1;
+  }
+  p.splits = splits;
+  p.k_per_split = splits > 1 ? ((k + splits - 1) / splits + 15) / 16 * 16 : k;
+  if (splits > 1) {
+    if constexpr (sizeof(TC) >= 4) prescale_c<TC>(s, static_cast<TC*>(C), nC, m, n, ldc, p.c_stride, beta);
+  }
+  dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), (unsigned)(nC * splits));
+  if (grid.y > 65535 || grid.z > 65535) { set_error(kBadArgument, "gemm: grid too large (m=%lu, batches=%lu)", m, nC); return; }
+  gemm_simt_kernel<TI, TC><<<grid, 256, 0, s>>>(static_cast<const TI*>(A), static_cast<const TI*>(B), static_cast<TC*>(C), p);
+  ZG_LAUNCH_CHECK();
+}
+
+// =====================================================================
+// tcgen05 path: host side
+// =====================================================================
+static int* tc_error_flag() {
+  // one device-visible flag per device, read back by zg_last_error callers via check_tc_errors()
+  static int* flags[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!flags[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    cudaMemset(p, 0, sizeof(int));
+    flags[dev] = p;
+  }
+  return flags[dev];
+}
+
+static bool make_tmap(CUtensorMap* map, bool bf16, const void* base, uint64_t inner, uint64_t rows, uint64_t batches, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_rows) {
+  static auto encode = ZG_DRV(cuTensorMapEncodeTiled);
+  if (!encode) return false;
+  const uint64_t es = bf16 ? 2 : 4;
+  cuuint64_t dims[3] = {inner, rows, batches};
+  cuuint64_t strides[2] = {ld * es, rows * ld * es};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
+                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return ZG_CU(r);
+}
+
+template <int BN, bool AK, bool BK_, int MODE>
+static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tb, const tc::Params& p, dim3 grid) {
+  using SL = tc::SmemLayout<BN, MODE>;
+  auto kern = tc::gemm_tc_kernel<BN, AK, BK_, MODE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::kTotal))) return false;
+    attr_set = true;
+  }
+  kern<<<grid, tc::kThreadsTc, SL::kTotal, s>>>(ta, tb, p);
+  return ZG_LAUNCH_CHECK();
+}
+
+template <int MODE>
+static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor, const CUtensorMap& ta, const CUtensorMap& tb,
+                           const tc::Params& p, dim3 grid) {
+#define ZG_TC_CASE(BNV)                                                                       \
+  if (bn == BNV) {                                                                            \
+    if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE>(s, ta, tb, p, grid);   \
+    if (a_kmajor && !b_kmajor) return launch_tc_inst<BNV, true, false, MODE>(s, ta, tb, p, grid); \
+    if (!a_kmajor && b_kmajor) return launch_tc_inst<BNV, false, true, MODE>(s, ta, tb, p, grid); \
+    return launch_tc_inst<BNV, false, false, MODE>(s, ta, tb, p, grid);                       \
+  }
+  if constexpr (MODE != tc::kBF16) { ZG_TC_CASE(32) }
+  ZG_TC_CASE(64)
+  ZG_TC_CASE(128)
+#undef ZG_TC_CASE
+  set_error(kBadArgument, "gemm: no tensor-core instance for BN=%d", bn);
+  return false;
+}
+
+// Returns true when the tensor-core path took the problem.
+static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
+                            len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
+                            int epilogue, const void* bias, const void* mask) {
+  const bool bf16 = (id == BF16);
+  if (!(id == SINGLE || bf16)) return false;
+  if (id == SINGLE && (g_math_mode == ZG_MATH_FFMA || c_id != SINGLE)) return false;
+  if (bf16 && !(c_id == SINGLE || c_id == BF16)) return false;
+  const size_t es = bf16 ? 2 : 4;
+  if (!host_aligned16(A) || !host_aligned16(B) || (lda * es) % 16 || (ldb * es) % 16) return false;
+  if (m == 0 || n == 0 || nC == 0) return false;
+  if (m > 0x7fffffffu || n > 0x7fffffffu || k > 0x7fffffffu || ldc > 0xffffffffu) return false;
+  // tiny problems are launch-bound either way; keep them on the FFMA kernel
+  const char* force = getenv("ZG_GEMM_FORCE_TC");
+  if (!(force && force[0] == '1') && (double)m * (double)n * (double)k < 64.0 * 64.0 * 64.0) return false;
+
+  const int mode = bf16 ? tc::kBF16 : (g_math_mode == ZG_MATH_TF32 ? tc::kTF32 : tc::kFP32X3);
+  const int atom = bf16 ? 64 : 32;        // M/N elements per 128-byte column block
+  const int bk = bf16 ? 64 : 32;
+  const bool a_kmajor = !ta;              // A stored [m,k] -> K contiguous
+  const bool b_kmajor = tb;               // B stored [n,k] -> K contiguous
+  int bn = n <= 32 ? 32 : (n <= 64 ? 64 : 128);
+  if (bn < atom) bn = atom;               // MN-major B needs whole column blocks; bf16 has no BN=32 instance
+  size_t tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
+  // few wide tiles: halve BN to put more SMs to work
+  if (bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) { bn = 64; tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC; }
+
+  unsigned splits = 1;
+  if (epilogue == ZG_EPI_NONE && c_id == SINGLE && k >= 2048 && tiles * 2 <= (size_t)sm_count()) {
+    size_t want = (size_t)sm_count() / tiles;
+    size_t maxs = k / 512;
+    splits = (unsigned)(want < maxs ? want : maxs);
+    if (splits < 1) splits = 1;
+  }
+  const size_t k_per_split = splits > 1 ? ((k + splits - 1) / splits + bk - 1) / bk * bk : ((k + bk - 1) / bk * bk);
+  if (splits > 1) splits = (unsigned)((k + k_per_split - 1) / k_per_split);
+
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (a_kmajor) ok = make_tmap(&tmA, bf16, A, k, m, nA, lda, bk, 128);
+  else ok = make_tmap(&tmA, bf16, A, m, k, nA, lda, atom, bk);
+  if (!ok) return true;  // error recorded
+  if (b_kmajor) ok = make_tmap(&tmB, bf16, B, k, n, nB, ldb, bk, bn);
+  else ok = make_tmap(&tmB, bf16, B, n, k, nB, ldb, atom, bk);
+  if (!ok) return true;
+
+  tc::Params p;
+  memset(&p, 0, sizeof(p));
+  if (c_id == SINGLE) { p.C = static_cast<float*>(C); p.mask = static_cast<const float*>(mask); }
+  else { p.Cb = static_cast<__nv_bfloat16*>(C); p.maskb = static_cast<const __nv_bfloat16*>(mask); }
+  p.bias = static_cast<const float*>(bias);
+  p.c_batch_stride = (uint64_t)m * ldc;
+  p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k; p.ldc = (uint32_t)ldc;
+  p.nA = (uint32_t)nA; p.nB = (uint32_t)nB;
+  p.splits = splits; p.k_per_split = (uint32_t)k_per_split;
+  p.alpha = (float)alpha; p.beta = (float)beta; p.epilogue = epilogue;
+  p.error_flag = tc_error_flag();
+  if (splits > 1) prescale_c<float>(s, static_cast<float*>(C), nC, m, n, ldc, m * ldc, beta);
+  dim3 grid((unsigned)((n + bn - 1) / bn), (unsigned)((m + 127) / 128), (unsigned)(nC * splits));
+  if (grid.y > 65535 || grid.z > 65535) return false;
+  if (mode == tc::kBF16) launch_tc_mode<tc::kBF16>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
+  else if (mode == tc::kTF32) launch_tc_mode<tc::kTF32>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
+  else launch_tc_mode<tc::kFP32X3>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
+  return true;
+}
+
+void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m,
+                  len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue,
+                  const void* bias, const void* mask) {
+  if (m == 0 || n == 0 || nC == 0) return;
+  if (nA == 0 || nB == 0) { set_error(kBadArgument, "bmm: empty operand batch"); return; }
+  if (epilogue < ZG_EPI_NONE || epilogue > ZG_EPI_RELU_MASK) { set_error(kBadArgument, "bmm: unknown epilogue %d", epilogue); return; }
+  if ((epilogue == ZG_EPI_BIAS || epilogue == ZG_EPI_BIAS_RELU) && !bias) { set_error(kBadArgument, "bmm: bias epilogue without bias"); return; }
+  if (epilogue == ZG_EPI_RELU_MASK && !mask) { set_error(kBadArgument, "bmm: mask epilogue without mask source"); return; }
+  if (try_tensor_core(id, c_id, s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask)) return;
+  if (id == SINGLE && c_id == SINGLE) launch_simt<float, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
+  else if (id == DOUBLE && c_id == DOUBLE) launch_simt<double, double>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
+  else if (id == BF16 && c_id == SINGLE) launch_simt<__nv_bfloat16, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
+  else if (id == BF16 && c_id == BF16) launch_simt<__nv_bfloat16, __nv_bfloat16>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
+  else set_error(kUnsupported, "bmm: unsupported dtype combination %d -> %d", (int)id, (int)c_id);
+}
+
+// Reads (and clears) the device flag that a timed-out tensor-core kernel raises.
+void check_tc_errors() {
+  int* f = tc_error_flag();
+  if (!f) return;
+  int v = 0;
+  if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && v) {
+    cudaMemset(f, 0, sizeof(int));
+    set_error(kKernelTimeout, "a tensor-core GEMM gave up waiting on a pipeline barrier");
+  }
+}
+
+// y = alpha*op(A)x + beta*y : one warp per output element of the no-trans
+// case, one thread per output element (coalesced over columns) when transposed
+template <typename T>
+__global__ void __launch_bounds__(256) gemv_n_kernel(const T* __restrict__ A, const T* __restrict__ x, T* y, size_t m, size_t n, T alpha, T beta) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < m; r += warps) {
+    T s = T(0);
+    for (size_t j = lane; j < n; j += 32) s += A[r * n + j] * x[j];
+    s = warp_sum(s);
+    if (lane == 0) y[r] = (beta == T(0)) ? alpha * s : alpha * s + beta * y[r];
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) gemv_t_kernel(const T* __restrict__ A, const T* __restrict__ x, T* y, size_t m, size_t n, T alpha, T beta) {
+  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < n; c += nth) {
+    T s = T(0);
+    for (size_t i = 0; i < m; ++i) s += A[i * n + c] * x[i];
+    y[c] = (beta == T(0)) ? alpha * s : alpha * s + beta * y[c];
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) ger_kernel(const T* __restrict__ a, const T* __restrict__ b, T* C, size_t m, size_t n, size_t ldc, T alpha) {
+  const size_t total = m * n, nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nth) {
+    const size_t r = i / n, c = i % n;
+    C[r * ldc + c] += alpha * a[r] * b[c];
+  }
+}
+
+}  // namespace zg
+
+using namespace zg;
+
+extern "C" void zg_set_math_mode(int mode) {
+  if (mode < ZG_MATH_FP32X3 || mode > ZG_MATH_FFMA) { set_error(kBadArgument, "zg_set_math_mode: unknown mode %d", mode); return; }
+  g_math_mode = mode;
+}
+extern "C" int zg_get_math_mode(void) { return g_math_mode; }
+
+extern "C" void zg_bmm(dtype id, dtype c_id, StreamWrapper stream, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
+                       len_t m, len_t n, len_t k, bool trans_a, bool trans_b, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
+                       int epilogue, const void* bias, const void* mask_src) {
+  bmm_dispatch(id, c_id, as_stream(stream), A, B, C, nA, nB, nC, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, epilogue, bias, mask_src);
+}
+
+extern "C" void gemm(dtype id, CublasWrapper w, const void* a, const void* b, void* c, len_t m, len_t n, len_t k, bool trans_a,
+                     bool trans_b, len_t lda, len_t ldb, len_t ldc, double alpha, double beta) {
+  bmm_dispatch(id, id, as_stream(w), a, b, c, 1, 1, 1, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, ZG_EPI_NONE, nullptr, nullptr);
+}
+
+extern "C" void gemv(dtype id, CublasWrapper w, const void* a, const void* x, void* y, len_t m, len_t n, bool trans_a, double alpha,
+                     double beta) {
+  if (m == 0 || n == 0) return;
+  cudaStream_t s = as_stream(w);
+  if (id == SINGLE) {
+    if (trans_a) gemv_t_kernel<float><<<grid_for(n, 256), 256, 0, s>>>((const float*)a, (const float*)x, (float*)y, m, n, (float)alpha, (float)beta);
+    else gemv_n_kernel<float><<<grid_for(m, 8), 256, 0, s>>>((const float*)a, (const float*)x, (float*)y, m, n, (float)alpha, (float)beta);
+  } else if (id == DOUBLE) {
+    if (trans_a) gemv_t_kernel<double><<<grid_for(n, 256), 256, 0, s>>>((const double*)a, (const double*)x, (double*)y, m, n, alpha, beta);
+    else gemv_n_kernel<double><<<grid_for(m, 8), 256, 0, s>>>((const double*)a, (const double*)x, (double*)y, m, n, alpha, beta);
+  } else { set_error(kUnsupported, "gemv: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void ger(dtype id, CublasWrapper w, const void* a, const void* b, void* c, len_t m, len_t n, len_t ldc, double alpha) {
+  if (m == 0 || n == 0) return;
+  cudaStream_t s = as_stream(w);
+  if (id == SINGLE) ger_kernel<float><<<grid_for(m * n, 1024), 256, 0, s>>>((const float*)a, (const float*)b, (float*)c, m, n, ldc, (float)alpha);
+  else if (id == DOUBLE) ger_kernel<double><<<grid_for(m * n, 1024), 256, 0, s>>>((const double*)a, (const double*)b, (double*)c, m, n, ldc, alpha);
+  else { set_error(kUnsupported, "ger: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}

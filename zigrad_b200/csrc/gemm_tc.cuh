@@ -1,0 +1,425 @@
+// tcgen05 / TMEM / TMA GEMM for sm_100a.
+//
+//   C[b] = epilogue(alpha * op(A[b % nA]) * op(B[b % nB]) + beta * C[b])
+//
+// One CTA computes one 128 x BN tile of C (optionally one K-split of it).
+// Roles inside the CTA (8 warps):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and B
+//               k-slabs into a ring of shared-memory stages (128-byte swizzle)
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma with the
+//               accumulator in tensor memory; also owns the TMEM allocation
+//   warps 2-7   FP32X3 mode only: split every fp32 operand slab into a TF32
+//               "hi" part (in place) and a "lo" remainder (second buffer), so
+//               that Ahi*Bhi + Alo*Bhi + Ahi*Blo recovers fp32-level accuracy
+//   warps 4-7   epilogue: tcgen05.ld of the accumulator (warp q reads TMEM
+//               lanes 32q..32q+31), alpha/beta/bias/ReLU/mask, and a
+//               transpose through shared memory so that global stores are
+//               full 128-byte row segments
+//
+// Operand layouts.  A row-major matrix whose contiguous dimension is K is a
+// "K-major" UMMA operand; one whose contiguous dimension is M (or N) is
+// "MN-major".  Both are fetched by TMA into the canonical 128-byte-swizzled
+// layouts that the shared-memory matrix descriptors name:
+//   K-major  : slab = rows x 128 bytes of K; 8-row groups are 1024 bytes apart
+//              (SBO); the k-th MMA inside the slab starts 32 bytes further
+//   MN-major : slab = column blocks of 128 bytes of M/N; inside a block the
+//              k rows are 128 bytes apart, 8-row groups 1024 bytes apart (SBO),
+//              column blocks BK*128 bytes apart (LBO)
+//
+// Every wait on an mbarrier is bounded: when the limit is reached the CTA
+// raises a flag in global memory, stops issuing work, and still releases its
+// tensor memory before it returns.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace zg {
+namespace tc {
+
+constexpr int kBM = 128;
+constexpr int kThreadsTc = 256;
+constexpr int kSlabBytes = 128;          // bytes of the contiguous dimension per smem row
+constexpr uint32_t kSpinLimit = 1u << 24;  // polls per wait before giving up
+
+enum Mode { kTF32 = 0, kFP32X3 = 1, kBF16 = 2 };
+
+struct Params {
+  float* C;             // fp32 output (or nullptr when Cb is used)
+  __nv_bfloat16* Cb;    // bf16 output
+  const float* bias;    // [n] or nullptr
+  const float* mask;    // fp32 mask source with C's layout (when C is fp32)
+  const __nv_bfloat16* maskb;
+  uint64_t c_batch_stride;  // elements
+  uint32_t m, n, k;
+  uint32_t ldc;
+  uint32_t nA, nB;      // operand batch counts (index wraps)
+  uint32_t splits;      // K splits (gridDim.z = batches * splits)
+  uint32_t k_per_split; // multiple of BK
+  float alpha, beta;
+  int epilogue;
+  int* error_flag;      // set to 1 when a bounded wait ran out
+};
+
+// ------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *failed) when the limit is hit or
+// another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) {
+      if (*failed) return false;
+      __nanosleep(40);
+    }
+  }
+  *failed = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+template <bool BF16>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (BF16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// mbarrier arrives once all previously issued MMAs of this thread are done
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread t gets row (lane base + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading-dimension
+// byte offset and stride byte offset in 16-byte units, descriptor version 1,
+// 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // version (Blackwell)
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, A/B format (tf32 = 2, bf16 = 1),
+// operand majors, N >> 3, M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn_major, bool b_mn_major, int N) {
+  return (1u << 4) | ((bf16 ? 1u : 2u) << 7) | ((bf16 ? 1u : 2u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+template <int MODE>
+struct ModeTraits {
+  static constexpr bool kBf16 = (MODE == kBF16);
+  static constexpr int kElem = kBf16 ? 2 : 4;
+  static constexpr int kBK = kSlabBytes / kElem;       // elements of K per stage: 32 (fp32) / 64 (bf16)
+  static constexpr int kUmmaK = 32 / kElem;            // K per MMA: 8 (tf32) / 16 (bf16)
+  static constexpr int kAtomMN = kSlabBytes / kElem;   // M/N elements per 128-byte column block
+  static constexpr int kBufs = (MODE == kFP32X3) ? 2 : 1;  // hi (+ lo) copies of each operand slab
+};
+
+template <int BN, int MODE>
+struct SmemLayout {
+  using MT = ModeTraits<MODE>;
+  static constexpr int kABytes = kBM * kSlabBytes;   // 16 KB
+  static constexpr int kBBytes = BN * kSlabBytes;
+  static constexpr int kStageBytes = (kABytes + kBBytes) * MT::kBufs;
+  static constexpr int kEpiBytes = 4 * 32 * 33 * 4;  // per-warp 32x33 fp32 transpose tiles
+  static constexpr int kBudget = 220 * 1024;
+  static constexpr int kStagesRaw = (kBudget - kEpiBytes - 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  using MT = ModeTraits<MODE>;
+  using SL = SmemLayout<BN, MODE>;
+  constexpr int S = SL::kStages;
+  constexpr bool X3 = (MODE == kFP32X3);
+  constexpr uint32_t kIdesc = make_idesc(MT::kBf16, !A_KMAJOR, !B_KMAJOR, BN);
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  // stages need 1024-byte alignment (swizzle atoms)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  float* epi_smem = reinterpret_cast<float*>(smem + S * SL::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * SL::kStageBytes + SL::kEpiBytes);
+  uint64_t* full = bars;            // [S] TMA bytes landed
+  uint64_t* ready = bars + S;       // [S] (X3) split done
+  uint64_t* empty = bars + 2 * S;   // [S] MMAs that read the stage retired
+  uint64_t* accum = bars + 3 * S;   // accumulator complete
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const uint32_t batch = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const uint32_t k_begin = split * p.k_per_split;
+  uint32_t k_end = k_begin + p.k_per_split;
+  if (k_end > p.k) k_end = p.k;
+  const int KT = (k_end > k_begin) ? (int)((k_end - k_begin + MT::kBK - 1) / MT::kBK) : 0;
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&ready[s], kThreadsTc - 64);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      const int za = (int)(batch % p.nA), zb = (int)(batch % p.nB);
+      for (int kt = 0; kt < KT; ++kt) {
+        const int s = kt % S;
+        if (kt >= S && !mbar_wait(&empty[s], ((kt / S) & 1) ^ 1, &failed)) break;
+        uint8_t* st = stage_base + s * SL::kStageBytes;
+        uint8_t* a_dst = st;
+        uint8_t* b_dst = st + SL::kABytes * MT::kBufs;
+        mbar_expect_tx(&full[s], SL::kABytes + SL::kBBytes);
+        const int k0 = (int)k_begin + kt * MT::kBK;
+        if (A_KMAJOR) {
+          tma_load_3d(a_dst, &tmA, &full[s], k0, (int)(tile_m * kBM), za);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBM / MT::kAtomMN; ++j)
+            tma_load_3d(a_dst + j * MT::kBK * kSlabBytes, &tmA, &full[s], (int)(tile_m * kBM) + j * MT::kAtomMN, k0, za);
+        }
+        if (B_KMAJOR) {
+          tma_load_3d(b_dst, &tmB, &full[s], k0, (int)(tile_n * BN), zb);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / MT::kAtomMN; ++j)
+            tma_load_3d(b_dst + j * MT::kBK * kSlabBytes, &tmB, &full[s], (int)(tile_n * BN) + j * MT::kAtomMN, k0, zb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      for (int kt = 0; kt < KT; ++kt) {
+        const int s = kt % S;
+        if (!mbar_wait(X3 ? &ready[s] : &full[s], (kt / S) & 1, &failed)) break;
+        tc_fence_after();
+        uint8_t* st = stage_base + s * SL::kStageBytes;
+        const uint32_t a_hi = smem_u32(st), a_lo = a_hi + SL::kABytes;
+        const uint32_t b_hi = a_hi + SL::kABytes * MT::kBufs, b_lo = b_hi + SL::kBBytes;
+#pragma unroll
+        for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk) {
+          // K-major: next MMA starts 32 bytes further inside the 128-byte rows.
+          // MN-major: next MMA starts kUmmaK k-rows (128 bytes each) further.
+          const uint32_t a_off = A_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
+          const uint32_t b_off = B_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
+          const uint32_t a_lbo = A_KMAJOR ? 16 : MT::kBK * kSlabBytes;
+          const uint32_t b_lbo = B_KMAJOR ? 16 : MT::kBK * kSlabBytes;
+          const uint64_t da = make_desc(a_hi + a_off, a_lbo, 1024);
+          const uint64_t db = make_desc(b_hi + b_off, b_lbo, 1024);
+          const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
+          if constexpr (X3) {
+            const uint64_t dal = make_desc(a_lo + a_off, a_lbo, 1024);
+            const uint64_t dbl = make_desc(b_lo + b_off, b_lbo, 1024);
+            umma<false>(tmem_d, dal, db, kIdesc, acc);   // Alo * Bhi
+            umma<false>(tmem_d, da, dbl, kIdesc, 1u);    // Ahi * Blo
+            umma<false>(tmem_d, da, db, kIdesc, 1u);     // Ahi * Bhi
+          } else {
+            umma<MT::kBf16>(tmem_d, da, db, kIdesc, acc);
+          }
+        }
+        umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+      }
+      umma_commit(accum);
+    }
+  } else if (X3) {
+    // ------------------------------------------- hi/lo split (warps 2..7)
+    const int t = threadIdx.x - 64;
+    constexpr int NT = kThreadsTc - 64;
+    for (int kt = 0; kt < KT; ++kt) {
+      const int s = kt % S;
+      if (!mbar_wait(&full[s], (kt / S) & 1, &failed)) break;
+      uint8_t* st = stage_base + s * SL::kStageBytes;
+      float4* a_hi = reinterpret_cast<float4*>(st);
+      float4* a_lo = reinterpret_cast<float4*>(st + SL::kABytes);
+      float4* b_hi = reinterpret_cast<float4*>(st + SL::kABytes * 2);
+      float4* b_lo = reinterpret_cast<float4*>(st + SL::kABytes * 2 + SL::kBBytes);
+      // the split is position independent, so the swizzle does not matter here
+#pragma unroll 4
+      for (int i = t; i < SL::kABytes / 16; i += NT) {
+        const float4 v = a_hi[i];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        a_hi[i] = h;
+        a_lo[i] = l;
+      }
+#pragma unroll 4
+      for (int i = t; i < SL::kBBytes / 16; i += NT) {
+        const float4 v = b_hi[i];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        b_hi[i] = h;
+        b_lo[i] = l;
+      }
+      fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+      mbar_arrive(&ready[s]);
+    }
+  }
+
+  // ---------------------------------------------------------------- epilogue
+  if (warp >= 4) {
+    const int q = warp - 4;  // TMEM lane quadrant
+    float* tile = epi_smem + q * 32 * 33;
+    const bool have_acc = (KT > 0) && mbar_wait(accum, 0, &failed);
+    tc_fence_after();
+    const uint32_t row0 = tile_m * kBM + q * 32;
+    const uint64_t c_off = (uint64_t)batch * p.c_batch_stride;
+    if ((KT == 0 || have_acc) && row0 < p.m) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const uint32_t col0 = tile_n * BN + c * 32;
+        if (col0 >= p.n) break;
+        uint32_t r[32];
+        if (KT > 0) {
+          tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        // registers (thread = row) -> smem -> (thread = column)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
+        const uint32_t col = col0 + lane;
+        const bool col_ok = col < p.n;
+        const float bias = (col_ok && p.bias && (p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU)) ? p.bias[col] : 0.f;
+        const uint32_t rows = (p.m - row0) < 32u ? (p.m - row0) : 32u;
+        if (col_ok) {
+          for (uint32_t rr = 0; rr < rows; ++rr) {
+            const uint64_t o = c_off + (uint64_t)(row0 + rr) * p.ldc + col;
+            float v = p.alpha * tile[rr * 33 + lane];
+            if (p.splits > 1) {
+              atomicAdd(p.C + o, v);  // C was pre-scaled by beta; no fused epilogue with split-K
+              continue;
+            }
+            if (p.beta != 0.f) v += p.beta * (p.C ? p.C[o] : __bfloat162float(p.Cb[o]));
+            if (p.epilogue == ZG_EPI_BIAS) v += bias;
+            else if (p.epilogue == ZG_EPI_BIAS_RELU) { v += bias; v = v > 0.f ? v : 0.f; }
+            else if (p.epilogue == ZG_EPI_RELU_MASK) {
+              const float mv = p.mask ? p.mask[o] : __bfloat162float(p.maskb[o]);
+              if (mv <= 0.f) v = 0.f;
+            }
+            if (p.C) p.C[o] = v;
+            else p.Cb[o] = __float2bfloat16_rn(v);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_d, kTmemCols);
+  }
+  if (threadIdx.x == 0 && failed && p.error_flag) *p.error_flag = 1;
+}
+
+}  // namespace tc
+}  // namespace zg

@@ -1,0 +1,111 @@
+// Index ops: scatter_add, row gather, and the GCN degree-scaled edge scatter
+// with its backward.  Semantics: src/device/host_device.zig:1039-1086,
+// :1356-1403 and src/ndarray.zig:593-633.
+//
+// Accumulation into shared destinations uses red.global.add.f32; the values
+// added are the reference's, the order in which duplicates land is not.
+#include "common.cuh"
+
+namespace zg {
+
+constexpr int kIThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kIThreads) scatter_add_kernel(const T* __restrict__ src, const len_t* __restrict__ offs, size_t n, T* dst) {
+  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) atomicAdd(dst + offs[i], src[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kIThreads) gather_rows_kernel(const T* __restrict__ src, const len_t* __restrict__ idx, size_t rows, size_t cols,
+                                                                T* __restrict__ dst, len_t* __restrict__ offsets_out, int* bad) {
+  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += nth) {
+    const size_t c = idx[r];
+    if (c >= cols) {  // the reference returns error.IndexOutOfBounds; never read out of range
+      if (bad) *bad = 1;
+      dst[r] = T(0);
+      if (offsets_out) offsets_out[r] = r * cols;
+      continue;
+    }
+    const size_t o = r * cols + c;
+    dst[r] = src[o];
+    if (offsets_out) offsets_out[r] = o;
+  }
+}
+
+// dst[tgt,:] += deg[src]*deg[tgt] * h[src,:]   -- one thread per (edge, feature)
+__global__ void __launch_bounds__(kIThreads) gcn_scatter_kernel(float* dst, const float* __restrict__ h, const float* __restrict__ deg,
+                                                                const len_t* __restrict__ src_idx, const len_t* __restrict__ tgt_idx,
+                                                                size_t stride, size_t n_edge) {
+  const size_t total = n_edge * stride, nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nth) {
+    const size_t e = i / stride, j = i % stride;
+    const size_t s = src_idx[e], t = tgt_idx[e];
+    const float w = deg[s] * deg[t];
+    atomicAdd(dst + t * stride + j, w * h[s * stride + j]);
+  }
+}
+
+// one thread per edge: the per-edge sums over the feature dim are formed in
+// the reference's order, then added to grad_deg with one atomic each
+__global__ void __launch_bounds__(kIThreads) gcn_scatter_bwd_kernel(const float* __restrict__ go, const float* __restrict__ h,
+                                                                    const float* __restrict__ deg, const len_t* __restrict__ src_idx,
+                                                                    const len_t* __restrict__ tgt_idx, float* grad_h, float* grad_deg,
+                                                                    size_t stride, size_t n_edge) {
+  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n_edge; e += nth) {
+    const size_t s = src_idx[e], t = tgt_idx[e];
+    const float ds = deg[s], dt = deg[t];
+    float gs = 0.f, gt = 0.f;
+    for (size_t j = 0; j < stride; ++j) {
+      const float g = go[t * stride + j];
+      const float hv = h[s * stride + j];
+      atomicAdd(grad_h + s * stride + j, g * ds * dt);
+      gs += g * dt * hv;
+      gt += g * ds * hv;
+    }
+    atomicAdd(grad_deg + s, gs);
+    atomicAdd(grad_deg + t, gt);
+  }
+}
+
+}  // namespace zg
+
+using namespace zg;
+
+extern "C" void zg_scatter_add(dtype id, StreamWrapper w, const void* src, const len_t* offsets, len_t n, void* dst) {
+  if (n == 0) return;
+  cudaStream_t s = as_stream(w);
+  if (id == SINGLE) scatter_add_kernel<float><<<grid_for(n, kIThreads * 2), kIThreads, 0, s>>>((const float*)src, offsets, n, (float*)dst);
+  else if (id == DOUBLE) scatter_add_kernel<double><<<grid_for(n, kIThreads * 2), kIThreads, 0, s>>>((const double*)src, offsets, n, (double*)dst);
+  else { set_error(kUnsupported, "zg_scatter_add: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_gather_rows(dtype id, StreamWrapper w, const void* src, const len_t* idx, len_t rows, len_t cols, void* dst,
+                               len_t* offsets_out) {
+  if (rows == 0) return;
+  cudaStream_t s = as_stream(w);
+  if (id == SINGLE) gather_rows_kernel<float><<<grid_for(rows, kIThreads), kIThreads, 0, s>>>((const float*)src, idx, rows, cols, (float*)dst, offsets_out, nullptr);
+  else if (id == DOUBLE) gather_rows_kernel<double><<<grid_for(rows, kIThreads), kIThreads, 0, s>>>((const double*)src, idx, rows, cols, (double*)dst, offsets_out, nullptr);
+  else { set_error(kUnsupported, "zg_gather_rows: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_scatter_gcn_deg_scaled(dtype id, StreamWrapper w, void* dst, const void* h, const void* deg, const len_t* src_idx,
+                                          const len_t* tgt_idx, len_t stride, len_t n_edge) {
+  if (id != SINGLE) { set_error(kUnsupported, "zg_scatter_gcn_deg_scaled: only SINGLE is implemented"); return; }
+  if (n_edge == 0 || stride == 0) return;
+  gcn_scatter_kernel<<<grid_for(n_edge * stride, kIThreads * 2), kIThreads, 0, as_stream(w)>>>((float*)dst, (const float*)h, (const float*)deg, src_idx, tgt_idx, stride, n_edge);
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_scatter_gcn_deg_scaled_bwd(dtype id, StreamWrapper w, const void* grad_out, const void* h, const void* deg,
+                                              const len_t* src_idx, const len_t* tgt_idx, void* grad_h, void* grad_deg, len_t stride,
+                                              len_t n_edge) {
+  if (id != SINGLE) { set_error(kUnsupported, "zg_scatter_gcn_deg_scaled_bwd: only SINGLE is implemented"); return; }
+  if (n_edge == 0 || stride == 0) return;
+  gcn_scatter_bwd_kernel<<<grid_for(n_edge, kIThreads), kIThreads, 0, as_stream(w)>>>((const float*)grad_out, (const float*)h, (const float*)deg, src_idx, tgt_idx, (float*)grad_h, (float*)grad_deg, stride, n_edge);
+  ZG_LAUNCH_CHECK();
+}

@@ -1,0 +1,437 @@
+"""``CudaDevice``: the host-side device object of this backend.
+
+Python mirror of ``src/device/cuda_device.zig`` (the Zig struct that sits
+behind ``DeviceReference``): it owns one stream, the op contexts, the
+stream-ordered cache and a capture object, offers the ``mem_*`` calls of
+``src/device/device_reference.zig:29-131`` and one method per ``opspec`` name,
+and forwards each of them to the C ABI of ``libamalgamate.so``.  There is no
+other implementation behind it: without the library or without a GPU it raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import abi
+from .abi import BF16, DOUBLE, SINGLE
+
+_NP2ID = {np.dtype(np.float32): SINGLE, np.dtype(np.float64): DOUBLE}
+_ITEMSIZE = {SINGLE: 4, DOUBLE: 8, BF16: 2}
+USIZE = 100  # pseudo dtype id for index buffers (u64); never passed to the library
+
+
+@dataclass
+class DeviceSlice:
+    """A typed view of device memory: Zig's ``[]T`` (plus the cache block handle
+    that ``DeviceData.ctx`` carries when the memory came from ``mem_cache_alloc``)."""
+    ptr: int
+    len: int
+    dtype: int = SINGLE
+    ctx: int = 0
+
+    @property
+    def itemsize(self) -> int:
+        return 8 if self.dtype == USIZE else _ITEMSIZE[self.dtype]
+
+    @property
+    def nbytes(self) -> int:
+        return self.len * self.itemsize
+
+    def view(self, offset: int, length: int) -> "DeviceSlice":
+        assert 0 <= offset and offset + length <= self.len
+        return DeviceSlice(self.ptr + offset * self.itemsize, length, self.dtype, 0)
+
+
+class DeviceOOM(MemoryError):
+    """error.DeviceOOM of src/allocators/device_data.zig:44."""
+
+
+def _shape(s: Sequence[int]):
+    return (abi.len_t * len(s))(*[int(v) for v in s])
+
+
+def _f32(v: float):
+    return C.byref(C.c_float(v))
+
+
+class ExecutionGraph:
+    """CUDA-graph capture of the device stream (cuda_device.zig:558-611)."""
+
+    def __init__(self, dev: "CudaDevice"):
+        self.dev = dev
+        self.wrapper = None
+        self.saved = False
+
+    def open(self):
+        self.free()
+        self.dev.sync()
+        self.wrapper = self.dev.L.open_capture(self.dev.stream)
+        abi.check()
+        self.saved = False
+
+    def save(self):
+        if self.wrapper is not None and not self.saved:
+            self.dev.L.save_capture(self.wrapper, self.dev.stream)
+            abi.check()
+            self.saved = True
+
+    def run(self):
+        if self.wrapper is None:
+            raise RuntimeError("UndefinedCapture")
+        if not self.saved:
+            raise RuntimeError("CaptureInProgress")
+        self.dev.L.run_capture(self.wrapper, self.dev.stream)
+
+    def free(self):
+        self.save()
+        if self.wrapper is not None:
+            self.dev.sync()
+            self.dev.L.free_capture(self.wrapper, self.dev.stream)
+            self.wrapper = None
+
+    def empty(self) -> bool:
+        return self.wrapper is None
+
+
+class CudaDevice:
+    def __init__(self, device_number: int = 0, cache_max_bytes: int = 0, stream: Optional[int] = None):
+        self.L = abi.lib()
+        if not self.L.zg_device_available():
+            raise RuntimeError("CudaDevice: no CUDA device is available (this backend has no CPU fallback)")
+        self.device_number = int(device_number)
+        self.properties = self.L.init_device(self.device_number)
+        abi.check()
+        if stream is None:
+            self.stream = self.L.init_stream()
+            self._own_stream = True
+        else:  # adopt a stream created elsewhere (e.g. by the process's communication library)
+            self.stream = abi.StreamWrapper(stream)
+            self._own_stream = False
+        self.cublas = self.L.init_cublas_handle(self.stream)
+        self.cudnn = self.L.init_cudnn_handle(self.stream)
+        self.cutensor = self.L.init_cutensor_handle(self.stream)
+        self.cache = self.L.zg_cache_create(self.device_number, cache_max_bytes)
+        self.capture = ExecutionGraph(self)
+        abi.check()
+
+    # ------------------------------------------------------------ lifecycle
+    def deinit(self):
+        if self.L is None:
+            return
+        self.sync()
+        self.capture.free()
+        self.L.zg_cache_destroy(self.cache)
+        self.L.deinit_cudnn_handle(self.cudnn)
+        self.L.deinit_cublas_handle(self.cublas)
+        self.L.deinit_cutensor_handle(self.cutensor)
+        if self._own_stream:
+            self.L.deinit_stream(self.stream)
+        self.L = None
+
+    def reference(self):
+        return self
+
+    def is_compatible(self, other: "CudaDevice") -> bool:
+        return self.device_number == other.device_number
+
+    def sync(self):
+        self.L.stream_synchronize(self.stream)
+        abi.check()
+
+    def make_current(self):
+        self.L.zg_set_device(self.device_number)
+
+    # --------------------------------------------------------------- memory
+    def mem_cache_alloc(self, dtype: int, n: int) -> DeviceSlice:
+        size = n * (8 if dtype == USIZE else _ITEMSIZE[dtype])
+        blk = self.L.zg_cache_alloc(self.cache, max(size, 1), self.stream)
+        if not blk.ptr:
+            abi.check()
+            raise DeviceOOM("mem_cache_alloc(%d bytes)" % size)
+        return DeviceSlice(blk.ptr, n, dtype, blk.ctx)
+
+    def mem_cache_free(self, data: DeviceSlice):
+        if data.ctx:
+            self.L.zg_cache_free(self.cache, abi.Block(data.ptr, data.ctx), self.stream)
+            data.ctx = 0
+
+    def mem_cache_dupe(self, src: DeviceSlice) -> DeviceSlice:
+        dst = self.mem_cache_alloc(src.dtype, src.len)
+        self.mem_copy(src, dst)
+        return dst
+
+    def mem_alloc(self, dtype: int, n: int) -> DeviceSlice:
+        if n == 0:
+            return DeviceSlice(0, 0, dtype)
+        size = n * (8 if dtype == USIZE else _ITEMSIZE[dtype])
+        p = self.L.mem_alloc(size, self.stream)
+        if not p:
+            abi.check()
+            raise DeviceOOM("mem_alloc(%d bytes)" % size)
+        return DeviceSlice(p, n, dtype)
+
+    def mem_free(self, s: DeviceSlice):
+        if s.len:
+            self.L.mem_free(s.ptr, self.stream)
+
+    def mem_scratch(self, dtype: int, n: int) -> DeviceSlice:
+        if n == 0:
+            return DeviceSlice(0, 0, dtype)
+        p = self.L.zg_cache_scratch(self.cache, n * _ITEMSIZE[dtype], self.stream)
+        if not p:
+            abi.check()
+            raise DeviceOOM("mem_scratch")
+        return DeviceSlice(p, n, dtype)
+
+    def mem_fill(self, s: DeviceSlice, value: float):
+        v = C.c_float(value) if s.dtype == SINGLE else C.c_double(value)
+        self.L.mem_fill(s.dtype, s.ptr, s.len, C.byref(v), self.stream)
+
+    def mem_sequence(self, s: DeviceSlice, initial: float, step: float):
+        T = C.c_float if s.dtype == SINGLE else C.c_double
+        self.L.mem_sequence(s.dtype, s.ptr, s.len, C.byref(T(initial)), C.byref(T(step)), self.stream)
+
+    def mem_random(self, s: DeviceSlice, op: str, seed: int):
+        self.L.mem_random(s.dtype, s.ptr, s.len, abi.NORMAL if op == "normal" else abi.UNIFORM, seed & 0xFFFFFFFF, self.stream)
+
+    def mem_copy(self, src: DeviceSlice, dst: DeviceSlice):
+        assert src.nbytes == dst.nbytes
+        self.L.memcpy_DtoD(dst.ptr, src.ptr, src.nbytes, self.stream)
+
+    def mem_transfer_htod(self, host: np.ndarray, dst: DeviceSlice):
+        assert host.flags["C_CONTIGUOUS"] and host.nbytes == dst.nbytes, (host.nbytes, dst.nbytes)
+        self.L.memcpy_HtoD(dst.ptr, host.ctypes.data, host.nbytes, self.stream)
+
+    def mem_transfer_dtoh(self, src: DeviceSlice, host: np.ndarray):
+        assert host.flags["C_CONTIGUOUS"] and host.nbytes == src.nbytes
+        self.L.memcpy_DtoH(host.ctypes.data, src.ptr, src.nbytes, self.stream)
+
+    def mem_take(self, src: DeviceSlice, idxs: DeviceSlice, dst: DeviceSlice):
+        assert dst.len >= idxs.len
+        self.L.mem_take(src.dtype, src.ptr, src.len, idxs.ptr, idxs.len, dst.ptr, self.stream)
+
+    def clear_cache(self):
+        self.L.zg_cache_clear(self.cache)
+
+    # numpy conveniences used by the tests and drivers -----------------------
+    def from_numpy(self, a: np.ndarray, cached: bool = True) -> DeviceSlice:
+        a = np.ascontiguousarray(a)
+        if a.dtype == np.uint64:
+            dt = USIZE
+        elif a.dtype == np.uint16:
+            dt = BF16  # raw bfloat16 bit patterns
+        else:
+            dt = _NP2ID[a.dtype]
+        s = self.mem_cache_alloc(dt, a.size) if cached else self.mem_alloc(dt, a.size)
+        if a.size:
+            self.mem_transfer_htod(a, s)
+            self.sync()  # the host array may be a temporary
+        return s
+
+    def to_numpy(self, s: DeviceSlice, shape=None) -> np.ndarray:
+        npdt = {SINGLE: np.float32, DOUBLE: np.float64, USIZE: np.uint64, BF16: np.uint16}[s.dtype]
+        out = np.empty(s.len, npdt)
+        if s.len:
+            self.mem_transfer_dtoh(s, out)
+        self.sync()
+        return out if shape is None else out.reshape(shape)
+
+    # -------------------------------------------------------------- dispatch
+    def dispatch(self, params):
+        """DeviceReference.dispatch: select the method by the op's name."""
+        name = type(params).op_name
+        fn = getattr(self, name, None)
+        if fn is None:
+            raise NotImplementedError("Unimplemented: CudaDevice." + name)
+        return fn(params)
+
+    # element-wise ------------------------------------------------------------
+    def _binary(self, fn, p):
+        fn(p.z.dtype, self.stream, p.x.ptr, p.y.ptr, p.z.ptr, p.x.len, p.y.len, p.z.len)
+
+    def add(self, p):
+        self._binary(self.L.addition, p)
+
+    def sub(self, p):
+        self._binary(self.L.subtraction, p)
+
+    def mul(self, p):
+        self._binary(self.L.multiplication, p)
+
+    def div(self, p):
+        self._binary(self.L.division, p)
+
+    # linear algebra ---------------------------------------------------------
+    def dot(self, p):
+        self.L.dot(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.z.ptr, p.x.len)
+
+    def axpy(self, p):
+        if isinstance(p.alpha, DeviceSlice):
+            self.L.axpy(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.x.len, p.alpha.ptr)
+        else:
+            a = C.c_float(p.alpha) if p.x.dtype == SINGLE else C.c_double(p.alpha)
+            self.L.axpy(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.x.len, C.cast(C.byref(a), C.c_void_p))
+
+    def outer(self, p):
+        self.L.ger(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.A.ptr, p.x.len, p.y.len, p.y.len, p.alpha)
+
+    def transpose(self, p):
+        self.L.zg_transpose(p.A.dtype, self.stream, p.A.ptr, p.B.ptr, p.m, p.n, p.alpha)
+
+    def matvec(self, p):
+        self.L.gemv(p.A.dtype, self.cublas, p.A.ptr, p.x.ptr, p.y.ptr, p.m, p.n, p.trans_a, p.alpha, p.beta)
+
+    def matmul(self, p):
+        self.L.gemm(p.A.dtype, self.cublas, p.A.ptr, p.B.ptr, p.C.ptr, p.m, p.n, p.k, p.trans_a, p.trans_b,
+                    p.lda, p.ldb, p.ldc, p.alpha, p.beta)
+
+    def bmm_acc(self, p):
+        self.L.zg_bmm(p.A.dtype, p.C.dtype, self.stream, p.A.ptr, p.B.ptr, p.C.ptr,
+                      p.A_shape[0], p.B_shape[0], p.C_shape[0], p.C_shape[1], p.C_shape[2], p.A_shape[2],
+                      p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, abi.EPI_NONE, None, None)
+
+    def linear(self, p):
+        epi = {"none": abi.EPI_NONE, "bias": abi.EPI_BIAS, "bias_relu": abi.EPI_BIAS_RELU, "relu_mask": abi.EPI_RELU_MASK}[p.epilogue]
+        nA, nB, nC = p.n_batch
+        self.L.zg_bmm(p.A.dtype, p.C.dtype, self.stream, p.A.ptr, p.B.ptr, p.C.ptr, nA, nB, nC, p.m, p.n, p.k,
+                      p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, epi,
+                      p.bias.ptr if p.bias is not None else None, p.mask_src.ptr if p.mask_src is not None else None)
+
+    def sum(self, p):
+        self.L.reduce_sum(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.x.len)
+
+    def scale(self, p):
+        self.L.scale(p.x.dtype, self.cublas, p.x.ptr, p.x.len, p.alpha)
+
+    def nrm2(self, p):
+        self.L.nrm2(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.x.len)
+
+    def clip_nrm2(self, p):
+        scratch = self.mem_scratch(p.x.dtype, 1)
+        self.L.clip_nrm2(p.x.dtype, self.cublas, p.x.ptr, scratch.ptr, p.x.len, p.max_norm, p.delta)
+
+    # non-linear ---------------------------------------------------------------
+    def _unary(self, op, p, param=0.0):
+        self.L.zg_unary_fwd(p.x.dtype, self.stream, op, p.x.ptr, p.y.ptr, p.x.len, param)
+
+    def exp_fwd(self, p):
+        self._unary(abi.UN_EXP, p)
+
+    def sqrt_fwd(self, p):
+        self._unary(abi.UN_SQRT, p)
+
+    def rsqrt_fwd(self, p):
+        self._unary(abi.UN_RSQRT, p, p.eps)
+
+    def tanh_fwd(self, p):
+        self._unary(abi.UN_TANH, p)
+
+    def sigm_fwd(self, p):
+        self._unary(abi.UN_SIGM, p)
+
+    def exp_bwd(self, p):
+        self.L.zg_unary_bwd(p.y.dtype, self.stream, abi.UN_EXP, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0)
+
+    def tanh_bwd(self, p):
+        self.L.zg_unary_bwd(p.y.dtype, self.stream, abi.UN_TANH, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0)
+
+    def sigm_bwd(self, p):
+        self.L.zg_unary_bwd(p.y.dtype, self.stream, abi.UN_SIGM, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0)
+
+    def sqrt_bwd(self, p):
+        self.L.zg_unary_bwd(p.x.dtype, self.stream, abi.UN_SQRT, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.eps)
+
+    def rsqrt_bwd(self, p):
+        self.L.zg_unary_bwd(p.x.dtype, self.stream, abi.UN_RSQRT, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.eps)
+
+    def relu_fwd(self, p):
+        self.L.relu_fwd(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.x.len)
+
+    def relu_bwd(self, p):
+        self.L.relu_bwd(p.x.dtype, self.stream, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len)
+
+    def relu_inplace_bwd(self, p):
+        self.L.zg_relu_inplace_bwd(p.x.dtype, self.stream, p.x.ptr, p.x_g.ptr, p.x.len)
+
+    def max_fwd(self, p):
+        self.L.max_fwd(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.x.len)
+
+    def max_bwd(self, p):
+        self.L.max_bwd(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len)
+
+    def clamp_fwd(self, p):
+        self.L.clamp(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.x.len, p.min, p.max)
+
+    def clamp_bwd(self, p):
+        self.L.zg_clamp_bwd(p.x.dtype, self.stream, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.min, p.max)
+
+    # reductions ---------------------------------------------------------------
+    def unbroadcast(self, p):
+        self.L.zg_unbroadcast(p.x.dtype, self.stream, p.x.ptr, _shape(p.x_shape), len(p.x_shape), p.y.ptr,
+                              _shape(p.y_shape), len(p.y_shape), p.scratch.ptr if p.scratch is not None and p.scratch.len else None,
+                              p.alpha, p.beta)
+
+    def broadcast(self, p):
+        self.L.zg_broadcast(p.x.dtype, self.stream, p.x.ptr, p.x.len, p.y.ptr, p.y.len, p.alpha, p.beta)
+
+    def sum_along(self, p):
+        self.L.zg_sum_along(p.x.dtype, self.stream, p.x.ptr, _shape(p.x_shape), len(p.x_shape), p.dim, p.y.ptr, p.alpha, p.beta)
+
+    def max_along(self, p):
+        self.L.zg_max_along(p.x.dtype, self.stream, p.x.ptr, _shape(p.x_shape), len(p.x_shape), p.dim, p.y.ptr)
+
+    # index ----------------------------------------------------------------------
+    def scatter_add(self, p):
+        self.L.zg_scatter_add(p.src.dtype, self.stream, p.src.ptr, p.offsets.ptr, p.src.len, p.dst.ptr)
+
+    def scatter_gcn_deg_scaled(self, p):
+        self.L.zg_scatter_gcn_deg_scaled(p.h.dtype, self.stream, p.dst.ptr, p.h.ptr, p.deg.ptr, p.src_indices.ptr,
+                                         p.tgt_indices.ptr, p.stride, p.n_edge)
+
+    def scatter_gcn_deg_scaled_bwd(self, p):
+        self.L.zg_scatter_gcn_deg_scaled_bwd(p.h.dtype, self.stream, p.grad_output.ptr, p.h.ptr, p.deg.ptr,
+                                             p.src_indices.ptr, p.tgt_indices.ptr, p.grad_h.ptr, p.grad_deg.ptr,
+                                             p.stride, p.n_edge)
+
+    def gather_rows(self, src: DeviceSlice, idx: DeviceSlice, rows: int, cols: int, dst: DeviceSlice,
+                    offsets_out: Optional[DeviceSlice] = None):
+        self.L.zg_gather_rows(src.dtype, self.stream, src.ptr, idx.ptr, rows, cols, dst.ptr,
+                              offsets_out.ptr if offsets_out is not None else None)
+
+    # added ops -----------------------------------------------------------------
+    def softmax_ce(self, p):
+        kind = abi.LABEL_INDEX if p.labels.dtype == USIZE else abi.LABEL_ONEHOT
+        div = float(p.loss_div if p.loss_div is not None else p.rows)
+        self.L.zg_softmax_ce_fwd_bwd(p.logits.dtype, self.stream, p.logits.ptr, p.labels.ptr, kind, p.rows, p.classes, div,
+                                     p.loss.ptr, p.grad.ptr if p.grad is not None else None, int(p.accumulate),
+                                     p.probs.ptr if p.probs is not None else None)
+
+    def smooth_l1(self, p):
+        self.L.zg_smooth_l1_fwd_bwd(p.pred.dtype, self.stream, p.pred.ptr, p.target.ptr, p.pred.len, p.beta, p.loss.ptr,
+                                    p.grad.ptr if p.grad is not None else None)
+
+    @staticmethod
+    def _segments(segs):
+        arr = (abi.Segment * len(segs))()
+        for i, (off, ln) in enumerate(segs):
+            arr[i].offset, arr[i].len = int(off), int(ln)
+        return arr
+
+    def sgd(self, p):
+        self.L.zg_sgd_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, self._segments(p.segments), len(p.segments),
+                           p.lr, int(p.clip), p.max_norm, p.delta, p.norms.ptr if p.norms is not None else None)
+
+    def adam(self, p):
+        self.L.zg_adam_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr,
+                            self._segments(p.segments), len(p.segments), p.t_first, p.lr, p.beta1, p.beta2, p.eps,
+                            int(p.clip), p.max_norm, p.delta, p.norms.ptr if p.norms is not None else None,
+                            p.bf16_copy.ptr if p.bf16_copy is not None else None)
+
+    def soft_update(self, src: DeviceSlice, target: DeviceSlice, tau: float):
+        self.L.zg_soft_update(src.dtype, self.stream, src.ptr, target.ptr, src.len, tau)
+
+    def cast(self, src: DeviceSlice, dst: DeviceSlice):
+        self.L.zg_cast(src.dtype, dst.dtype, self.stream, src.ptr, dst.ptr, src.len)
