@@ -25,6 +25,10 @@ EXTERN_C int zg_device_available(void);
 /* Binds the calling thread to a device ordinal (multi-device processes). */
 EXTERN_C void zg_set_device(unsigned device_number);
 
+/* Number of kernel nodes in a saved capture (cuda_utils.h: open_capture /
+ * save_capture): what one run_capture launches. */
+EXTERN_C len_t zg_capture_kernel_count(GraphWrapper graph);
+
 /* --------------------------------------------------------------- math mode
  * How SINGLE-precision GEMMs use the tensor cores:
  *   ZG_MATH_FP32X3  three TF32 passes on an error-compensated hi/lo split
@@ -89,8 +93,11 @@ EXTERN_C void zg_sum_along(dtype id, StreamWrapper stream, const void* x, const 
 /* max_along ignores alpha/beta, as the host does (host_device.zig:853-874) */
 EXTERN_C void zg_max_along(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t ndim,
                            len_t dim, void* y);
-/* opspec.unbroadcast (host_device.zig:709-780); scratch sized by the caller
- * as NDArray.unbroadcast_ does (src/ndarray.zig:697-715) */
+/* opspec.unbroadcast (host_device.zig:709-780).  `scratch` is accepted for
+ * signature compatibility with the op struct and may be NULL: intermediates of
+ * multi-stage reductions are kept in the library's own workspace, because the
+ * size NDArray.unbroadcast_ computes (src/ndarray.zig:697-715) does not cover
+ * a leading fold followed by an interior reduction. */
 EXTERN_C void zg_unbroadcast(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t x_ndim,
                              void* y, const len_t* y_shape, len_t y_ndim, void* scratch,
                              double alpha, double beta);

@@ -296,7 +296,10 @@ def unbroadcast_scratch_len(x_shape, y_shape) -> int:
 
 
 def unbroadcast(x, x_shape, y, y_shape, alpha=1.0, beta=0.0):
-    n = unbroadcast_scratch_len(x_shape, y_shape)
+    # the reference's own sizing rule (unbroadcast_scratch_len) under-allocates
+    # when a leading fold is followed by an interior reduction; give the C
+    # restatement room for the largest intermediate instead of overflowing
+    n = max(unbroadcast_scratch_len(x_shape, y_shape), int(np.prod(x_shape)))
     scratch = np.zeros(max(n, 1), np.float32)
     rc = lib().orc_unbroadcast(_f(x), _shape(x_shape), len_t(len(x_shape)), _f(y), _shape(y_shape),
                                len_t(len(y_shape)), _f(scratch), C.c_float(alpha), C.c_float(beta))

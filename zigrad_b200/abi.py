@@ -163,6 +163,7 @@ SIGNATURES = {
     "zg_clear_error": (None, []),
     "zg_device_available": (i32, []),
     "zg_set_device": (None, [C.c_uint]),
+    "zg_capture_kernel_count": (len_t, [GraphWrapper]),
     "zg_set_math_mode": (None, [i32]),
     "zg_get_math_mode": (i32, []),
     "zg_bmm": (None, [dtype_t, dtype_t, S, vp, vp, vp, len_t, len_t, len_t, len_t, len_t, len_t, b8, b8, len_t, len_t, len_t,

@@ -47,7 +47,7 @@ int sm_count();  // SMs of the current device (cached)
 // Per-stream scratch owned by the library (runtime.cu).  Returns a 256-byte
 // aligned buffer of at least `bytes`; *counters points at 64 zero-initialised
 // unsigned counters that a kernel must leave at zero when it finishes.
-void* workspace(cudaStream_t s, size_t bytes, unsigned** counters);
+void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot = 0);
 
 // gemm.cu: reads (and clears) the per-device flag that a tensor-core kernel
 // raises when one of its bounded waits runs out; allocates the flag on first use.

@@ -185,7 +185,7 @@ static int* tc_error_flag() {
 }
 
 static bool make_tmap(CUtensorMap* map, bool bf16, const void* base, uint64_t inner, uint64_t rows, uint64_t batches, uint64_t ld,
-                      uint32_t box_inner, uint32_t box_rows) {
+                      uint32_t box_inner, uint32_t box_rows, bool atom32) {
   static auto encode = ZG_DRV(cuTensorMapEncodeTiled);
   if (!encode) return false;
   const uint64_t es = bf16 ? 2 : 4;
@@ -194,7 +194,8 @@ static bool make_tmap(CUtensorMap* map, bool bf16, const void* base, uint64_t in
   cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims,
-                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return ZG_CU(r);
 }
@@ -269,11 +270,12 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
 
   CUtensorMap tmA, tmB;
   bool ok;
-  if (a_kmajor) ok = make_tmap(&tmA, bf16, A, k, m, nA, lda, bk, 128);
-  else ok = make_tmap(&tmA, bf16, A, m, k, nA, lda, atom, bk);
+  // MN-major fp32 operands travel in the 128-byte swizzle with 32-byte atoms
+  if (a_kmajor) ok = make_tmap(&tmA, bf16, A, k, m, nA, lda, bk, 128, false);
+  else ok = make_tmap(&tmA, bf16, A, m, k, nA, lda, atom, bk, !bf16);
   if (!ok) return true;  // error recorded
-  if (b_kmajor) ok = make_tmap(&tmB, bf16, B, k, n, nB, ldb, bk, bn);
-  else ok = make_tmap(&tmB, bf16, B, n, k, nB, ldb, atom, bk);
+  if (b_kmajor) ok = make_tmap(&tmB, bf16, B, k, n, nB, ldb, bk, bn, false);
+  else ok = make_tmap(&tmB, bf16, B, n, k, nB, ldb, atom, bk, !bf16);
   if (!ok) return true;
 
   tc::Params p;

@@ -23,8 +23,11 @@
 //   K-major  : slab = rows x 128 bytes of K; 8-row groups are 1024 bytes apart
 //              (SBO); the k-th MMA inside the slab starts 32 bytes further
 //   MN-major : slab = column blocks of 128 bytes of M/N; inside a block the
-//              k rows are 128 bytes apart, 8-row groups 1024 bytes apart (SBO),
-//              column blocks BK*128 bytes apart (LBO)
+//              k rows are 128 bytes apart, swizzle-row groups are SBO apart,
+//              column blocks BK*128 bytes apart (LBO).  16-bit types use the
+//              plain 128-byte swizzle (8-row groups, SBO 1024); 32-bit types
+//              must use the 128-byte swizzle with 32-byte atoms (4-row groups,
+//              SBO 512) -- the only MN-major layout tcgen05 accepts for tf32
 //
 // Every wait on an mbarrier is bounded: when the limit is reached the CTA
 // raises a flag in global memory, stops issuing work, and still releases its
@@ -163,13 +166,14 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Shared-memory matrix descriptor (tcgen05): start address, leading-dimension
 // byte offset and stride byte offset in 16-byte units, descriptor version 1,
 // 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// `layout`: 2 = 128-byte swizzle, 1 = 128-byte swizzle with 32-byte atoms.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;  // version (Blackwell)
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  d |= (uint64_t)layout << 61;
   return d;
 }
 
@@ -301,12 +305,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t b_off = B_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
           const uint32_t a_lbo = A_KMAJOR ? 16 : MT::kBK * kSlabBytes;
           const uint32_t b_lbo = B_KMAJOR ? 16 : MT::kBK * kSlabBytes;
-          const uint64_t da = make_desc(a_hi + a_off, a_lbo, 1024);
-          const uint64_t db = make_desc(b_hi + b_off, b_lbo, 1024);
+          // MN-major 32-bit operands: 32-byte-atom swizzle, 4-row groups
+          constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
+          constexpr uint32_t a_sbo = (a_lay == 1u) ? 512u : 1024u, b_sbo = (b_lay == 1u) ? 512u : 1024u;
+          const uint64_t da = make_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
+          const uint64_t db = make_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
           const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
           if constexpr (X3) {
-            const uint64_t dal = make_desc(a_lo + a_off, a_lbo, 1024);
-            const uint64_t dbl = make_desc(b_lo + b_off, b_lbo, 1024);
+            const uint64_t dal = make_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
+            const uint64_t dbl = make_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
             umma<false>(tmem_d, dal, db, kIdesc, acc);   // Alo * Bhi
             umma<false>(tmem_d, da, dbl, kIdesc, 1u);    // Ahi * Blo
             umma<false>(tmem_d, da, db, kIdesc, 1u);     // Ahi * Bhi

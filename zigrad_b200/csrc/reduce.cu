@@ -342,10 +342,15 @@ __global__ void __launch_bounds__(kRThreads) scaled_copy_kernel(const T* __restr
 
 // HostDevice.unbroadcast (src/device/host_device.zig:709-780) restated on the
 // host side of the launch: the shape logic picks the same sequence of
-// fold_rows / sum_along calls and the same use of `scratch`.
+// fold_rows / sum_along calls.  Intermediates of a multi-stage reduction live
+// in the library's own workspace (two halves used alternately), not in the
+// caller's `scratch`: the reference sizes that buffer from the leading dims
+// only (src/ndarray.zig:697-715), which is too small when a leading fold is
+// followed by an interior reduction, and it reduces scratch into scratch in
+// place, which a parallel kernel cannot do.
 template <typename T>
 void unbroadcast_impl(cudaStream_t s, const T* x, const len_t* x_shape, size_t xnd, T* y, const len_t* y_shape, size_t ynd,
-                      T* scratch, T alpha, T beta) {
+                      T alpha, T beta) {
   const size_t xlen = prod(x_shape, 0, xnd), ylen = prod(y_shape, 0, ynd);
   if (xlen == 0) return;
   if (xlen == ylen) {
@@ -360,21 +365,38 @@ void unbroadcast_impl(cudaStream_t s, const T* x, const len_t* x_shape, size_t x
   while (!ys.empty() && ys.back() == 1) ys.pop_back();
   size_t ones = 0;
   for (len_t v : ys) ones += (v == 1);
-  if (xs.size() > ys.size()) {
+  const bool leading = xs.size() > ys.size();
+  const size_t stages = (leading ? 1 : 0) + ones;
+  T* half[2] = {nullptr, nullptr};
+  if (stages > 1) {  // at least one intermediate result
+    const size_t cap = ((xlen * sizeof(T) + 255) / 256) * 256;
+    char* base = static_cast<char*>(workspace(s, 2 * cap, nullptr, 1));
+    if (!base) return;
+    half[0] = reinterpret_cast<T*>(base);
+    half[1] = reinterpret_cast<T*>(base + cap);
+  }
+  const T* cur = x;
+  int flip = 0;
+  if (leading) {
     const size_t dif = xs.size() - ys.size();
-    T* dst = ones == 0 ? y : scratch;
-    if (ones != 0 && !scratch) { set_error(kBadArgument, "unbroadcast: scratch required"); return; }
-    fold_rows_launch<T>(s, x, dst, 1, prod(xs.data(), 0, dif), prod(xs.data(), dif, xs.size()), alpha, beta);
+    // alpha and beta belong to the LAST stage only: y = alpha * sum + beta * y.
+    // (The host code passes them to every stage, which squares alpha and reads
+    // unwritten scratch through beta whenever two stages run.)
+    T* dst = ones == 0 ? y : half[flip];
+    fold_rows_launch<T>(s, cur, dst, 1, prod(xs.data(), 0, dif), prod(xs.data(), dif, xs.size()), ones == 0 ? alpha : T(1),
+                        ones == 0 ? beta : T(0));
     if (ones == 0) return;
+    cur = dst;
+    flip ^= 1;
     xs.erase(xs.begin(), xs.begin() + dif);
   }
   size_t i = 0;
   while (ones > 0 && i < xs.size()) {
     if (ys[i] == 1 && xs[i] != 1) {
-      const T* xd = (xs.size() == xnd) ? x : scratch;
-      T* yd = (ones == 1) ? y : scratch;
-      if ((xd == scratch || yd == scratch) && !scratch) { set_error(kBadArgument, "unbroadcast: scratch required"); return; }
-      sum_along_impl<T>(s, xd, xs.data(), xs.size(), i, yd, alpha, beta);
+      T* dst = (ones == 1) ? y : half[flip];
+      sum_along_impl<T>(s, cur, xs.data(), xs.size(), i, dst, ones == 1 ? alpha : T(1), ones == 1 ? beta : T(0));
+      cur = dst;
+      flip ^= 1;
       xs.erase(xs.begin() + i);
       ys.erase(ys.begin() + i);
       --ones;
@@ -409,9 +431,10 @@ extern "C" void zg_max_along(dtype id, StreamWrapper w, const void* x, const len
   ZG_FLOAT_SWITCH("zg_max_along", id, (max_along_impl<T>(as_stream(w), (const T*)x, x_shape, ndim, dim, (T*)y)));
 }
 extern "C" void zg_unbroadcast(dtype id, StreamWrapper w, const void* x, const len_t* x_shape, len_t x_ndim, void* y,
-                               const len_t* y_shape, len_t y_ndim, void* scratch, double alpha, double beta) {
+                               const len_t* y_shape, len_t y_ndim, void* /*scratch: unused, see unbroadcast_impl*/, double alpha,
+                               double beta) {
   ZG_FLOAT_SWITCH("zg_unbroadcast", id,
-                  (unbroadcast_impl<T>(as_stream(w), (const T*)x, x_shape, x_ndim, (T*)y, y_shape, y_ndim, (T*)scratch, (T)alpha, (T)beta)));
+                  (unbroadcast_impl<T>(as_stream(w), (const T*)x, x_shape, x_ndim, (T*)y, y_shape, y_ndim, (T)alpha, (T)beta)));
 }
 extern "C" void zg_broadcast(dtype id, StreamWrapper w, const void* x, len_t x_len, void* y, len_t y_len, double alpha, double beta) {
   if (y_len == 0 || x_len == 0) return;

@@ -157,19 +157,21 @@ __global__ void random_kernel(T* __restrict__ p, size_t n, int normal, uint32_t 
 // two-stage reductions and split-K GEMMs live here.  Grown with cudaMalloc on
 // demand (so the first call of a given size must happen outside a stream
 // capture); never shrinks.  The first 256 bytes hold counters that kernels
-// leave at zero when they finish.
+// leave at zero when they finish.  Slot 0 holds kernel partials; slot 1 holds
+// intermediates of multi-stage host-sequenced reductions (which themselves
+// launch kernels that use slot 0).
 struct Workspace {
   void* base = nullptr;
   size_t bytes = 0;
 };
 static std::mutex g_ws_mu;
-static std::map<std::pair<int, cudaStream_t>, Workspace> g_ws;
+static std::map<std::pair<std::pair<int, int>, cudaStream_t>, Workspace> g_ws;
 
-void* workspace(cudaStream_t s, size_t bytes, unsigned** counters) {
+void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot) {
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> lk(g_ws_mu);
-  Workspace& w = g_ws[{dev, s}];
+  Workspace& w = g_ws[{{dev, slot}, s}];
   const size_t need = bytes + 256;
   if (w.bytes < need) {
     size_t cap = w.bytes ? w.bytes : (size_t)1 << 20;
@@ -434,6 +436,21 @@ extern "C" void run_capture(GraphWrapper graph, StreamWrapper stream) {
     return;
   }
   ZG_CUDA(cudaGraphLaunch(b->exec, as_stream(stream)));
+}
+
+extern "C" len_t zg_capture_kernel_count(GraphWrapper graph) {
+  GraphBackend* b = static_cast<GraphBackend*>(graph.ptr);
+  if (!b || !b->graph) return 0;
+  size_t n = 0;
+  if (!ZG_CUDA(cudaGraphGetNodes(b->graph, nullptr, &n)) || n == 0) return 0;
+  std::vector<cudaGraphNode_t> nodes(n);
+  if (!ZG_CUDA(cudaGraphGetNodes(b->graph, nodes.data(), &n))) return 0;
+  len_t kernels = 0;
+  for (size_t i = 0; i < n; ++i) {
+    cudaGraphNodeType t;
+    if (cudaGraphNodeGetType(nodes[i], &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++kernels;
+  }
+  return kernels;
 }
 
 // ======================================================================

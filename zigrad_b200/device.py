@@ -95,6 +95,19 @@ class ExecutionGraph:
     def empty(self) -> bool:
         return self.wrapper is None
 
+    def kernel_count(self) -> int:
+        """Kernel launches one run() performs."""
+        return int(self.dev.L.zg_capture_kernel_count(self.wrapper)) if self.wrapper is not None else 0
+
+    def detach(self):
+        """Hand the saved graph to the caller (several graphs can then coexist,
+        e.g. one per resident input batch); returns an object with run()/free()."""
+        self.save()
+        g = ExecutionGraph(self.dev)
+        g.wrapper, g.saved = self.wrapper, self.saved
+        self.wrapper, self.saved = None, False
+        return g
+
 
 class CudaDevice:
     def __init__(self, device_number: int = 0, cache_max_bytes: int = 0, stream: Optional[int] = None):

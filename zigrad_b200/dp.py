@@ -1,0 +1,65 @@
+"""Data-parallel training step: one process per GPU, the batch sharded by
+contiguous row blocks, ONE all-reduce of the flat gradient buffer between
+backward and the optimizer kernel.
+
+The reference has no distributed code (its roadmap lists "Distributed comms"
+as future work, ``docs/roadmap.norg:74-76``); this module is new.  Plumbing is
+``torch.distributed``: NCCL over NVLink on GPUs, gloo for the CPU tests of the
+host logic.  Parameters and optimizer state are replicated; every rank divides
+its loss and logits gradient by the GLOBAL batch so that the summed gradients
+equal the single-device gradients, and clipping/updates run after the
+all-reduce, exactly as on one device.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import numpy as np
+
+
+def shard_rows(global_batch: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous row block [start, stop) of `rank`; the first
+    (global_batch % world) ranks take one extra row."""
+    if not (0 <= rank < world):
+        raise ValueError("rank %d outside world of %d" % (rank, world))
+    base, extra = divmod(global_batch, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+class _CudaView:
+    """Exposes raw device memory to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, n: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class GradAllReduce:
+    """Sum-all-reduce of a gradient buffer over a torch.distributed group."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self._views = {}
+
+    def host(self, grads: np.ndarray) -> np.ndarray:
+        """In-place sum over ranks of a host array (gloo path)."""
+        import torch
+        t = torch.from_numpy(grads)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+        return grads
+
+    def device(self, grads, torch_stream) -> None:
+        """In-place sum over ranks of a DeviceSlice, enqueued on `torch_stream`
+        (the stream the CudaDevice was created on), so it is ordered after
+        the backward kernels and before the optimizer kernel."""
+        import torch
+        key = (grads.ptr, grads.len)
+        t = self._views.get(key)
+        if t is None:
+            t = torch.as_tensor(_CudaView(grads.ptr, grads.len, "<f4"), device=torch_stream.device)
+            self._views[key] = t
+        with torch.cuda.stream(torch_stream):
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)

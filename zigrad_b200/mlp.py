@@ -1,0 +1,220 @@
+"""MLP training step on the device interface.
+
+Restates what the reference's MNIST example does above the device boundary
+(``examples/mnist/src/model.zig:17-111`` for the model,
+``examples/mnist/src/main-simple.zig:61-71`` for the loop, and the autograd
+backward order of ``src/graph.zig:55-85`` / ``src/ndtensor.zig:780-796,
+1092-1136``) as a fixed sequence of device ops over preallocated buffers, so
+that the whole step can be captured once into a CUDA graph
+(``CudaDevice.capture``) and replayed.
+
+Two op sequences produce the same tensors:
+
+* ``fused=False`` -- exactly the device calls the reference issues: per layer
+  ``bmm_acc`` (beta 0), ``add`` (bias, in place), ``relu_fwd`` (in place); the
+  loss; then per layer ``relu_inplace_bwd``, zero fill + ``unbroadcast``
+  (alpha = beta = 1) for the bias gradient, zero fill + ``bmm_acc`` (beta 1)
+  for dX and dW; then the optimizer.
+* ``fused=True``  -- ``linear`` ops with bias / ReLU / ReLU-mask epilogues and
+  beta = 0 GEMMs (no zero fills): 13 launches for the three-layer model.
+
+Parameters, gradients and optimizer state live in flat buffers in attach
+order (W0, b0, W1, b1, ...), which is what a data-parallel step all-reduces
+(one buffer) and what the multi-tensor optimizer kernels consume.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from . import opspec
+from .abi import BF16, SINGLE
+from .device import CudaDevice, DeviceSlice
+
+
+def kaiming_uniform(dims: Sequence[int], seed: int):
+    """Seeded U(+-sqrt(6/fan_in)) weights and zero biases (synthetic stand-in
+    for the reference's initialiser, examples/mnist/src/model.zig:75-87; the
+    same host arrays are uploaded to every backend under comparison)."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    Ws, bs = [], []
+    for fan_in, fan_out in zip(dims[:-1], dims[1:]):
+        bound = np.sqrt(6.0 / fan_in)
+        Ws.append(g.uniform(-bound, bound, (fan_out, fan_in)).astype(np.float32))
+        bs.append(np.zeros(fan_out, np.float32))
+    return Ws, bs
+
+
+class MlpTrainer:
+    def __init__(self, dev: CudaDevice, dims: Sequence[int], batch: int, weights, biases, opt: str = "sgd",
+                 lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
+                 max_norm: float = 10.0, delta: float = 1e-6, fused: bool = True, loss_div: Optional[int] = None,
+                 index_labels: bool = False, bf16: bool = False):
+        self.dev, self.dims, self.B, self.L = dev, [int(d) for d in dims], int(batch), len(dims) - 1
+        self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
+        self.clip, self.max_norm, self.delta = clip, max_norm, delta
+        self.fused, self.index_labels, self.bf16 = fused, index_labels, bf16
+        self.loss_div = float(loss_div if loss_div is not None else batch)
+        self.t = 0  # Adam's optimizer-wide counter (advances once per tensor per step)
+        if bf16 and not fused:
+            raise ValueError("the bf16 path exists only as fused ops")
+        # flat parameter layout, attach order
+        self.segments, off = [], 0
+        for l in range(self.L):
+            for n in (self.dims[l + 1] * self.dims[l], self.dims[l + 1]):
+                self.segments.append((off, n))
+                off += n
+        self.n_params = off
+        d = dev
+        self.params = d.mem_cache_alloc(SINGLE, off)
+        self.grads = d.mem_cache_alloc(SINGLE, off)
+        self.norms = d.mem_cache_alloc(SINGLE, len(self.segments))
+        flat = np.concatenate([np.concatenate([np.asarray(w, np.float32).ravel(), np.asarray(b, np.float32).ravel()])
+                               for w, b in zip(weights, biases)])
+        d.mem_transfer_htod(flat, self.params)
+        d.mem_fill(self.grads, 0.0)
+        if opt == "adam":
+            self.m, self.v = d.mem_cache_alloc(SINGLE, off), d.mem_cache_alloc(SINGLE, off)
+            d.mem_fill(self.m, 0.0)
+            d.mem_fill(self.v, 0.0)
+        self.W = [self.params.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
+        self.b = [self.params.view(self.segments[2 * l + 1][0], self.segments[2 * l + 1][1]) for l in range(self.L)]
+        self.dW = [self.grads.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
+        self.db = [self.grads.view(self.segments[2 * l + 1][0], self.segments[2 * l + 1][1]) for l in range(self.L)]
+        # activations and their gradients.  bf16 mode: hidden activations and all
+        # backward operands are bf16, logits / loss / parameter gradients fp32.
+        act_t = BF16 if bf16 else SINGLE
+        self.act = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.dims[l + 1]) for l in range(self.L)]
+        self.dact = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.dims[l + 1]) for l in range(self.L)]
+        self.loss = d.mem_cache_alloc(SINGLE, 1)
+        if bf16:
+            self.params_bf16 = d.mem_cache_alloc(BF16, off)
+            d.cast(self.params, self.params_bf16)
+            self.Wb = [self.params_bf16.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
+            self.dlogits_bf16 = d.mem_cache_alloc(BF16, self.B * self.dims[-1])
+        d.sync()
+
+    # ------------------------------------------------------------------ pieces
+    def forward(self, X: DeviceSlice):
+        d, B = self.dev, self.B
+        inp = X
+        for l in range(self.L):
+            K, N = self.dims[l], self.dims[l + 1]
+            last = l + 1 == self.L
+            if self.fused:
+                W = self.Wb[l] if self.bf16 else self.W[l]
+                d.dispatch(opspec.linear(inp, W, self.act[l], B, N, K, False, True, K, K, N, 1.0, 0.0,
+                                         "bias" if last else "bias_relu", self.b[l]))
+            else:
+                d.dispatch(opspec.bmm_acc(inp, self.W[l], self.act[l], (1, B, K), (1, K, N), (1, B, N), False, True, K, K, N, 1.0, 0.0))
+                d.dispatch(opspec.add(self.b[l], self.act[l], self.act[l]))
+                if not last:
+                    d.dispatch(opspec.relu_fwd(self.act[l], self.act[l]))
+            inp = self.act[l]
+        return self.act[-1]
+
+    def loss_and_grad(self, T: DeviceSlice):
+        d, B, C = self.dev, self.B, self.dims[-1]
+        if not self.fused:
+            d.mem_fill(self.dact[-1], 0.0)  # ensure_grad(0), then `+=`
+        d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=not self.fused))
+
+    def backward(self, X: DeviceSlice):
+        d, B = self.dev, self.B
+        for l in range(self.L - 1, -1, -1):
+            K, N = self.dims[l], self.dims[l + 1]
+            a_in = X if l == 0 else self.act[l - 1]
+            dy = self.dact[l]
+            if self.fused:
+                if self.bf16 and l + 1 == self.L:  # fp32 dlogits -> bf16 operand of the backward GEMMs
+                    d.dispatch(opspec.unbroadcast(dy, [B, N], self.db[l], [N], None, 1.0, 0.0))
+                    d.cast(dy, self.dlogits_bf16)
+                    dy = self.dlogits_bf16
+                elif self.bf16:
+                    self._fold_rows_bf16(dy, self.db[l], B, N)
+                else:
+                    d.dispatch(opspec.unbroadcast(dy, [B, N], self.db[l], [N], None, 1.0, 0.0))
+                if l > 0:  # dX = dY . W, zeroed where the previous activation is <= 0
+                    W = self.Wb[l] if self.bf16 else self.W[l]
+                    d.dispatch(opspec.linear(dy, W, self.dact[l - 1], B, K, N, False, False, N, K, K, 1.0, 0.0,
+                                             "relu_mask", None, self.act[l - 1]))
+                d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 0.0))
+            else:
+                if l + 1 < self.L:
+                    d.dispatch(opspec.relu_inplace_bwd(self.act[l], dy))
+                d.mem_fill(self.db[l], 0.0)
+                d.dispatch(opspec.unbroadcast(dy, [B, N], self.db[l], [N], None, 1.0, 1.0))
+                if l > 0:
+                    d.mem_fill(self.dact[l - 1], 0.0)
+                    d.dispatch(opspec.bmm_acc(dy, self.W[l], self.dact[l - 1], (1, B, N), (1, N, K), (1, B, K), False, False, N, K, K, 1.0, 1.0))
+                d.mem_fill(self.dW[l], 0.0)
+                d.dispatch(opspec.bmm_acc(dy, a_in, self.dW[l], (1, N, B), (1, B, K), (1, N, K), True, False, N, K, K, 1.0, 1.0))
+
+    def _fold_rows_bf16(self, dy, db, B, N):
+        # bias gradient of a bf16 activation gradient: ones[1,B] . dY[B,N] on the tensor cores
+        if not hasattr(self, "_ones_bf16"):
+            ones = self.dev.mem_cache_alloc(SINGLE, self.B)
+            self.dev.mem_fill(ones, 1.0)
+            self._ones_bf16 = self.dev.mem_cache_alloc(BF16, self.B)
+            self.dev.cast(ones, self._ones_bf16)
+            self.dev.sync()
+            self.dev.mem_cache_free(ones)
+        self.dev.dispatch(opspec.linear(self._ones_bf16, dy, db, 1, N, B, False, False, B, N, N, 1.0, 0.0))
+
+    def update(self):
+        d = self.dev
+        if self.opt == "sgd":
+            d.dispatch(opspec.sgd(self.params, self.grads, self.segments, self.lr, self.clip, self.max_norm, self.delta, self.norms))
+        elif self.opt == "adam":
+            d.dispatch(opspec.adam(self.params, self.grads, self.m, self.v, self.segments, self.t + 1, self.lr, self.beta1,
+                                   self.beta2, self.eps, self.clip, self.max_norm, self.delta, self.norms,
+                                   self.params_bf16 if self.bf16 else None))
+            self.t += len(self.segments)
+        elif self.opt != "none":
+            raise ValueError(self.opt)
+
+    # -------------------------------------------------------------------- step
+    def step(self, X: DeviceSlice, T: DeviceSlice, allreduce: Optional[Callable[[DeviceSlice], None]] = None):
+        """forward + loss + backward [+ gradient all-reduce] + update, all
+        asynchronous on the device stream.  The loss stays in ``self.loss``."""
+        self.forward(X)
+        self.loss_and_grad(T)
+        self.backward(X)
+        if allreduce is not None:
+            allreduce(self.grads)
+        self.update()
+
+    def read_loss(self) -> float:
+        return float(self.dev.to_numpy(self.loss)[0])
+
+    # ------------------------------------------------------------- inspection
+    def get_params(self):
+        flat = self.dev.to_numpy(self.params)
+        return self._split(flat)
+
+    def get_grads(self):
+        return self._split(self.dev.to_numpy(self.grads))
+
+    def _split(self, flat):
+        Ws, bs = [], []
+        for l in range(self.L):
+            o, n = self.segments[2 * l]
+            Ws.append(flat[o:o + n].reshape(self.dims[l + 1], self.dims[l]).copy())
+            o, n = self.segments[2 * l + 1]
+            bs.append(flat[o:o + n].copy())
+        return Ws, bs
+
+    def free(self):
+        d = self.dev
+        d.sync()
+        for s in [self.params, self.grads, self.norms, self.loss] + self.act + self.dact:
+            d.mem_cache_free(s)
+        if self.opt == "adam":
+            d.mem_cache_free(self.m)
+            d.mem_cache_free(self.v)
+        if self.bf16:
+            d.mem_cache_free(self.params_bf16)
+            d.mem_cache_free(self.dlogits_bf16)
+            if hasattr(self, "_ones_bf16"):
+                d.mem_cache_free(self._ones_bf16)
