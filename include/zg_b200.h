@@ -54,14 +54,19 @@ EXTERN_C int zg_get_math_mode(void);
  *   ZG_EPI_BIAS_RELU  max(0, . + bias[j])     (+ nn.relu_, src/nn/nn.zig:39-62)
  *   ZG_EPI_RELU_MASK  0 where mask_src[i,j] <= 0 (relu_inplace_bwd on the result,
  *                     src/device/host_device.zig:543-547); mask_src has C's shape and ld
- * bias is fp32 [n]; mask_src has C's element type. */
+ * bias is fp32 [n]; mask_src has C's element type.
+ * colsum (optional, fp32 [n]): the column sums of the values stored to C are
+ * ADDED to it with fp32 atomics (order not fixed) -- the bias gradient that
+ * InplaceAddBwd's unbroadcast (src/ndtensor.zig:783-788) would compute from C
+ * in a separate pass.  Not available together with split-K (plain epilogue,
+ * deep k, few tiles). */
 enum { ZG_EPI_NONE = 0, ZG_EPI_BIAS = 1, ZG_EPI_BIAS_RELU = 2, ZG_EPI_RELU_MASK = 3 };
 EXTERN_C void zg_bmm(dtype id, dtype c_id, StreamWrapper stream,
                      const void* A, const void* B, void* C,
                      len_t nA, len_t nB, len_t nC, len_t m, len_t n, len_t k,
                      bool trans_a, bool trans_b, len_t lda, len_t ldb, len_t ldc,
                      double alpha, double beta,
-                     int epilogue, const void* bias, const void* mask_src);
+                     int epilogue, const void* bias, const void* mask_src, void* colsum);
 
 /* ------------------------------------------------------------- elementwise */
 /* opspec.relu_inplace_bwd (host_device.zig:543-547): if (x <= 0) x_g = 0 */
@@ -116,11 +121,16 @@ EXTERN_C void zg_broadcast(dtype id, StreamWrapper stream, const void* x, len_t 
  * loss_out is ONE device scalar (overwritten); probs_out (optional) receives
  * p.  loss_div = the batch size; a data-parallel shard passes the GLOBAL
  * batch and sums loss_out over the shards.  accumulate != 0 adds into dlogits
- * (the reference's `+=` into a zero-filled gradient), 0 overwrites. */
+ * (the reference's `+=` into a zero-filled gradient), 0 overwrites.
+ * ld = row stride (elements) of logits, dlogits and probs_out (0 means C);
+ * one-hot labels are contiguous [rows, C].  dbias (optional, fp32 [C],
+ * C <= 1024) receives the column sums of (p - t)/loss_div, i.e. the bias
+ * gradient of the layer that produced the logits (what InplaceAddBwd's
+ * unbroadcast computes, src/ndtensor.zig:783-788), saving a pass over dlogits. */
 enum { ZG_LABEL_ONEHOT = 0, ZG_LABEL_INDEX = 1 };
 EXTERN_C void zg_softmax_ce_fwd_bwd(dtype id, StreamWrapper stream, const void* logits, const void* labels,
-                                    int label_kind, len_t rows, len_t C, double loss_div,
-                                    void* loss_out, void* dlogits, int accumulate, void* probs_out);
+                                    int label_kind, len_t rows, len_t C, len_t ld, double loss_div,
+                                    void* loss_out, void* dlogits, int accumulate, void* probs_out, void* dbias);
 /* Smooth-L1 / Huber, mean reduction (src/nn/loss.zig:259-305):
  * loss_out[0] = mean(huber(pred - target)) (overwritten);
  * grad += d/(beta*n) or sign(d)/n  (when grad != NULL) */

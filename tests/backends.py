@@ -186,12 +186,15 @@ class GpuBackend:
         self.d.dispatch(opspec.bmm_acc(a, b, c, As, Bs, Cs, ta, tb, lda, ldb, ldc, alpha, beta))
         return self.down(c, np.asarray(C).shape)
 
-    def linear(self, A, B, C, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias=None, mask=None):
+    def linear(self, A, B, C, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias=None, mask=None, colsum=None):
         a, b, c = self.up(A), self.up(B), self.up(C)
         bs = self.up(bias) if bias is not None else None
         mk = self.up(mask) if mask is not None else None
-        self.d.dispatch(opspec.linear(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bs, mk))
-        return self.down(c, np.asarray(C).shape)
+        cs = self.up(colsum) if colsum is not None else None
+        self.d.dispatch(opspec.linear(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bs, mk, colsum=cs))
+        sums = self.d.to_numpy(cs) if cs is not None else None
+        out = self.down(c, np.asarray(C).shape)
+        return (out, sums) if colsum is not None else out
 
     def matvec(self, A, x, m, n, ta, alpha=1.0, beta=0.0, y=None):
         y0 = np.zeros(n if ta else m, np.float32) if y is None else f32(y)
@@ -344,17 +347,25 @@ class GpuBackend:
         gh = self.d.to_numpy(GH)
         return gh, self.down(GD)
 
-    def softmax_ce(self, logits, target, loss_div=None, grad0=None, index_labels=None):
+    def softmax_ce(self, logits, target, loss_div=None, grad0=None, index_labels=None, ld=0, want_bias=False):
         logits = f32(logits)
         rows, Cc = (1, logits.shape[0]) if logits.ndim == 1 else logits.shape
-        X = self.up(logits)
+        ldv = ld if ld else Cc
+        padded = np.zeros((rows, ldv), np.float32)
+        padded[:, :Cc] = logits.reshape(rows, Cc)
+        g0 = np.zeros((rows, ldv), np.float32)
+        if grad0 is not None:
+            g0[:, :Cc] = f32(grad0).reshape(rows, Cc)
+        X = self.up(padded)
         T = self.up(index_labels, np.uint64) if index_labels is not None else self.up(target)
-        G = self.up(np.zeros(logits.size, np.float32) if grad0 is None else grad0)
-        P, Ls = self.up(np.zeros(logits.size, np.float32)), self.scalar()
-        self.d.dispatch(opspec.softmax_ce(X, T, rows, Cc, Ls, G, loss_div, True, P))
-        g = self.d.to_numpy(G, logits.shape)
-        pr = self.d.to_numpy(P, logits.shape)
-        return float(self.down(Ls)[0]), g, pr
+        G, P, Ls = self.up(g0), self.up(np.zeros((rows, ldv), np.float32)), self.scalar()
+        Bg = self.up(np.zeros(Cc, np.float32)) if want_bias else None
+        self.d.dispatch(opspec.softmax_ce(X, T, rows, Cc, Ls, G, loss_div, True, P, ld, Bg))
+        g = self.d.to_numpy(G, (rows, ldv))[:, :Cc].reshape(logits.shape)
+        pr = self.d.to_numpy(P, (rows, ldv))[:, :Cc].reshape(logits.shape)
+        bias = self.d.to_numpy(Bg) if want_bias else None
+        loss = float(self.down(Ls)[0])
+        return (loss, g, pr, bias) if want_bias else (loss, g, pr)
 
     def smooth_l1(self, pred, target, beta):
         Pd, T = self.up(pred), self.up(target)

@@ -129,6 +129,29 @@ def test_linear_fused_epilogues_equal_separate_ops(gpu, mode, m, n, k):
         gpu.L.zg_set_math_mode(abi.MATH_FP32X3)
 
 
+@pytest.mark.parametrize("mode", ["ffma", "fp32x3"])
+@pytest.mark.parametrize("m,n,k", [(8192, 128, 64), (1024, 64, 12), (300, 100, 40), (33, 17, 9)])
+def test_gemm_epilogue_column_sums_are_the_bias_gradient(gpu, mode, m, n, k):
+    """dX GEMM with the ReLU mask AND the column sums of what it stores, added to
+    a pre-existing vector: equals relu_inplace_bwd followed by unbroadcast
+    (alpha = beta = 1) on the oracle."""
+    g = rng(m * 2 + n + k)
+    dY, W = g.standard_normal((m, k)).astype(np.float32), g.standard_normal((k, n)).astype(np.float32)
+    prev = np.maximum(g.standard_normal((m, n)).astype(np.float32), 0)
+    db0 = g.standard_normal(n).astype(np.float32)
+    dx = ORC.bmm_acc(dY, W, np.zeros((m, n), np.float32), (1, m, k), (1, k, n), (1, m, n), False, False, k, n, n, 1.0, 0.0)
+    dx = ORC.relu_inplace_bwd(prev.ravel(), dx.ravel()).reshape(m, n)
+    want_db = ORC.unbroadcast(dx.ravel(), [m, n], db0, [n], 1.0, 1.0)
+    gpu.L.zg_set_math_mode(MODES[mode][0])
+    try:
+        got, sums = GpuBackend(gpu).linear(dY, W, np.zeros((m, n), np.float32), m, n, k, False, False, k, n, n, 1.0, 0.0,
+                                           "relu_mask", mask=prev, colsum=db0)
+    finally:
+        gpu.L.zg_set_math_mode(abi.MATH_FP32X3)
+    assert rel_err(got, dx) <= MODES[mode][1]
+    assert rel_err(sums, want_db) <= 3e-5, rel_err(sums, want_db)
+
+
 def to_bf16_bits(x):
     return (oracle.round_bf16(np.ascontiguousarray(x, np.float32).ravel()).view(np.uint32) >> 16).astype(np.uint16)
 

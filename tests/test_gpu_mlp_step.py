@@ -44,11 +44,10 @@ def test_one_sgd_step_every_tensor(gpu, fused, B):
     got_loss = tr.read_loss()
     assert abs(got_loss - want_loss) <= 1e-4 * abs(want_loss)
     for l in range(3):
-        act = gpu.to_numpy(tr.act[l], (B, DIMS[l + 1]))
-        assert_close("act%d" % l, act, orc.act[l])
-        assert_close("dact%d" % l, gpu.to_numpy(tr.dact[l], (B, DIMS[l + 1])), orc.dact[l])
+        assert_close("act%d" % l, tr.act_numpy(l), orc.act[l])
+        assert_close("dact%d" % l, tr.act_numpy(l, grad=True), orc.dact[l])
     # predictions: argmax of the logits is bit-exact
-    np.testing.assert_array_equal(np.argmax(gpu.to_numpy(tr.act[2], (B, 10)), 1), np.argmax(orc.act[2], 1))
+    np.testing.assert_array_equal(np.argmax(tr.act_numpy(2), 1), np.argmax(orc.act[2], 1))
     gW, gb = tr.get_grads()
     pW, pb = tr.get_params()
     for l in range(3):

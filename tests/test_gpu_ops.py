@@ -235,6 +235,19 @@ def test_softmax_cross_entropy_fused(gpu, rows, C):
     assert abs(l2 - wl2) <= 1e-5 * max(1.0, abs(wl2)) and rel_err(g2, wg2) <= 1e-5
 
 
+@pytest.mark.parametrize("rows,C,ld", [(8192, 10, 12), (64, 10, 16), (33, 1000, 1000), (300, 7, 8)])
+def test_softmax_cross_entropy_row_stride_and_fused_bias_gradient(gpu, rows, C, ld):
+    g = rng(rows * 3 + C)
+    x = (g.standard_normal((rows, C)) * 2).astype(np.float32)
+    t = np.eye(C, dtype=np.float32)[g.integers(0, C, rows)]
+    loss, grad, probs, bias = GpuBackend(gpu).softmax_ce(x, t, ld=ld, want_bias=True)
+    wl, wg, wp = ORC.softmax_ce(x, t)
+    assert abs(loss - wl) <= 1e-5 * max(1.0, abs(wl))
+    assert rel_err(grad, wg) <= 1e-5 and rel_err(probs, wp) <= 1e-5
+    want_bias = ORC.fold_rows(wg.ravel(), rows, C)  # what InplaceAddBwd's unbroadcast would produce
+    assert rel_err(bias, want_bias) <= 1e-5
+
+
 def test_softmax_cross_entropy_accumulates_into_grad(gpu):
     g = rng(1)
     x, g0 = g.standard_normal((16, 10)).astype(np.float32), g.standard_normal((16, 10)).astype(np.float32)

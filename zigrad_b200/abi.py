@@ -167,7 +167,7 @@ SIGNATURES = {
     "zg_set_math_mode": (None, [i32]),
     "zg_get_math_mode": (i32, []),
     "zg_bmm": (None, [dtype_t, dtype_t, S, vp, vp, vp, len_t, len_t, len_t, len_t, len_t, len_t, b8, b8, len_t, len_t, len_t,
-                      dbl, dbl, i32, vp, vp]),
+                      dbl, dbl, i32, vp, vp, vp]),
     "zg_relu_inplace_bwd": (None, [dtype_t, S, vp, vp, len_t]),
     "zg_clamp_bwd": (None, [dtype_t, S, vp, vp, vp, len_t, dbl, dbl]),
     "zg_unary_fwd": (None, [dtype_t, S, i32, vp, vp, len_t, dbl]),
@@ -179,7 +179,7 @@ SIGNATURES = {
     "zg_max_along": (None, [dtype_t, S, vp, lenp, len_t, len_t, vp]),
     "zg_unbroadcast": (None, [dtype_t, S, vp, lenp, len_t, vp, lenp, len_t, vp, dbl, dbl]),
     "zg_broadcast": (None, [dtype_t, S, vp, len_t, vp, len_t, dbl, dbl]),
-    "zg_softmax_ce_fwd_bwd": (None, [dtype_t, S, vp, vp, i32, len_t, len_t, dbl, vp, vp, i32, vp]),
+    "zg_softmax_ce_fwd_bwd": (None, [dtype_t, S, vp, vp, i32, len_t, len_t, len_t, dbl, vp, vp, i32, vp, vp]),
     "zg_smooth_l1_fwd_bwd": (None, [dtype_t, S, vp, vp, len_t, dbl, vp, vp]),
     "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp]),
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp]),

@@ -34,6 +34,7 @@ struct SimtParams {
   int epilogue;
   const float* bias;
   const void* mask;
+  float* colsum;
   unsigned splits;
   size_t k_per_split;
 };
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A
         if (to_acc<TC>(mk[o]) <= AT(0)) v = AT(0);
       }
       c[o] = from_acc<TC, AT>(v);
+      if (p.colsum) atomicAdd(p.colsum + gn, (float)v);
     }
   }
 }
@@ -140,8 +142,9 @@ static void prescale_c(cudaStream_t s, T* C, size_t batches, size_t m, size_t n,
 template <typename TI, typename TC>
 static void launch_simt(cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m, len_t n, len_t k,
                         bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue, const void* bias,
-                        const void* mask) {
+                        const void* mask, void* colsum) {
   SimtParams p;
+  p.colsum = static_cast<float*>(colsum);
   p.nA = nA; p.nB = nB; p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldb = ldb; p.ldc = ldc;
   p.a_stride = (ta ? k : m) * lda; p.b_stride = (tb ? n : k) * ldb; p.c_stride = m * ldc;
   p.ta = ta; p.tb = tb; p.alpha = alpha; p.beta = beta; p.epilogue = epilogue;
@@ -149,7 +152,7 @@ static void launch_simt(cudaStream_t s, const void* A, const void* B, void* C, l
   const size_t tiles = ((m + 63) / 64) * ((n + 63) / 64) * nC;
   unsigned splits = 1;
   // deep-k, few-tile problems (weight gradients): split K over more CTAs
-  if (epilogue == ZG_EPI_NONE && sizeof(TC) >= 4 && k >= 1024 && tiles * 2 <= (size_t)sm_count()) {
+  if (epilogue == ZG_EPI_NONE && !colsum && sizeof(TC) >= 4 && k >= 1024 && tiles * 2 <= (size_t)sm_count()) {
     size_t want = (size_t)sm_count() * 2 / tiles;
     size_t maxs = k / 256;
     splits = (unsigned)(want < maxs ? want : maxs);
@@ -234,7 +237,7 @@ static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor,
 // Returns true when the tensor-core path took the problem.
 static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                             len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
-                            int epilogue, const void* bias, const void* mask) {
+                            int epilogue, const void* bias, const void* mask, void* colsum) {
   const bool bf16 = (id == BF16);
   if (!(id == SINGLE || bf16)) return false;
   if (id == SINGLE && (g_math_mode == ZG_MATH_FFMA || c_id != SINGLE)) return false;
@@ -259,7 +262,7 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   if (bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) { bn = 64; tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC; }
 
   unsigned splits = 1;
-  if (epilogue == ZG_EPI_NONE && c_id == SINGLE && k >= 2048 && tiles * 2 <= (size_t)sm_count()) {
+  if (epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 2048 && tiles * 2 <= (size_t)sm_count()) {
     size_t want = (size_t)sm_count() / tiles;
     size_t maxs = k / 512;
     splits = (unsigned)(want < maxs ? want : maxs);
@@ -283,11 +286,19 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   if (c_id == SINGLE) { p.C = static_cast<float*>(C); p.mask = static_cast<const float*>(mask); }
   else { p.Cb = static_cast<__nv_bfloat16*>(C); p.maskb = static_cast<const __nv_bfloat16*>(mask); }
   p.bias = static_cast<const float*>(bias);
+  p.colsum = static_cast<float*>(colsum);
   p.c_batch_stride = (uint64_t)m * ldc;
   p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k; p.ldc = (uint32_t)ldc;
   p.nA = (uint32_t)nA; p.nB = (uint32_t)nB;
   p.splits = splits; p.k_per_split = (uint32_t)k_per_split;
   p.alpha = (float)alpha; p.beta = (float)beta; p.epilogue = epilogue;
+  {
+    const size_t ce = (c_id == SINGLE) ? 4 : 2;
+    bool ok = host_aligned16(C) && (ldc * ce) % 16 == 0 && ((uint64_t)m * ldc * ce) % 16 == 0;
+    if (mask) ok = ok && host_aligned16(mask);
+    if (bias) ok = ok && host_aligned16(bias);
+    p.vec_ok = ok ? 1 : 0;
+  }
   p.error_flag = tc_error_flag();
   if (splits > 1) prescale_c<float>(s, static_cast<float*>(C), nC, m, n, ldc, m * ldc, beta);
   dim3 grid((unsigned)((n + bn - 1) / bn), (unsigned)((m + 127) / 128), (unsigned)(nC * splits));
@@ -300,17 +311,18 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
 
 void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m,
                   len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue,
-                  const void* bias, const void* mask) {
+                  const void* bias, const void* mask, void* colsum) {
   if (m == 0 || n == 0 || nC == 0) return;
   if (nA == 0 || nB == 0) { set_error(kBadArgument, "bmm: empty operand batch"); return; }
   if (epilogue < ZG_EPI_NONE || epilogue > ZG_EPI_RELU_MASK) { set_error(kBadArgument, "bmm: unknown epilogue %d", epilogue); return; }
   if ((epilogue == ZG_EPI_BIAS || epilogue == ZG_EPI_BIAS_RELU) && !bias) { set_error(kBadArgument, "bmm: bias epilogue without bias"); return; }
   if (epilogue == ZG_EPI_RELU_MASK && !mask) { set_error(kBadArgument, "bmm: mask epilogue without mask source"); return; }
-  if (try_tensor_core(id, c_id, s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask)) return;
-  if (id == SINGLE && c_id == SINGLE) launch_simt<float, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
-  else if (id == DOUBLE && c_id == DOUBLE) launch_simt<double, double>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
-  else if (id == BF16 && c_id == SINGLE) launch_simt<__nv_bfloat16, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
-  else if (id == BF16 && c_id == BF16) launch_simt<__nv_bfloat16, __nv_bfloat16>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask);
+  if (colsum && id == DOUBLE) { set_error(kUnsupported, "bmm: column sums are fp32 only"); return; }
+  if (try_tensor_core(id, c_id, s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum)) return;
+  if (id == SINGLE && c_id == SINGLE) launch_simt<float, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);
+  else if (id == DOUBLE && c_id == DOUBLE) launch_simt<double, double>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);
+  else if (id == BF16 && c_id == SINGLE) launch_simt<__nv_bfloat16, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);
+  else if (id == BF16 && c_id == BF16) launch_simt<__nv_bfloat16, __nv_bfloat16>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);
   else set_error(kUnsupported, "bmm: unsupported dtype combination %d -> %d", (int)id, (int)c_id);
 }
 
@@ -368,13 +380,13 @@ extern "C" int zg_get_math_mode(void) { return g_math_mode; }
 
 extern "C" void zg_bmm(dtype id, dtype c_id, StreamWrapper stream, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                        len_t m, len_t n, len_t k, bool trans_a, bool trans_b, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
-                       int epilogue, const void* bias, const void* mask_src) {
-  bmm_dispatch(id, c_id, as_stream(stream), A, B, C, nA, nB, nC, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, epilogue, bias, mask_src);
+                       int epilogue, const void* bias, const void* mask_src, void* colsum) {
+  bmm_dispatch(id, c_id, as_stream(stream), A, B, C, nA, nB, nC, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, epilogue, bias, mask_src, colsum);
 }
 
 extern "C" void gemm(dtype id, CublasWrapper w, const void* a, const void* b, void* c, len_t m, len_t n, len_t k, bool trans_a,
                      bool trans_b, len_t lda, len_t ldb, len_t ldc, double alpha, double beta) {
-  bmm_dispatch(id, id, as_stream(w), a, b, c, 1, 1, 1, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, ZG_EPI_NONE, nullptr, nullptr);
+  bmm_dispatch(id, id, as_stream(w), a, b, c, 1, 1, 1, m, n, k, trans_a, trans_b, lda, ldb, ldc, alpha, beta, ZG_EPI_NONE, nullptr, nullptr, nullptr);
 }
 
 extern "C" void gemv(dtype id, CublasWrapper w, const void* a, const void* x, void* y, len_t m, len_t n, bool trans_a, double alpha,

@@ -8,13 +8,15 @@
 //               k-slabs into a ring of shared-memory stages (128-byte swizzle)
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma with the
 //               accumulator in tensor memory; also owns the TMEM allocation
-//   warps 2-7   FP32X3 mode only: split every fp32 operand slab into a TF32
-//               "hi" part (in place) and a "lo" remainder (second buffer), so
-//               that Ahi*Bhi + Alo*Bhi + Ahi*Blo recovers fp32-level accuracy
+//   warps 2-7   FP32X3 mode only: for every fp32 operand slab write the
+//               remainder lo = x - tf32(x) to a second buffer.  The MMA reads
+//               only the top 19 bits of an fp32 word (measured: results do not
+//               change when the low 13 bits are cleared first), so the fetched
+//               slab itself serves as "hi" and Ahi*Bhi + Alo*Bhi + Ahi*Blo
+//               recovers fp32-level accuracy
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator (warp q reads TMEM
-//               lanes 32q..32q+31), alpha/beta/bias/ReLU/mask, and a
-//               transpose through shared memory so that global stores are
-//               full 128-byte row segments
+//               lanes 32q..32q+31, one row per thread), alpha/beta/bias/ReLU/
+//               mask in registers, 128-bit row-contiguous global accesses
 //
 // Operand layouts.  A row-major matrix whose contiguous dimension is K is a
 // "K-major" UMMA operand; one whose contiguous dimension is M (or N) is
@@ -54,6 +56,7 @@ struct Params {
   float* C;             // fp32 output (or nullptr when Cb is used)
   __nv_bfloat16* Cb;    // bf16 output
   const float* bias;    // [n] or nullptr
+  float* colsum;        // [n] or nullptr: column sums of the stored values are ADDED here (fp32 atomics)
   const float* mask;    // fp32 mask source with C's layout (when C is fp32)
   const __nv_bfloat16* maskb;
   uint64_t c_batch_stride;  // elements
@@ -64,6 +67,7 @@ struct Params {
   uint32_t k_per_split; // multiple of BK
   float alpha, beta;
   int epilogue;
+  int vec_ok;           // C (and mask, bias) rows allow 16-byte accesses at every 32-column boundary
   int* error_flag;      // set to 1 when a bounded wait ran out
 };
 
@@ -200,7 +204,7 @@ struct SmemLayout {
   static constexpr int kABytes = kBM * kSlabBytes;   // 16 KB
   static constexpr int kBBytes = BN * kSlabBytes;
   static constexpr int kStageBytes = (kABytes + kBBytes) * MT::kBufs;
-  static constexpr int kEpiBytes = 4 * 32 * 33 * 4;  // per-warp 32x33 fp32 transpose tiles
+  static constexpr int kEpiBytes = 0;
   static constexpr int kBudget = 220 * 1024;
   static constexpr int kStagesRaw = (kBudget - kEpiBytes - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -221,7 +225,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // stages need 1024-byte alignment (swizzle atoms)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
-  float* epi_smem = reinterpret_cast<float*>(smem + S * SL::kStageBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * SL::kStageBytes + SL::kEpiBytes);
   uint64_t* full = bars;            // [S] TMA bytes landed
   uint64_t* ready = bars + S;       // [S] (X3) split done
@@ -346,7 +349,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
         h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
         h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
-        a_hi[i] = h;
         a_lo[i] = l;
       }
 #pragma unroll 4
@@ -357,7 +359,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
         h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
         h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
-        b_hi[i] = h;
         b_lo[i] = l;
       }
       fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
@@ -366,54 +367,158 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   // ---------------------------------------------------------------- epilogue
+  // Each epilogue thread owns one accumulator row: 32 consecutive columns per
+  // tcgen05.ld, i.e. one full 128-byte line of C, read (beta / mask) and
+  // written with 128-bit accesses straight from registers.
   if (warp >= 4) {
     const int q = warp - 4;  // TMEM lane quadrant
-    float* tile = epi_smem + q * 32 * 33;
     const bool have_acc = (KT > 0) && mbar_wait(accum, 0, &failed);
     tc_fence_after();
-    const uint32_t row0 = tile_m * kBM + q * 32;
-    const uint64_t c_off = (uint64_t)batch * p.c_batch_stride;
-    if ((KT == 0 || have_acc) && row0 < p.m) {
+    const uint32_t row = tile_m * kBM + q * 32 + lane;
+    const uint64_t c_off = (uint64_t)batch * p.c_batch_stride + (uint64_t)row * p.ldc;
+    const bool row_ok = row < p.m;
+    const bool need_c = p.beta != 0.f, need_m = p.epilogue == ZG_EPI_RELU_MASK;
+    const bool has_bias = p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU;
+    if (KT == 0 || have_acc) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const uint32_t col0 = tile_n * BN + c * 32;
-        if (col0 >= p.n) break;
+        if (col0 >= p.n) break;  // uniform across the warp
         uint32_t r[32];
         if (KT > 0) {
-          tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+          tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);  // warp-collective
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        // registers (thread = row) -> smem -> (thread = column)
+        if (!row_ok && !p.colsum) continue;
+        float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(r[j]);
-        __syncwarp();
-        const uint32_t col = col0 + lane;
-        const bool col_ok = col < p.n;
-        const float bias = (col_ok && p.bias && (p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU)) ? p.bias[col] : 0.f;
-        const uint32_t rows = (p.m - row0) < 32u ? (p.m - row0) : 32u;
-        if (col_ok) {
-          for (uint32_t rr = 0; rr < rows; ++rr) {
-            const uint64_t o = c_off + (uint64_t)(row0 + rr) * p.ldc + col;
-            float v = p.alpha * tile[rr * 33 + lane];
-            if (p.splits > 1) {
-              atomicAdd(p.C + o, v);  // C was pre-scaled by beta; no fused epilogue with split-K
-              continue;
+        for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+        const uint64_t o = c_off + col0;
+        const bool full = p.vec_ok && (col0 + 32 <= p.n);
+        if (!row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        } else if (full) {
+          if (p.splits > 1) {
+            // C was pre-scaled by beta on the host side; no fused epilogue with split-K
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.C + o + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
+            continue;
+          }
+          if (p.C) {  // fp32 C / mask
+            if (need_c) {
+              float4 cv[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) cv[j] = *reinterpret_cast<const float4*>(p.C + o + 4 * j);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { v[4 * j] += p.beta * cv[j].x; v[4 * j + 1] += p.beta * cv[j].y; v[4 * j + 2] += p.beta * cv[j].z; v[4 * j + 3] += p.beta * cv[j].w; }
             }
-            if (p.beta != 0.f) v += p.beta * (p.C ? p.C[o] : __bfloat162float(p.Cb[o]));
-            if (p.epilogue == ZG_EPI_BIAS) v += bias;
-            else if (p.epilogue == ZG_EPI_BIAS_RELU) { v += bias; v = v > 0.f ? v : 0.f; }
-            else if (p.epilogue == ZG_EPI_RELU_MASK) {
-              const float mv = p.mask ? p.mask[o] : __bfloat162float(p.maskb[o]);
-              if (mv <= 0.f) v = 0.f;
+            if (has_bias) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+              }
+              if (p.epilogue == ZG_EPI_BIAS_RELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+              }
+            } else if (need_m) {
+              float4 mv[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) mv[j] = *reinterpret_cast<const float4*>(p.mask + o + 4 * j);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (mv[j].x <= 0.f) v[4 * j] = 0.f;
+                if (mv[j].y <= 0.f) v[4 * j + 1] = 0.f;
+                if (mv[j].z <= 0.f) v[4 * j + 2] = 0.f;
+                if (mv[j].w <= 0.f) v[4 * j + 3] = 0.f;
+              }
             }
-            if (p.C) p.C[o] = v;
-            else p.Cb[o] = __float2bfloat16_rn(v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(p.C + o + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {  // bf16 C / mask: 32 values = 64 bytes = 4 x 16-byte accesses
+            if (need_c) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 u = *reinterpret_cast<const uint4*>(p.Cb + o + 8 * j);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) { const float2 f = __bfloat1622float2(h[t]); v[8 * j + 2 * t] += p.beta * f.x; v[8 * j + 2 * t + 1] += p.beta * f.y; }
+              }
+            }
+            if (has_bias) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+              }
+              if (p.epilogue == ZG_EPI_BIAS_RELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+              }
+            } else if (need_m) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 u = *reinterpret_cast<const uint4*>(p.maskb + o + 8 * j);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 f = __bfloat1622float2(h[t]);
+                  if (f.x <= 0.f) v[8 * j + 2 * t] = 0.f;
+                  if (f.y <= 0.f) v[8 * j + 2 * t + 1] = 0.f;
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 u;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+              *reinterpret_cast<uint4*>(p.Cb + o + 8 * j) = u;
+            }
+          }
+        } else {
+          // ragged edge or unaligned C: element-wise with a column bound
+          const uint32_t ncol = (p.n - col0) < 32u ? (p.n - col0) : 32u;
+#pragma unroll
+          for (uint32_t j = 0; j < 32; ++j) {
+            if (j < ncol) {
+              float x = v[j];
+              if (p.splits > 1) { atomicAdd(p.C + o + j, x); continue; }
+              if (need_c) x += p.beta * (p.C ? p.C[o + j] : __bfloat162float(p.Cb[o + j]));
+              if (has_bias) { x += p.bias[col0 + j]; if (p.epilogue == ZG_EPI_BIAS_RELU) x = x > 0.f ? x : 0.f; }
+              else if (need_m) { if ((p.mask ? p.mask[o + j] : __bfloat162float(p.maskb[o + j])) <= 0.f) x = 0.f; }
+              if (p.C) p.C[o + j] = x;
+              else p.Cb[o + j] = __float2bfloat16_rn(x);
+              v[j] = x;
+            } else {
+              v[j] = 0.f;
+            }
           }
         }
-        __syncwarp();
+        if (p.colsum) {
+          // Column sums of this warp's 32 x 32 block without shared memory: five
+          // exchange rounds, each halving the columns a lane still carries (a lane
+          // keeps the half selected by its own bit); lane j ends with column j.
+#pragma unroll
+          for (int off = 16; off >= 1; off >>= 1) {
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int j = 0; j < off; ++j) {
+              const float send = upper ? v[j] : v[j + off];
+              const float keep = upper ? v[j + off] : v[j];
+              v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+          }
+          if (col0 + lane < p.n) atomicAdd(p.colsum + col0 + lane, v[0]);
+        }
       }
     }
   }

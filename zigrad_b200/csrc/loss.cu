@@ -32,19 +32,97 @@ __device__ __forceinline__ void grid_sum_store(float v, float* sm32, float* part
   if (threadIdx.x == 0 && out) *out = s / divisor;
 }
 
+struct SmceArgs {
+  const float* logits;   // [rows, ld]
+  const void* labels;    // fp32 [rows, C] (contiguous) or u64 [rows]
+  size_t rows;
+  int C;
+  size_t ld;             // row stride of logits / dlogits / probs, in elements
+  float divisor;
+  float* loss_out;
+  float* dlogits;        // [rows, ld] or nullptr
+  int accumulate;
+  float* probs_out;      // [rows, ld] or nullptr
+  float* dbias;          // [C] or nullptr: column sums of (p - t)/divisor
+  float* partial;        // workspace: gridDim.x loss partials, then gridDim.x * C bias partials
+  unsigned* counter;
+};
+
+// Column sums over the whole grid of per-thread values acc[i] (column lane+32i):
+// CTA partials in a fixed warp order -> workspace -> folded by the last CTA
+// (the caller guarantees that this runs in the last CTA only after all
+// partials are visible).
+template <int ITEMS>
+__device__ __forceinline__ void cta_column_partials(const float (&acc)[ITEMS], float* colsum /*smem [32*ITEMS]*/, float* out, int C) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int w = 0; w < kLThreads / 32; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < C) colsum[j] = (w == 0 ? 0.f : colsum[j]) + acc[i];
+      }
+    }
+    __syncthreads();
+  }
+  for (int j = threadIdx.x; j < C; j += blockDim.x) out[j] = colsum[j];
+}
+
+// Tail shared by the softmax-CE kernels: per-CTA loss partial -> workspace; the
+// last CTA (atomic ticket) folds the loss partials and, when requested, the
+// per-CTA bias-gradient partials that every CTA has already written to
+// partial[gridDim.x + cta*C ...], both in a fixed order.
+__device__ __forceinline__ void smce_finish(const SmceArgs& a, float loss_acc, float* sm32) {
+  const int C = a.C;
+  float* bias_partial = a.partial + gridDim.x;
+  const float bs = block_sum<float>(loss_acc, sm32);
+  if (threadIdx.x == 0) a.partial[blockIdx.x] = bs;
+  __threadfence();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(a.counter, 1u);
+    last = (t == gridDim.x - 1);
+    if (last) *a.counter = 0;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  float s = 0.f;
+  for (unsigned k = threadIdx.x; k < gridDim.x; k += blockDim.x) s += __ldcg(a.partial + k);
+  s = block_sum<float>(s, sm32);
+  if (threadIdx.x == 0 && a.loss_out) *a.loss_out = s / a.divisor;
+  if (a.dbias) {
+    // `parts` threads per column, each over every parts-th CTA partial, then a shuffle tree
+    const unsigned parts = (C * 8 <= (int)blockDim.x) ? 8u : ((C * 4 <= (int)blockDim.x) ? 4u : ((C * 2 <= (int)blockDim.x) ? 2u : 1u));
+    const unsigned part = threadIdx.x % parts;
+    const int per_trip = blockDim.x / parts;
+    for (int base = 0; base < C; base += per_trip) {
+      const int j = base + threadIdx.x / parts;
+      float v = 0.f;
+      if (j < C)
+        for (unsigned k = part; k < gridDim.x; k += parts) v += __ldcg(bias_partial + (size_t)k * C + j);
+      for (unsigned o = parts >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (j < C && part == 0) a.dbias[j] = v;
+    }
+  }
+}
+
 // One warp per row; ITEMS = ceil(C/32) logits per lane held in registers, so
 // the logits are read from memory exactly once and dlogits written once.
 template <int ITEMS, bool INDEX_LABELS>
-__global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const float* __restrict__ logits, const void* __restrict__ labels,
-                                                               size_t rows, int C, float divisor, float* loss_out,
-                                                               float* dlogits, int accumulate, float* probs_out,
-                                                               float* partial, unsigned* counter) {
+__global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a) {
   __shared__ float sm32[32];
+  __shared__ float colsum[32 * ITEMS];
   const int lane = threadIdx.x & 31;
+  const int C = a.C;
   const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
   float loss_acc = 0.f;
-  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
-    const float* xr = logits + r * (size_t)C;
+  float bias_acc[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) bias_acc[i] = 0.f;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < a.rows; r += warps) {
+    const float* xr = a.logits + r * a.ld;
     float x[ITEMS];
     float mx = -INFINITY;
 #pragma unroll
@@ -60,8 +138,8 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const float* __re
     se = warp_sum(se);
     const float lse = mx + logf(se);
     size_t label_idx = 0;
-    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(labels)[r];
-    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(labels) + r * (size_t)C;
+    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
+    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       const int j = lane + 32 * i;
@@ -70,30 +148,98 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const float* __re
         const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
         const float safe = fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f);
         if (t != 0.f) loss_acc -= t * logf(safe);
-        const size_t o = r * (size_t)C + j;
-        if (probs_out) probs_out[o] = p;
-        if (dlogits) {
-          const float g = (p - t) / divisor;
-          dlogits[o] = accumulate ? dlogits[o] + g : g;
-        }
+        const size_t o = r * a.ld + j;
+        if (a.probs_out) a.probs_out[o] = p;
+        const float g = (p - t) / a.divisor;
+        bias_acc[i] += g;
+        if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g : g;
       }
     }
   }
-  grid_sum_store(loss_acc, sm32, partial, counter, loss_out, divisor);
+  float* bias_partial = a.partial + gridDim.x;
+  if (a.dbias) cta_column_partials<ITEMS>(bias_acc, colsum, bias_partial + (size_t)blockIdx.x * C, C);
+  smce_finish(a, loss_acc, sm32);
+}
+
+// Narrow rows (C <= 32): one THREAD per row.  All loads of a row are issued at
+// once, the exponentials run without cross-lane traffic, and the bias gradient
+// of the CTA comes from one 32x32 exchange-reduce per warp.
+template <bool INDEX_LABELS>
+__global__ void __launch_bounds__(128) softmax_ce_row_kernel(const SmceArgs a) {
+  __shared__ float sm32[32];
+  __shared__ float wsum[4][32];
+  const int C = a.C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool ok = r < a.rows;
+  float g[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) g[j] = 0.f;
+  float loss_acc = 0.f;
+  if (ok) {
+    const float* xr = a.logits + r * a.ld;
+    float x[32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      x[j] = (j < C) ? xr[j] : -INFINITY;
+      mx = fmaxf(mx, x[j]);
+    }
+    float se = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < C) se += expf(x[j] - mx);
+    const float lse = mx + logf(se);
+    size_t label_idx = 0;
+    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
+    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < C) {
+        const float p = expf(x[j] - lse);
+        const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
+        const float safe = fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f);
+        if (t != 0.f) loss_acc -= t * logf(safe);
+        const size_t o = r * a.ld + j;
+        if (a.probs_out) a.probs_out[o] = p;
+        g[j] = (p - t) / a.divisor;
+        if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g[j] : g[j];
+      }
+    }
+  }
+  if (a.dbias) {
+    // five exchange rounds: lane j ends with the warp's sum of column j
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int j = 0; j < off; ++j) {
+        const float send = upper ? g[j] : g[j + off];
+        const float keep = upper ? g[j + off] : g[j];
+        g[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    wsum[warp][lane] = g[0];
+    __syncthreads();
+    if ((int)threadIdx.x < C) {
+      float s = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += wsum[w][threadIdx.x];
+      a.partial[gridDim.x + (size_t)blockIdx.x * C + threadIdx.x] = s;
+    }
+  }
+  smce_finish(a, loss_acc, sm32);
 }
 
 // Rows wider than 1024: three passes over the row (values come back from L1/L2).
 template <bool INDEX_LABELS>
-__global__ void __launch_bounds__(kLThreads) softmax_ce_wide_kernel(const float* __restrict__ logits, const void* __restrict__ labels,
-                                                                    size_t rows, int C, float divisor, float* loss_out,
-                                                                    float* dlogits, int accumulate, float* probs_out,
-                                                                    float* partial, unsigned* counter) {
+__global__ void __launch_bounds__(kLThreads) softmax_ce_wide_kernel(const SmceArgs a) {
   __shared__ float sm32[32];
   const int lane = threadIdx.x & 31;
+  const int C = a.C;
   const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
   float loss_acc = 0.f;
-  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
-    const float* xr = logits + r * (size_t)C;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < a.rows; r += warps) {
+    const float* xr = a.logits + r * a.ld;
     float mx = -INFINITY;
     for (int j = lane; j < C; j += 32) mx = fmaxf(mx, xr[j]);
     mx = warp_max(mx);
@@ -102,22 +248,22 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_wide_kernel(const float*
     se = warp_sum(se);
     const float lse = mx + logf(se);
     size_t label_idx = 0;
-    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(labels)[r];
-    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(labels) + r * (size_t)C;
+    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
+    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
     for (int j = lane; j < C; j += 32) {
       const float p = expf(xr[j] - lse);
       const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
       const float safe = fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f);
       if (t != 0.f) loss_acc -= t * logf(safe);
-      const size_t o = r * (size_t)C + j;
-      if (probs_out) probs_out[o] = p;
-      if (dlogits) {
-        const float g = (p - t) / divisor;
-        dlogits[o] = accumulate ? dlogits[o] + g : g;
+      const size_t o = r * a.ld + j;
+      if (a.probs_out) a.probs_out[o] = p;
+      if (a.dlogits) {
+        const float g = (p - t) / a.divisor;
+        a.dlogits[o] = a.accumulate ? a.dlogits[o] + g : g;
       }
     }
   }
-  grid_sum_store(loss_acc, sm32, partial, counter, loss_out, divisor);
+  grid_sum_store(loss_acc, sm32, a.partial, a.counter, a.loss_out, a.divisor);
 }
 
 __global__ void __launch_bounds__(kLThreads) smooth_l1_kernel(const float* __restrict__ pred, const float* __restrict__ target, size_t n,
@@ -193,21 +339,37 @@ __global__ void __launch_bounds__(kLThreads) nll_bwd_kernel(const float* __restr
 }
 
 template <bool IDX>
-static void launch_softmax_ce(cudaStream_t s, const float* logits, const void* labels, size_t rows, int C, float divisor, float* loss_out,
-                              float* dlogits, int accumulate, float* probs_out) {
-  unsigned g = grid_for(rows, kLThreads / 32, 8);
-  if (g > 2048) g = 2048;
+static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
+  if (a.C <= 32 && a.rows <= (size_t)128 * 4096) {  // narrow rows: thread per row, grid covers the rows
+    const unsigned gr = (unsigned)((a.rows + 127) / 128);
+    unsigned* counters = nullptr;
+    float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)gr + (a.dbias ? (size_t)gr * a.C : 0)), &counters));
+    if (!partial) return;
+    a.partial = partial;
+    a.counter = counters;
+    softmax_ce_row_kernel<IDX><<<gr, 128, 0, s>>>(a);
+    ZG_LAUNCH_CHECK();
+    return;
+  }
+  // with a bias gradient the last CTA folds gridDim.x partial rows per column: keep the grid small
+  unsigned g = grid_for(a.rows, kLThreads / 32, 8);
+  const unsigned cap = a.dbias ? 128u : 2048u;
+  if (g > cap) g = cap;
   unsigned* counters = nullptr;
-  float* partial = static_cast<float*>(workspace(s, sizeof(float) * g, &counters));
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)g + (a.dbias ? (size_t)g * a.C : 0)), &counters));
   if (!partial) return;
-#define ZG_SMCE(ITEMS) softmax_ce_kernel<ITEMS, IDX><<<g, kLThreads, 0, s>>>(logits, labels, rows, C, divisor, loss_out, dlogits, accumulate, probs_out, partial, counters)
+  a.partial = partial;
+  a.counter = counters;
+  const int C = a.C;
+#define ZG_SMCE(ITEMS) softmax_ce_kernel<ITEMS, IDX><<<g, kLThreads, 0, s>>>(a)
   if (C <= 32) ZG_SMCE(1);
   else if (C <= 64) ZG_SMCE(2);
   else if (C <= 128) ZG_SMCE(4);
   else if (C <= 256) ZG_SMCE(8);
   else if (C <= 512) ZG_SMCE(16);
   else if (C <= 1024) ZG_SMCE(32);
-  else softmax_ce_wide_kernel<IDX><<<g, kLThreads, 0, s>>>(logits, labels, rows, C, divisor, loss_out, dlogits, accumulate, probs_out, partial, counters);
+  else if (a.dbias) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: the fused bias gradient supports C <= 1024"); return; }
+  else softmax_ce_wide_kernel<IDX><<<g, kLThreads, 0, s>>>(a);
 #undef ZG_SMCE
   ZG_LAUNCH_CHECK();
 }
@@ -217,15 +379,20 @@ static void launch_softmax_ce(cudaStream_t s, const float* logits, const void* l
 using namespace zg;
 
 extern "C" void zg_softmax_ce_fwd_bwd(dtype id, StreamWrapper w, const void* logits, const void* labels, int label_kind, len_t rows,
-                                      len_t C, double loss_div, void* loss_out, void* dlogits, int accumulate, void* probs_out) {
+                                      len_t C, len_t ld, double loss_div, void* loss_out, void* dlogits, int accumulate,
+                                      void* probs_out, void* dbias) {
   if (id != SINGLE) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: only SINGLE is implemented"); return; }
   if (rows == 0 || C == 0) return;
   if (C > (len_t)0x7fffffff) { set_error(kBadArgument, "zg_softmax_ce_fwd_bwd: C too large"); return; }
+  if (ld == 0) ld = C;
+  if (ld < C) { set_error(kBadArgument, "zg_softmax_ce_fwd_bwd: ld %lu < C %lu", ld, C); return; }
+  SmceArgs a;
+  a.logits = (const float*)logits; a.labels = labels; a.rows = rows; a.C = (int)C; a.ld = ld; a.divisor = (float)loss_div;
+  a.loss_out = (float*)loss_out; a.dlogits = (float*)dlogits; a.accumulate = accumulate; a.probs_out = (float*)probs_out;
+  a.dbias = (float*)dbias; a.partial = nullptr; a.counter = nullptr;
   cudaStream_t s = as_stream(w);
-  if (label_kind == ZG_LABEL_INDEX)
-    launch_softmax_ce<true>(s, (const float*)logits, labels, rows, (int)C, (float)loss_div, (float*)loss_out, (float*)dlogits, accumulate, (float*)probs_out);
-  else if (label_kind == ZG_LABEL_ONEHOT)
-    launch_softmax_ce<false>(s, (const float*)logits, labels, rows, (int)C, (float)loss_div, (float*)loss_out, (float*)dlogits, accumulate, (float*)probs_out);
+  if (label_kind == ZG_LABEL_INDEX) launch_softmax_ce<true>(s, a);
+  else if (label_kind == ZG_LABEL_ONEHOT) launch_softmax_ce<false>(s, a);
   else set_error(kBadArgument, "zg_softmax_ce_fwd_bwd: unknown label kind %d", label_kind);
 }
 

@@ -84,18 +84,38 @@ __global__ void __launch_bounds__(kRThreads) fold_rows_kernel(const T* __restric
   __syncthreads();
   if (!last) return;
   __threadfence();
-  // final fold by the last CTA, fixed chunk order
+  // final fold by the last CTA: `parts` threads share one output column (each
+  // takes every parts-th chunk, four loads in flight), then a shuffle tree
+  // combines them -- a fixed order, so the result is reproducible
   const size_t ntile = gridDim.y, nb = gridDim.z;
-  for (size_t idx = threadIdx.x; idx < nb * ntile * TILE; idx += blockDim.x) {
+  const size_t outputs = nb * ntile * TILE;
+  const unsigned parts = outputs >= 256 ? 1u : (outputs * 8 <= 256 ? 8u : (outputs * 4 <= 256 ? 4u : (outputs * 2 <= 256 ? 2u : 1u)));
+  const unsigned part = threadIdx.x % parts;
+  const size_t per_trip = blockDim.x / parts;
+  for (size_t base = 0; base < outputs; base += per_trip) {
+    const size_t idx = base + threadIdx.x / parts;
     const size_t bb = idx / (ntile * TILE), rem = idx % (ntile * TILE);
     const size_t tile = rem / TILE, cc = rem % TILE;
     const size_t c = tile * TILE + cc;
-    if (c >= col) continue;
-    const T* p = partial + ((bb * ntile + tile) * chunks) * TILE + cc;
-    T s = T(0);
-    for (size_t k = 0; k < chunks; ++k) s += __ldcg(p + k * TILE);
-    T* yo = y + bb * col + c;
-    *yo = (beta == T(0)) ? alpha * s : alpha * s + beta * (*yo);
+    const bool ok = idx < outputs && c < col;
+    T s0 = T(0), s1 = T(0), s2 = T(0), s3 = T(0);
+    if (ok) {
+      const T* p = partial + ((bb * ntile + tile) * chunks) * TILE + cc;
+      size_t k = part;
+      for (; k + 3 * parts < chunks; k += 4 * parts) {
+        s0 += __ldcg(p + k * TILE);
+        s1 += __ldcg(p + (k + parts) * TILE);
+        s2 += __ldcg(p + (k + 2 * parts) * TILE);
+        s3 += __ldcg(p + (k + 3 * parts) * TILE);
+      }
+      for (; k < chunks; k += parts) s0 += __ldcg(p + k * TILE);
+    }
+    T s = (s0 + s1) + (s2 + s3);
+    for (unsigned o = parts >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (ok && part == 0) {
+      T* yo = y + bb * col + c;
+      *yo = (beta == T(0)) ? alpha * s : alpha * s + beta * (*yo);
+    }
   }
 }
 
@@ -106,13 +126,13 @@ void fold_rows_launch(cudaStream_t s, const T* x, T* y, size_t batch, size_t row
   const bool vec = sizeof(T) == 4 && (col % 4 == 0) && host_aligned16(x);
   const size_t tile = vec ? 128 : 32;
   const size_t col_tiles = (col + tile - 1) / tile;
-  // row chunks: enough CTAs for ~2 per SM, at least 32 rows per CTA, and a
-  // final fold that stays short (<= 256 chunks)
+  // row chunks: enough CTAs for ~2 per SM, at least 64 rows per CTA, and a
+  // final fold that stays short (<= 64 chunks)
   size_t want = (size_t)2 * sm_count() / (col_tiles * batch);
   if (want < 1) want = 1;
-  size_t by_rows = (row + 31) / 32;
+  size_t by_rows = (row + 63) / 64;
   size_t chunks = want < by_rows ? want : by_rows;
-  if (chunks > 256) chunks = 256;
+  if (chunks > 64) chunks = 64;
   if (chunks < 1) chunks = 1;
   if (col_tiles > 65535 || batch > 65535) { set_error(kBadArgument, "fold_rows: shape too large (%zu col tiles, batch %zu)", col_tiles, batch); return; }
   unsigned* counters = nullptr;
@@ -520,7 +540,7 @@ static Plan* keep(CutensorWrapper w, const Plan& p) {
 }
 void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                   len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
-                  int epilogue, const void* bias, const void* mask_src);
+                  int epilogue, const void* bias, const void* mask_src, void* colsum);
 }  // namespace zg
 
 extern "C" CutensorPlanWrapper get_reduce_plan(CutensorWrapper w, dtype id, const len_t* src_dims, const unsigned char* src_syms,
@@ -643,5 +663,5 @@ extern "C" void contraction(CutensorWrapper w, void* plan, const void* A_vals, c
   else if (p->id == DOUBLE) { memcpy(&a, alpha, 8); memcpy(&g, gamma, 8); }
   else { set_error(kUnsupported, "contraction: unsupported dtype"); return; }
   bmm_dispatch(p->id, p->id, as_stream(w), A_vals, x_vals, y_vals, p->nA, p->nB, p->nC, p->m, p->n, p->k, p->ta, p->tb, p->lda, p->ldb,
-               p->ldc, a, g, ZG_EPI_NONE, nullptr, nullptr);
+               p->ldc, a, g, ZG_EPI_NONE, nullptr, nullptr, nullptr);
 }

@@ -304,14 +304,15 @@ class CudaDevice:
     def bmm_acc(self, p):
         self.L.zg_bmm(p.A.dtype, p.C.dtype, self.stream, p.A.ptr, p.B.ptr, p.C.ptr,
                       p.A_shape[0], p.B_shape[0], p.C_shape[0], p.C_shape[1], p.C_shape[2], p.A_shape[2],
-                      p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, abi.EPI_NONE, None, None)
+                      p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, abi.EPI_NONE, None, None, None)
 
     def linear(self, p):
         epi = {"none": abi.EPI_NONE, "bias": abi.EPI_BIAS, "bias_relu": abi.EPI_BIAS_RELU, "relu_mask": abi.EPI_RELU_MASK}[p.epilogue]
         nA, nB, nC = p.n_batch
         self.L.zg_bmm(p.A.dtype, p.C.dtype, self.stream, p.A.ptr, p.B.ptr, p.C.ptr, nA, nB, nC, p.m, p.n, p.k,
                       p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, epi,
-                      p.bias.ptr if p.bias is not None else None, p.mask_src.ptr if p.mask_src is not None else None)
+                      p.bias.ptr if p.bias is not None else None, p.mask_src.ptr if p.mask_src is not None else None,
+                      p.colsum.ptr if p.colsum is not None else None)
 
     def sum(self, p):
         self.L.reduce_sum(p.x.dtype, self.cublas, p.x.ptr, p.y.ptr, p.x.len)
@@ -418,9 +419,10 @@ class CudaDevice:
     def softmax_ce(self, p):
         kind = abi.LABEL_INDEX if p.labels.dtype == USIZE else abi.LABEL_ONEHOT
         div = float(p.loss_div if p.loss_div is not None else p.rows)
-        self.L.zg_softmax_ce_fwd_bwd(p.logits.dtype, self.stream, p.logits.ptr, p.labels.ptr, kind, p.rows, p.classes, div,
+        self.L.zg_softmax_ce_fwd_bwd(p.logits.dtype, self.stream, p.logits.ptr, p.labels.ptr, kind, p.rows, p.classes, p.ld, div,
                                      p.loss.ptr, p.grad.ptr if p.grad is not None else None, int(p.accumulate),
-                                     p.probs.ptr if p.probs is not None else None)
+                                     p.probs.ptr if p.probs is not None else None,
+                                     p.bias_grad.ptr if p.bias_grad is not None else None)
 
     def smooth_l1(self, p):
         self.L.zg_smooth_l1_fwd_bwd(p.pred.dtype, self.stream, p.pred.ptr, p.target.ptr, p.pred.len, p.beta, p.loss.ptr,

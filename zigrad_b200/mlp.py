@@ -15,8 +15,10 @@ Two op sequences produce the same tensors:
   loss; then per layer ``relu_inplace_bwd``, zero fill + ``unbroadcast``
   (alpha = beta = 1) for the bias gradient, zero fill + ``bmm_acc`` (beta 1)
   for dX and dW; then the optimizer.
-* ``fused=True``  -- ``linear`` ops with bias / ReLU / ReLU-mask epilogues and
-  beta = 0 GEMMs (no zero fills): 13 launches for the three-layer model.
+* ``fused=True``  -- one zero fill of the flat gradient buffer, ``linear`` ops
+  with bias / ReLU / ReLU-mask epilogues, bias gradients taken from the loss
+  kernel (last layer) and from the dX GEMM epilogues (hidden layers): 10 kernel
+  launches + 1 memset for the three-layer model.
 
 Parameters, gradients and optimizer state live in flat buffers in attach
 order (W0, b0, W1, b1, ...), which is what a data-parallel step all-reduces
@@ -85,26 +87,40 @@ class MlpTrainer:
         # activations and their gradients.  bf16 mode: hidden activations and all
         # backward operands are bf16, logits / loss / parameter gradients fp32.
         act_t = BF16 if bf16 else SINGLE
-        self.act = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.dims[l + 1]) for l in range(self.L)]
-        self.dact = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.dims[l + 1]) for l in range(self.L)]
+        # Row stride of the logits and their gradient: padded to a multiple of 4
+        # floats in the fused path so that the skinny last-layer GEMMs (n, k or m
+        # = number of classes) satisfy TMA's 16-byte stride rule and run on the
+        # tensor cores; the reference op sequence keeps them contiguous.
+        C = self.dims[-1]
+        self.ld_out = (C + 3) // 4 * 4 if fused else C
+        self.ld = [self.dims[l + 1] if l + 1 < self.L else self.ld_out for l in range(self.L)]
+        self.act = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.ld[l]) for l in range(self.L)]
+        self.dact = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.ld[l]) for l in range(self.L)]
+        if self.ld_out != C:
+            d.mem_fill(self.act[-1], 0.0)
+            d.mem_fill(self.dact[-1], 0.0)
         self.loss = d.mem_cache_alloc(SINGLE, 1)
         if bf16:
             self.params_bf16 = d.mem_cache_alloc(BF16, off)
             d.cast(self.params, self.params_bf16)
             self.Wb = [self.params_bf16.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
-            self.dlogits_bf16 = d.mem_cache_alloc(BF16, self.B * self.dims[-1])
+            self.dlogits_bf16 = d.mem_cache_alloc(BF16, self.B * self.ld_out)
         d.sync()
 
     # ------------------------------------------------------------------ pieces
     def forward(self, X: DeviceSlice):
         d, B = self.dev, self.B
         inp = X
+        if self.fused:
+            # zero_grad (model.zig:57-62) as ONE fill of the flat gradient buffer; the
+            # weight-gradient GEMMs then accumulate with beta = 1 as the reference does
+            d.mem_fill(self.grads, 0.0)
         for l in range(self.L):
             K, N = self.dims[l], self.dims[l + 1]
             last = l + 1 == self.L
             if self.fused:
                 W = self.Wb[l] if self.bf16 else self.W[l]
-                d.dispatch(opspec.linear(inp, W, self.act[l], B, N, K, False, True, K, K, N, 1.0, 0.0,
+                d.dispatch(opspec.linear(inp, W, self.act[l], B, N, K, False, True, K, K, self.ld[l], 1.0, 0.0,
                                          "bias" if last else "bias_relu", self.b[l]))
             else:
                 d.dispatch(opspec.bmm_acc(inp, self.W[l], self.act[l], (1, B, K), (1, K, N), (1, B, N), False, True, K, K, N, 1.0, 0.0))
@@ -118,7 +134,11 @@ class MlpTrainer:
         d, B, C = self.dev, self.B, self.dims[-1]
         if not self.fused:
             d.mem_fill(self.dact[-1], 0.0)  # ensure_grad(0), then `+=`
-        d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=not self.fused))
+        if self.fused:  # the bias gradient of the last layer comes out of the same pass
+            d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=False,
+                                         ld=self.ld_out, bias_grad=self.db[-1]))
+        else:
+            d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=True))
 
     def backward(self, X: DeviceSlice):
         d, B = self.dev, self.B
@@ -127,19 +147,19 @@ class MlpTrainer:
             a_in = X if l == 0 else self.act[l - 1]
             dy = self.dact[l]
             if self.fused:
-                if self.bf16 and l + 1 == self.L:  # fp32 dlogits -> bf16 operand of the backward GEMMs
-                    d.dispatch(opspec.unbroadcast(dy, [B, N], self.db[l], [N], None, 1.0, 0.0))
-                    d.cast(dy, self.dlogits_bf16)
-                    dy = self.dlogits_bf16
-                elif self.bf16:
-                    self._fold_rows_bf16(dy, self.db[l], B, N)
-                else:
-                    d.dispatch(opspec.unbroadcast(dy, [B, N], self.db[l], [N], None, 1.0, 0.0))
+                ldy = self.ld[l]
+                if l + 1 == self.L:
+                    if self.bf16:  # fp32 dlogits -> bf16 operand of the backward GEMMs
+                        d.cast(dy, self.dlogits_bf16)
+                        dy = self.dlogits_bf16
+                # bias gradients: db[L-1] came out of the loss kernel; db[l-1] is the
+                # column sum of the masked dX that this layer's dX GEMM stores
+                # (added by its epilogue into the zero-filled gradient buffer)
                 if l > 0:  # dX = dY . W, zeroed where the previous activation is <= 0
                     W = self.Wb[l] if self.bf16 else self.W[l]
-                    d.dispatch(opspec.linear(dy, W, self.dact[l - 1], B, K, N, False, False, N, K, K, 1.0, 0.0,
-                                             "relu_mask", None, self.act[l - 1]))
-                d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 0.0))
+                    d.dispatch(opspec.linear(dy, W, self.dact[l - 1], B, K, N, False, False, ldy, K, K, 1.0, 0.0,
+                                             "relu_mask", None, self.act[l - 1], colsum=self.db[l - 1]))
+                d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, ldy, K, K, 1.0, 1.0))
             else:
                 if l + 1 < self.L:
                     d.dispatch(opspec.relu_inplace_bwd(self.act[l], dy))
@@ -150,17 +170,6 @@ class MlpTrainer:
                     d.dispatch(opspec.bmm_acc(dy, self.W[l], self.dact[l - 1], (1, B, N), (1, N, K), (1, B, K), False, False, N, K, K, 1.0, 1.0))
                 d.mem_fill(self.dW[l], 0.0)
                 d.dispatch(opspec.bmm_acc(dy, a_in, self.dW[l], (1, N, B), (1, B, K), (1, N, K), True, False, N, K, K, 1.0, 1.0))
-
-    def _fold_rows_bf16(self, dy, db, B, N):
-        # bias gradient of a bf16 activation gradient: ones[1,B] . dY[B,N] on the tensor cores
-        if not hasattr(self, "_ones_bf16"):
-            ones = self.dev.mem_cache_alloc(SINGLE, self.B)
-            self.dev.mem_fill(ones, 1.0)
-            self._ones_bf16 = self.dev.mem_cache_alloc(BF16, self.B)
-            self.dev.cast(ones, self._ones_bf16)
-            self.dev.sync()
-            self.dev.mem_cache_free(ones)
-        self.dev.dispatch(opspec.linear(self._ones_bf16, dy, db, 1, N, B, False, False, B, N, N, 1.0, 0.0))
 
     def update(self):
         d = self.dev
@@ -189,6 +198,15 @@ class MlpTrainer:
         return float(self.dev.to_numpy(self.loss)[0])
 
     # ------------------------------------------------------------- inspection
+    def act_numpy(self, l: int, grad: bool = False) -> np.ndarray:
+        """Activation (or its gradient) of layer l as a [B, dims[l+1]] fp32 array
+        (row padding of the logits stripped, bf16 widened)."""
+        s = (self.dact if grad else self.act)[l]
+        a = self.dev.to_numpy(s)
+        if s.dtype == BF16:
+            a = (a.astype(np.uint32) << 16).view(np.float32)
+        return a.reshape(self.B, self.ld[l])[:, :self.dims[l + 1]].copy()
+
     def get_params(self):
         flat = self.dev.to_numpy(self.params)
         return self._split(flat)
@@ -216,5 +234,3 @@ class MlpTrainer:
         if self.bf16:
             d.mem_cache_free(self.params_bf16)
             d.mem_cache_free(self.dlogits_bf16)
-            if hasattr(self, "_ones_bf16"):
-                d.mem_cache_free(self._ones_bf16)

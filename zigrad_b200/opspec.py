@@ -369,6 +369,8 @@ class softmax_ce:
     loss_div: Optional[float] = None
     accumulate: bool = True
     probs: Optional[Any] = None
+    ld: int = 0                      # row stride of logits / grad / probs (0 = classes)
+    bias_grad: Optional[Any] = None  # [classes]: column sums of the gradient written
 
 
 @_op("smooth_l1")
@@ -436,3 +438,4 @@ class linear:
     bias: Optional[Any] = None
     mask_src: Optional[Any] = None
     n_batch: tuple = field(default=(1, 1, 1))
+    colsum: Optional[Any] = None  # fp32 [n]: column sums of the stored C are added here (a bias gradient)
