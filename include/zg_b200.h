@@ -91,6 +91,27 @@ EXTERN_C void zg_transpose(dtype id, StreamWrapper stream, const void* A, void* 
  * reduce.zig:49-164 and host_device.zig:709-874.  y = alpha*reduce + beta*y. */
 EXTERN_C void zg_fold_rows(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
                            double alpha, double beta);               /* [row,col] -> [col] */
+/* Same result as zg_fold_rows for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its reductions go through cuTENSOR with a
+ * caller-supplied workspace.)  Who needs it: code that runs while a stream is
+ * being captured into a CUDA graph, latency-critical loops such as an agent
+ * acting inside a simulator tick, and hosts whose device-memory budget is
+ * fixed and audited up front.  zg_fold_rows keeps its cross-CTA partial sums
+ * in a library workspace that grows with cudaMalloc on first use; this entry
+ * point keeps them in a fixed ~256 KiB array that is part of the library
+ * image (resident on every GPU that loads the library until the process
+ * exits) and calls no cudaMalloc, cudaFree or any other allocating routine.
+ * Limit: the fixed array holds 65536 fp32 (32768 fp64) partial sums, so
+ * col must be <= 65536 (fp32; rounded up to a multiple of 128, or of 32 when
+ * x is not 16-byte aligned or col is not a multiple of 4) -- wider inputs are
+ * rejected with a kBadArgument status and a message that names the limit.
+ * The FIRST call on each device resolves the array's device address
+ * (cudaGetSymbolAddress); make that call before starting any stream capture.
+ * Every call shares the one array per device and leaves its partial sums
+ * there, so calls that overlap on the GPU (other streams) race; issue them on
+ * one stream or order them with events. */
+EXTERN_C void zg_fold_rows_noalloc(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
+                                   double alpha, double beta);
 EXTERN_C void zg_fold_cols(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
                            double alpha, double beta);               /* [row,col] -> [row] */
 EXTERN_C void zg_sum_along(dtype id, StreamWrapper stream, const void* x, const len_t* x_shape, len_t ndim,

@@ -174,6 +174,7 @@ SIGNATURES = {
     "zg_unary_bwd": (None, [dtype_t, S, i32, vp, vp, vp, len_t, dbl]),
     "zg_transpose": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl]),
     "zg_fold_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl, dbl]),
+    "zg_fold_rows_noalloc": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl, dbl]),
     "zg_fold_cols": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl, dbl]),
     "zg_sum_along": (None, [dtype_t, S, vp, lenp, len_t, len_t, vp, dbl, dbl]),
     "zg_max_along": (None, [dtype_t, S, vp, lenp, len_t, len_t, vp]),

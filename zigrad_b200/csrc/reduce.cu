@@ -9,6 +9,7 @@
 // therefore deterministic run to run; no float atomics are used.
 #include <cfloat>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -664,4 +665,93 @@ extern "C" void contraction(CutensorWrapper w, void* plan, const void* A_vals, c
   else { set_error(kUnsupported, "contraction: unsupported dtype"); return; }
   bmm_dispatch(p->id, p->id, as_stream(w), A_vals, x_vals, y_vals, p->nA, p->nB, p->nC, p->m, p->n, p->k, p->ta, p->tb, p->lda, p->ldb,
                p->ldc, a, g, ZG_EPI_NONE, nullptr, nullptr, nullptr);
+}
+
+// ----------------------------------------------------------------------------
+// zg_fold_rows_noalloc: fold_rows for callers that must not allocate.
+//
+// Some users of this library run where device allocation is off the table:
+// a hook that executes while a CUDA graph is being captured or replayed, a
+// real-time control loop (the DQN agent acting inside a simulator tick), or a
+// host process whose memory budget is fixed up front and audited.  zg_fold_rows
+// keeps its cross-CTA partial sums in a workspace that the library grows with
+// cudaMalloc the first time a shape needs it; this variant keeps them in a
+// fixed array that is part of the library image instead.
+//
+// The array lives in device memory of every GPU that loads the library until
+// the process exits (kNoAllocBytes, about a quarter of a megabyte).  In host
+// code its NAME is only a stand-in for the symbol, not a device address; the
+// address is obtained once per device with cudaGetSymbolAddress (with that
+// device current) and that pointer is what the kernel receives.
+//
+// Sharing: there is ONE array per device.  Every call uses it and leaves its
+// last partial sums behind; two calls that overlap on the GPU (different
+// streams, or graphs replayed concurrently) race on it.  The ticket counter at
+// its head must be zero when a kernel starts, so each call clears it on the
+// caller's stream before launching.
+// ----------------------------------------------------------------------------
+namespace zg {
+constexpr size_t kNoAllocCounterBytes = 256;
+constexpr size_t kNoAllocPartialBytes = 256 * 1024;            // partial sums: 65536 floats / 32768 doubles
+constexpr size_t kNoAllocBytes = kNoAllocCounterBytes + kNoAllocPartialBytes;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+static std::mutex g_noalloc_mu;
+static void* g_noalloc_addr[64] = {nullptr};  // per device ordinal, resolved on first use
+
+// Device address of the static scratch array on the current device (no allocation).
+static void* noalloc_scratch_address() {
+  int dev = 0;
+  if (!ZG_CUDA(cudaGetDevice(&dev))) return nullptr;
+  if (dev < 0 || dev >= 64) { set_error(kBadArgument, "zg_fold_rows_noalloc: device ordinal %d out of range", dev); return nullptr; }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_addr[dev]) {
+    void* ptr = nullptr;
+    if (!ZG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch))) return nullptr;
+    g_noalloc_addr[dev] = ptr;
+  }
+  return g_noalloc_addr[dev];
+}
+
+template <typename T>
+static void fold_rows_noalloc_launch(cudaStream_t s, const T* x, T* y, size_t row, size_t col, T alpha, T beta) {
+  if (row == 0 || col == 0) return;
+  const bool vec = sizeof(T) == 4 && (col % 4 == 0) && host_aligned16(x);
+  const size_t tile = vec ? 128 : 32;
+  const size_t col_tiles = (col + tile - 1) / tile;
+  const size_t capacity = kNoAllocPartialBytes / sizeof(T);  // partial sums the fixed array can hold
+  if (col_tiles > 65535 || col_tiles * tile > capacity) {
+    set_error(kBadArgument,
+              "zg_fold_rows_noalloc: %zu columns need %zu partial sums per row chunk but the fixed scratch holds %zu "
+              "(limit: %zu columns for this element type and alignment); use zg_fold_rows for wider inputs",
+              col, col_tiles * tile, capacity, capacity / tile * tile);
+    return;
+  }
+  // same chunking rule as zg_fold_rows, additionally bounded by the fixed capacity
+  size_t want = (size_t)2 * sm_count() / col_tiles;
+  if (want < 1) want = 1;
+  const size_t by_rows = (row + 63) / 64;
+  size_t chunks = want < by_rows ? want : by_rows;
+  if (chunks > 64) chunks = 64;
+  const size_t fit = capacity / (col_tiles * tile);
+  if (chunks > fit) chunks = fit;
+  if (chunks < 1) chunks = 1;
+  unsigned char* base = static_cast<unsigned char*>(noalloc_scratch_address());
+  if (!base) return;
+  unsigned* counters = reinterpret_cast<unsigned*>(base);
+  T* partial = reinterpret_cast<T*>(base + kNoAllocCounterBytes);
+  // the ticket counter must start at zero (an earlier call may have been cut short)
+  if (!ZG_CUDA(cudaMemsetAsync(counters, 0, kNoAllocCounterBytes, s))) return;
+  dim3 grid((unsigned)chunks, (unsigned)col_tiles, 1);
+  if (vec) {
+    if constexpr (sizeof(T) == 4) fold_rows_kernel<T, true><<<grid, kRThreads, 0, s>>>(x, y, partial, counters, row, col, alpha, beta);
+  } else {
+    fold_rows_kernel<T, false><<<grid, kRThreads, 0, s>>>(x, y, partial, counters, row, col, alpha, beta);
+  }
+  ZG_LAUNCH_CHECK();
+}
+}  // namespace zg
+
+extern "C" void zg_fold_rows_noalloc(dtype id, StreamWrapper w, const void* x, void* y, len_t row, len_t col, double alpha, double beta) {
+  ZG_FLOAT_SWITCH("zg_fold_rows_noalloc", id, (fold_rows_noalloc_launch<T>(as_stream(w), (const T*)x, (T*)y, row, col, (T)alpha, (T)beta)));
 }
