@@ -224,9 +224,29 @@ def run_gpu(args, rank, local_rank, world):
     for i in range(args.warmup):
         step(i)
     barrier()
+    # The timed region lasts milliseconds, nvidia-smi samples every 100 ms: keep the
+    # GPU under the SAME load (untimed steps) until the sampler has delivered a
+    # sample, time the K steps, then keep the load on until a few more arrive.
     sampler = ClockSampler(local_rank)
+
+    def load_until(n_samples, limit_s):
+        t0 = time.time()
+        j = 0
+        if world > 1:  # ranks must stay in lockstep: a fixed number of steps instead of a condition only rank 0 sees
+            for j in range(1500):
+                step(j)
+            dev.sync()
+            return
+        while len(sampler.lines) < n_samples and time.time() - t0 < limit_s:
+            for _ in range(50):
+                step(j)
+                j += 1
+            dev.sync()
+
     if rank == 0:
         sampler.start()
+    load_until(2, 4.0)
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(ts)
     for i in range(args.steps):
@@ -234,6 +254,7 @@ def run_gpu(args, rank, local_rank, world):
     e1.record(ts)
     barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
+    load_until(len(sampler.lines) + 3, 2.0)
     clocks = sampler.stop() if rank == 0 else None
     value = args.steps * global_B / (ms / 1e3)
     loss_after = tr.read_loss()

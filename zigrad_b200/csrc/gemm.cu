@@ -258,13 +258,20 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   int bn = n <= 32 ? 32 : (n <= 64 ? 64 : 128);
   if (bn < atom) bn = atom;               // MN-major B needs whole column blocks; bf16 has no BN=32 instance
   size_t tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
-  // few wide tiles: halve BN to put more SMs to work
-  if (bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) { bn = 64; tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC; }
+  // Deep-k problems with a plain epilogue (weight gradients) get their
+  // parallelism from K splits, so they keep the wide tile (fewer operand bytes
+  // per flop through shared memory); everything else halves BN when there are
+  // too few tiles to occupy the SMs.
+  const bool can_split = epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 1024;
+  if (!can_split && bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) {
+    bn = 64;
+    tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
+  }
 
   unsigned splits = 1;
-  if (epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 2048 && tiles * 2 <= (size_t)sm_count()) {
+  if (can_split && tiles * 2 <= (size_t)sm_count()) {
     size_t want = (size_t)sm_count() / tiles;
-    size_t maxs = k / 512;
+    size_t maxs = k / (4 * (size_t)bk);  // at least four k-slabs per split
     splits = (unsigned)(want < maxs ? want : maxs);
     if (splits < 1) splits = 1;
   }
