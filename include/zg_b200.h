@@ -176,11 +176,15 @@ EXTERN_C void zg_sgd_step(dtype id, StreamWrapper stream, void* params, void* gr
 /* Adam.update over every segment (src/nn/optim.zig:177-234), all in fp32:
  * the step counter advances once per TENSOR (optim.zig:189): segment j uses
  * t = t_first + j.  m, v are laid out like params.  When bf16_copy != NULL
- * the updated parameters are also written there as bfloat16. */
+ * the updated parameters are also written there as bfloat16.
+ * step_counter (optional): a device u64 holding the number of tensor updates
+ * done so far.  When given, t comes from it (segment j uses counter + j + 1,
+ * t_first is ignored) and it is advanced by n_seg after the update, so a step
+ * captured into a CUDA graph keeps counting when it is replayed. */
 EXTERN_C void zg_adam_step(dtype id, StreamWrapper stream, void* params, void* grads, void* m, void* v,
                            const zg_segment* seg, len_t n_seg, len_t t_first,
                            double lr, double beta1, double beta2, double eps,
-                           int clip, double max_norm, double delta, void* norms, void* bf16_copy);
+                           int clip, double max_norm, double delta, void* norms, void* bf16_copy, void* step_counter);
 /* target[i] = tau*src[i] + (1-tau)*target[i] (examples/dqn/src/dqn_agent.zig:111-123) */
 EXTERN_C void zg_soft_update(dtype id, StreamWrapper stream, const void* src, void* target, len_t n, double tau);
 /* fp32 -> bf16 (round to nearest even) and back */

@@ -1,0 +1,121 @@
+"""Mixed-precision MLP step (the wide-MLP configuration in miniature): bf16
+inputs, weights and hidden activations, fp32 accumulation, fp32 logits / loss /
+parameter gradients, fp32 master weights updated by Adam with a bf16 copy.
+
+The reference is fp32/fp64 only, so the oracle here is the CPU restatement run
+on bf16-ROUNDED operands (fp32 BLAS over values that are exactly representable
+in bf16), rounding to bf16 at the same points as the device path.
+
+Tolerances (max |got - want| / max |want| per tensor), stated separately from
+the fp32 path as the specification allows:
+  fp32 tensors computed from bf16 operands (logits, dW, db)   2e-3
+  tensors STORED in bf16 (hidden activations, their grads)    1e-2  (one bf16 ulp = 3.9e-3
+      of the element; a 1e-6 accumulation difference can flip a rounding)
+  loss                                                        1e-3 relative
+"""
+import numpy as np
+import pytest
+
+import oracle
+from zigrad_b200.mlp import MlpTrainer, kaiming_uniform
+
+from .test_gpu_ops import rel_err, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def r16(x):
+    x = np.ascontiguousarray(x, np.float32)
+    return oracle.round_bf16(x.ravel()).reshape(x.shape)
+
+
+def bits(x):
+    return (r16(x).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def mm(A, B, ta, tb):
+    m = A.shape[1] if ta else A.shape[0]
+    k = A.shape[0] if ta else A.shape[1]
+    n = B.shape[0] if tb else B.shape[1]
+    C = np.zeros((m, n), np.float32)
+    return oracle.matmul(np.ascontiguousarray(A), np.ascontiguousarray(B), C, m, n, k, ta, tb, A.shape[1], B.shape[1], n, 1.0, 0.0)
+
+
+def bf16_step_oracle(dims, Ws, bs, X, labels, loss_div):
+    """Forward/backward of the mixed-precision step on the CPU."""
+    L = len(dims) - 1
+    Wb = [r16(w) for w in Ws]
+    act, inp = [], r16(X)
+    for l in range(L):
+        z = mm(inp, Wb[l], False, True) + bs[l][None, :]
+        if l + 1 < L:
+            z = r16(np.maximum(z, 0))
+        act.append(z.astype(np.float32))
+        inp = act[-1]
+    T = np.eye(dims[-1], dtype=np.float32)[labels]
+    loss, sm = oracle.softmax_ce_fwd(act[-1], T, loss_div)
+    dlog = ((sm - T) / np.float32(loss_div)).astype(np.float32)
+    dW, db, dact = [None] * L, [None] * L, [None] * L
+    db[L - 1] = dlog.sum(0)
+    dy = r16(dlog)
+    dact[L - 1] = dlog
+    for l in range(L - 1, -1, -1):
+        a_in = r16(X) if l == 0 else act[l - 1]
+        if l > 0:
+            dx = mm(dy, Wb[l], False, False)
+            dx[act[l - 1] <= 0] = 0
+            db[l - 1] = dx.sum(0)
+            dact[l - 1] = r16(dx)
+        dW[l] = mm(dy, a_in, True, False)
+        if l > 0:
+            dy = dact[l - 1]
+    return loss, act, dact, dW, db
+
+
+@pytest.mark.parametrize("dims,B", [([256, 256, 128, 1000], 512), ([512, 384, 64], 1024)])
+def test_bf16_step_forward_backward(gpu, dims, B):
+    g = rng(B + sum(dims))
+    Ws, bs = kaiming_uniform(dims, 3)
+    bs = [g.standard_normal(b.size).astype(np.float32) * 0.1 for b in bs]
+    X = g.standard_normal((B, dims[0])).astype(np.float32)
+    labels = g.integers(0, dims[-1], B)
+    want_loss, act, dact, dW, db = bf16_step_oracle(dims, Ws, bs, X, labels, B)
+    tr = MlpTrainer(gpu, dims, B, Ws, bs, "none", fused=True, bf16=True)
+    Xd, Td = gpu.from_numpy(bits(X)), gpu.from_numpy(labels.astype(np.uint64))
+    tr.step(Xd, Td)
+    assert abs(tr.read_loss() - want_loss) <= 1e-3 * abs(want_loss)
+    L = len(dims) - 1
+    for l in range(L):
+        tol = 2e-3 if l + 1 == L else 1e-2
+        assert rel_err(tr.act_numpy(l), act[l]) <= tol, ("act", l, rel_err(tr.act_numpy(l), act[l]))
+        assert rel_err(tr.act_numpy(l, grad=True), dact[l]) <= tol, ("dact", l)
+    np.testing.assert_array_equal(np.argmax(tr.act_numpy(L - 1), 1), np.argmax(act[L - 1], 1)) if dims[-1] <= 64 else None
+    gW, gb = tr.get_grads()
+    for l in range(L):
+        assert rel_err(gW[l], dW[l]) <= 2e-3, ("dW", l, rel_err(gW[l], dW[l]))
+        assert rel_err(gb[l], db[l]) <= 2e-3, ("db", l, rel_err(gb[l], db[l]))
+    tr.free()
+    gpu.mem_cache_free(Xd)
+    gpu.mem_cache_free(Td)
+
+
+def test_bf16_adam_keeps_master_and_copy_in_step(gpu):
+    dims, B = [256, 128, 64], 256
+    g = rng(77)
+    Ws, bs = kaiming_uniform(dims, 5)
+    X = g.standard_normal((B, dims[0])).astype(np.float32)
+    labels = g.integers(0, dims[-1], B)
+    tr = MlpTrainer(gpu, dims, B, Ws, bs, "adam", lr=1e-3, fused=True, bf16=True, clip=True)
+    Xd, Td = gpu.from_numpy(bits(X)), gpu.from_numpy(labels.astype(np.uint64))
+    losses = []
+    for _ in range(5):
+        tr.step(Xd, Td)
+        losses.append(tr.read_loss())
+    assert losses[-1] < losses[0]
+    master = gpu.to_numpy(tr.params)
+    copy = gpu.to_numpy(tr.params_bf16)
+    np.testing.assert_array_equal(copy, bits(master))  # the bf16 copy is the RNE rounding of the master, bit for bit
+    assert tr.t == 4 * 5
+    tr.free()
+    gpu.mem_cache_free(Xd)
+    gpu.mem_cache_free(Td)

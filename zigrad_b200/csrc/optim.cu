@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* gr
 template <bool CLIP, bool BF16COPY>
 __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* grads, float* ms, float* vs, const __grid_constant__ SegTable tab,
                                                          float b1, float b2, float eps, const float* __restrict__ norms, float max_norm,
-                                                         float delta, __nv_bfloat16* copy) {
+                                                         float delta, __nv_bfloat16* copy, const unsigned long long* t_dev, float lr) {
   const int seg = blockIdx.y;
   const size_t off = tab.offset[seg];
   float* p = params + off;
@@ -108,7 +108,11 @@ __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* g
   float* m = ms + off;
   float* v = vs + off;
   const size_t n = tab.len[seg];
-  const float lr_t = tab.lr_t[seg];
+  float lr_t = tab.lr_t[seg];
+  if (t_dev) {  // step counter kept on the device (graph replay): t = counter + position of this tensor
+    const float t_f = (float)(*t_dev + (unsigned long long)(tab.first + seg + 1));
+    lr_t = lr * sqrtf(1.f - powf(b2, t_f)) / (1.f - powf(b1, t_f));
+  }
   const float omb1 = 1.f - b1, omb2 = 1.f - b2;
   bool on = false;
   float f = 1.f;
@@ -126,6 +130,8 @@ __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* g
     if (BF16COPY) copy[off + i] = __float2bfloat16_rn(pi);
   }
 }
+
+__global__ void counter_add_kernel(unsigned long long* c, unsigned long long inc) { *c += inc; }
 
 static unsigned chunks_for(const zg_segment* seg, size_t n_seg) {
   size_t mx = 0;
@@ -181,8 +187,9 @@ extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads
 
 extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grads, void* m, void* v, const zg_segment* seg, len_t n_seg,
                              len_t t_first, double lr_, double beta1_, double beta2_, double eps_, int clip, double max_norm, double delta,
-                             void* norms, void* bf16_copy) {
+                             void* norms, void* bf16_copy, void* step_counter) {
   if (id != SINGLE) { set_error(kUnsupported, "zg_adam_step: only SINGLE is implemented"); return; }
+  const unsigned long long* TD = static_cast<const unsigned long long*>(step_counter);
   if (n_seg == 0) return;
   cudaStream_t s = as_stream(w);
   const float lr = (float)lr_, beta1 = (float)beta1_, beta2 = (float)beta2_, eps = (float)eps_;
@@ -201,10 +208,14 @@ extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grad
     const dim3 grid(chunks_for(seg + first, tab.n), tab.n);
     float* P = (float*)params; float* G = (float*)grads; float* M = (float*)m; float* V = (float*)v;
     __nv_bfloat16* cp = (__nv_bfloat16*)bf16_copy;
-    if (clip && cp) adam_kernel<true, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, cp);
-    else if (clip) adam_kernel<true, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, nullptr);
-    else if (cp) adam_kernel<false, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, cp);
-    else adam_kernel<false, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, nullptr);
+    if (clip && cp) adam_kernel<true, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, cp, TD, lr);
+    else if (clip) adam_kernel<true, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, nullptr, TD, lr);
+    else if (cp) adam_kernel<false, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, cp, TD, lr);
+    else adam_kernel<false, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, nullptr, TD, lr);
+    ZG_LAUNCH_CHECK();
+  }
+  if (step_counter) {  // advance the device counter once per tensor, after every update kernel has read it
+    counter_add_kernel<<<1, 1, 0, s>>>(static_cast<unsigned long long*>(step_counter), (unsigned long long)n_seg);
     ZG_LAUNCH_CHECK();
   }
 }

@@ -1,0 +1,127 @@
+"""Two-layer GCN training step with a dense normalised adjacency.
+
+Restates the reference's GCN example above the device boundary
+(``examples/gcn/src/model.zig:17-112`` model and layer, ``:296-353`` MaskLayer,
+``examples/gcn/src/main.zig:40-95`` Adam + loop).  Each GraphConvLayer is
+``h = x . W^T`` (``bmm_acc`` with ``trans_b``), a propagation step, then
+``+ bias``; the reference propagates with an edge scatter
+(``scatter_gcn_deg_scaled``, ``src/device/host_device.zig:1356-1370``), this
+configuration uses the dense matrix that scatter equals, ``p = A_hat . h``.
+
+Device op sequence (fused path): 4 forward GEMMs (bias / bias+ReLU epilogues),
+row gather of the masked logits, softmax-CE (+ last bias gradient), row scatter,
+2 transposed propagation GEMMs, dW2, dA1 (ReLU mask + bias-gradient column sums),
+dW1, Adam.  Rows of X and W1 are padded to a multiple of 4 floats and the class
+dimension to a multiple of 4 so that every operand meets TMA's 16-byte stride
+rule; padding columns are zero and stay zero.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import opspec
+from .abi import SINGLE
+from .device import USIZE, CudaDevice, DeviceSlice
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+class GcnTrainer:
+    def __init__(self, dev: CudaDevice, A_hat: np.ndarray, X: np.ndarray, W1, b1, W2, b2, mask_idx: np.ndarray,
+                 lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = True,
+                 max_norm: float = 10.0, delta: float = 1e-6, opt: str = "adam"):
+        d = self.dev = dev
+        self.N, self.F = X.shape
+        self.H, self.C = W1.shape[0], W2.shape[0]
+        self.Fp, self.Cp = _pad4(self.F), _pad4(self.C)
+        self.M = len(mask_idx)
+        self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
+        self.clip, self.max_norm, self.delta = clip, max_norm, delta
+        self.t = 0
+        N, F, H, C, Fp, Cp, M = self.N, self.F, self.H, self.C, self.Fp, self.Cp, self.M
+        Xp = np.zeros((N, Fp), np.float32)
+        Xp[:, :F] = X
+        self.X = d.from_numpy(Xp)
+        self.A = d.from_numpy(np.ascontiguousarray(A_hat, np.float32))
+        # flat parameters in attach order: W1 [H, Fp], b1 [H], W2 [C, H], b2 [C]
+        W1p = np.zeros((H, Fp), np.float32)
+        W1p[:, :F] = W1
+        flat = np.concatenate([W1p.ravel(), np.asarray(b1, np.float32), np.asarray(W2, np.float32).ravel(), np.asarray(b2, np.float32)])
+        sizes = [H * Fp, H, C * H, C]
+        self.segments, off = [], 0
+        for n in sizes:
+            self.segments.append((off, n))
+            off += n
+        self.params = d.from_numpy(flat)
+        self.grads = d.mem_cache_alloc(SINGLE, off)
+        self.m, self.v = d.mem_cache_alloc(SINGLE, off), d.mem_cache_alloc(SINGLE, off)
+        self.norms = d.mem_cache_alloc(SINGLE, 4)
+        self.t_dev = d.from_numpy(np.zeros(1, np.uint64))  # Adam's counter on the device (graph-replay safe)
+        for s in (self.grads, self.m, self.v):
+            d.mem_fill(s, 0.0)
+        v = lambda buf, i: buf.view(self.segments[i][0], self.segments[i][1])
+        self.W1, self.b1, self.W2, self.b2 = (v(self.params, i) for i in range(4))
+        self.dW1, self.db1, self.dW2, self.db2 = (v(self.grads, i) for i in range(4))
+        alloc = lambda n: d.mem_cache_alloc(SINGLE, n)
+        self.h1, self.a1, self.h2, self.logits = alloc(N * H), alloc(N * H), alloc(N * Cp), alloc(N * Cp)
+        self.dlog, self.dh2, self.da1, self.dh1 = alloc(N * Cp), alloc(N * Cp), alloc(N * H), alloc(N * H)
+        self.mlog, self.dm = alloc(M * Cp), alloc(M * Cp)
+        for s in (self.h2, self.logits, self.dlog, self.dh2, self.mlog, self.dm):
+            d.mem_fill(s, 0.0)
+        # MaskLayer as flat offsets: row r of the mask -> Cp consecutive elements of node mask_idx[r]
+        offs = (np.asarray(mask_idx, np.uint64)[:, None] * np.uint64(Cp) + np.arange(Cp, dtype=np.uint64)[None, :]).ravel()
+        self.offsets = d.from_numpy(np.ascontiguousarray(offs, np.uint64))
+        self.loss = alloc(1)
+        d.sync()
+
+    def _mm(self, A, B, Cbuf, m, n, k, ta, tb, lda, ldb, ldc, beta=0.0, epilogue="none", bias=None, mask=None, colsum=None):
+        self.dev.dispatch(opspec.linear(A, B, Cbuf, m, n, k, ta, tb, lda, ldb, ldc, 1.0, beta, epilogue, bias, mask, colsum=colsum))
+
+    def step(self, T_masked: DeviceSlice):
+        """T_masked: one-hot targets of the masked rows, fp32 [M, C] contiguous."""
+        d, N, F, H, C, Fp, Cp, M = self.dev, self.N, self.F, self.H, self.C, self.Fp, self.Cp, self.M
+        d.mem_fill(self.grads, 0.0)  # zero_grad (model.zig:49-54)
+        # ---- forward
+        self._mm(self.X, self.W1, self.h1, N, H, F, False, True, Fp, Fp, H)                       # h1 = X . W1^T
+        self._mm(self.A, self.h1, self.a1, N, H, N, False, False, N, H, H, 0.0, "bias_relu", self.b1)  # relu(A.h1 + b1)
+        self._mm(self.a1, self.W2, self.h2, N, C, H, False, True, H, H, Cp)                       # h2 = a1 . W2^T
+        self._mm(self.A, self.h2, self.logits, N, C, N, False, False, N, Cp, Cp, 0.0, "bias", self.b2)  # A.h2 + b2
+        # ---- mask rows, loss, gradient of the masked logits (+ db2 = its column sums)
+        d.mem_take(self.logits, self.offsets, self.mlog)
+        d.dispatch(opspec.softmax_ce(self.mlog, T_masked, M, C, self.loss, self.dm, float(M), accumulate=False, ld=Cp,
+                                     bias_grad=self.db2))
+        d.mem_fill(self.dlog, 0.0)
+        d.dispatch(opspec.scatter_add(self.dm, self.offsets, self.dlog))                            # MaskLayer backward
+        # ---- backward
+        self._mm(self.A, self.dlog, self.dh2, N, C, N, True, False, N, Cp, Cp)                    # dh2 = A^T . dlogits
+        self._mm(self.dh2, self.a1, self.dW2, C, H, N, True, False, Cp, H, H, 1.0)                # dW2 += dh2^T . a1
+        self._mm(self.dh2, self.W2, self.da1, N, H, C, False, False, Cp, H, H, 0.0, "relu_mask", None, self.a1,
+                 colsum=self.db1)                                                                   # da1, db1
+        self._mm(self.A, self.da1, self.dh1, N, H, N, True, False, N, H, H)                       # dh1 = A^T . da1
+        self._mm(self.dh1, self.X, self.dW1, H, F, N, True, False, H, Fp, Fp, 1.0)                # dW1 += dh1^T . X
+        # ---- update
+        if self.opt == "adam":
+            d.dispatch(opspec.adam(self.params, self.grads, self.m, self.v, self.segments, self.t + 1, self.lr, self.beta1,
+                                   self.beta2, self.eps, self.clip, self.max_norm, self.delta, self.norms, None, self.t_dev))
+            self.t += 4
+
+    def read_loss(self) -> float:
+        return float(self.dev.to_numpy(self.loss)[0])
+
+    def numpy(self, name: str) -> np.ndarray:
+        """A tensor by name with the padding stripped."""
+        d, N, F, H, C, Fp, Cp = self.dev, self.N, self.F, self.H, self.C, self.Fp, self.Cp
+        shapes = {"W1": (H, Fp, F), "dW1": (H, Fp, F), "W2": (C, H, H), "dW2": (C, H, H), "b1": (1, H, H), "db1": (1, H, H),
+                  "b2": (1, C, C), "db2": (1, C, C), "a1": (N, H, H), "da1": (N, H, H), "logits": (N, Cp, C), "dlog": (N, Cp, C)}
+        r, ld, c = shapes[name]
+        a = d.to_numpy(getattr(self, name)).reshape(r, ld)[:, :c]
+        return a.copy() if r > 1 else a.ravel().copy()
+
+    def free(self):
+        d = self.dev
+        d.sync()
+        for s in (self.X, self.A, self.params, self.grads, self.m, self.v, self.norms, self.h1, self.a1, self.h2, self.logits,
+                  self.dlog, self.dh2, self.da1, self.dh1, self.mlog, self.dm, self.offsets, self.loss, self.t_dev):
+            d.mem_cache_free(s)

@@ -52,7 +52,7 @@ class MlpTrainer:
     def __init__(self, dev: CudaDevice, dims: Sequence[int], batch: int, weights, biases, opt: str = "sgd",
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
                  max_norm: float = 10.0, delta: float = 1e-6, fused: bool = True, loss_div: Optional[int] = None,
-                 index_labels: bool = False, bf16: bool = False):
+                 index_labels: bool = False, bf16: bool = False, pad_logits: bool = True):
         self.dev, self.dims, self.B, self.L = dev, [int(d) for d in dims], int(batch), len(dims) - 1
         self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
         self.clip, self.max_norm, self.delta = clip, max_norm, delta
@@ -80,6 +80,8 @@ class MlpTrainer:
             self.m, self.v = d.mem_cache_alloc(SINGLE, off), d.mem_cache_alloc(SINGLE, off)
             d.mem_fill(self.m, 0.0)
             d.mem_fill(self.v, 0.0)
+            # tensor updates done so far, kept on the device so that a captured step keeps counting on replay
+            self.t_dev = d.from_numpy(np.zeros(1, np.uint64))
         self.W = [self.params.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
         self.b = [self.params.view(self.segments[2 * l + 1][0], self.segments[2 * l + 1][1]) for l in range(self.L)]
         self.dW = [self.grads.view(self.segments[2 * l][0], self.segments[2 * l][1]) for l in range(self.L)]
@@ -92,7 +94,7 @@ class MlpTrainer:
         # = number of classes) satisfy TMA's 16-byte stride rule and run on the
         # tensor cores; the reference op sequence keeps them contiguous.
         C = self.dims[-1]
-        self.ld_out = (C + 3) // 4 * 4 if fused else C
+        self.ld_out = (C + 3) // 4 * 4 if (fused and pad_logits) else C
         self.ld = [self.dims[l + 1] if l + 1 < self.L else self.ld_out for l in range(self.L)]
         self.act = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.ld[l]) for l in range(self.L)]
         self.dact = [d.mem_cache_alloc(act_t if l + 1 < self.L else SINGLE, self.B * self.ld[l]) for l in range(self.L)]
@@ -140,8 +142,15 @@ class MlpTrainer:
         else:
             d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=True))
 
-    def backward(self, X: DeviceSlice):
+    def backward(self, X: DeviceSlice, last_bias_done: bool = True):
+        """Backward from dact[L-1].  `last_bias_done`: the bias gradient of the last
+        layer was already produced by the loss kernel (fused path); pass False when
+        dact[L-1] comes from elsewhere (e.g. the DQN's gather backward)."""
         d, B = self.dev, self.B
+        if self.fused and not last_bias_done:
+            if self.ld_out != self.dims[-1]:
+                raise ValueError("an external output gradient needs unpadded logits (pad_logits=False)")
+            d.dispatch(opspec.unbroadcast(self.dact[-1], [B, self.dims[-1]], self.db[-1], [self.dims[-1]], None, 1.0, 0.0))
         for l in range(self.L - 1, -1, -1):
             K, N = self.dims[l], self.dims[l + 1]
             a_in = X if l == 0 else self.act[l - 1]
@@ -178,8 +187,8 @@ class MlpTrainer:
         elif self.opt == "adam":
             d.dispatch(opspec.adam(self.params, self.grads, self.m, self.v, self.segments, self.t + 1, self.lr, self.beta1,
                                    self.beta2, self.eps, self.clip, self.max_norm, self.delta, self.norms,
-                                   self.params_bf16 if self.bf16 else None))
-            self.t += len(self.segments)
+                                   self.params_bf16 if self.bf16 else None, self.t_dev))
+            self.t += len(self.segments)  # host mirror (eager steps only; read_t() is the truth)
         elif self.opt != "none":
             raise ValueError(self.opt)
 
@@ -196,6 +205,10 @@ class MlpTrainer:
 
     def read_loss(self) -> float:
         return float(self.dev.to_numpy(self.loss)[0])
+
+    def read_t(self) -> int:
+        """Adam's counter as the device holds it (tensor updates done so far)."""
+        return int(self.dev.to_numpy(self.t_dev)[0]) if self.opt == "adam" else 0
 
     # ------------------------------------------------------------- inspection
     def act_numpy(self, l: int, grad: bool = False) -> np.ndarray:
@@ -231,6 +244,7 @@ class MlpTrainer:
         if self.opt == "adam":
             d.mem_cache_free(self.m)
             d.mem_cache_free(self.v)
+            d.mem_cache_free(self.t_dev)
         if self.bf16:
             d.mem_cache_free(self.params_bf16)
             d.mem_cache_free(self.dlogits_bf16)

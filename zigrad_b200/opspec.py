@@ -414,6 +414,7 @@ class adam:
     delta: float = 1e-6
     norms: Optional[Any] = None
     bf16_copy: Optional[Any] = None
+    step_counter: Optional[Any] = None  # device u64: tensor updates so far (graph-replay safe step count)
 
 
 @_op("linear")

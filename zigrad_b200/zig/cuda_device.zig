@@ -235,7 +235,7 @@ pub fn sgd(self: *const Self, T: type, p: opspec.sgd(T)) void {
     cuda.zg_sgd_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.segments.ptr, p.segments.len, p.lr, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr);
 }
 pub fn adam(self: *const Self, T: type, p: opspec.adam(T)) void {
-    cuda.zg_adam_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, p.segments.ptr, p.segments.len, p.t_first, p.lr, p.beta1, p.beta2, p.eps, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr, null);
+    cuda.zg_adam_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, p.segments.ptr, p.segments.len, p.t_first, p.lr, p.beta1, p.beta2, p.eps, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr, null, null);
 }
 pub fn linear(self: *const Self, T: type, p: opspec.linear(T)) void {
     cuda.zg_bmm(dtype(T), dtype(T), self.context.stream, p.A.ptr, p.B.ptr, p.C.ptr, 1, 1, 1, p.m, p.n, p.k, p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, @intFromEnum(p.epilogue), if (p.bias) |b| b.ptr else null, if (p.mask_src) |m| m.ptr else null, if (p.colsum) |c| c.ptr else null);
