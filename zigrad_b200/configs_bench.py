@@ -1,0 +1,157 @@
+"""Timing of the other benchmark configurations on one GPU (bench.py at the
+repository root covers the headline one, the batch-8192 MLP).
+
+    python -m zigrad_b200.configs_bench [--configs c1,c3,c4,c5] [--no-cpu]
+
+  c1  MLP 784-128-64-10, batch 64, fp32 (3xTF32), SGD           -> samples/s, us/step
+  c3  MLP 4096-4096-4096-4096-1000, bf16 + fp32 master, Adam, one GPU's 8192-row
+      shard of the global batch of 65536                         -> samples/s, TFLOP/s
+  c4  2-layer GCN, dense adjacency, 2708 nodes, Adam, full batch -> steps/s
+  c5  DQN 4-128-128-2 (policy + target), batch 256, Huber, Adam  -> us/step
+
+Every step is captured into one CUDA graph and replayed; times come from CUDA
+events on the device stream.  Inputs are seeded synthetic tensors
+(zigrad_b200.synthetic).  With the CPU legs enabled, the same steps are timed
+on the host cores through the oracle package (test infrastructure that
+restates the reference's BLAS backend); one JSON line per configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import numpy as np
+
+
+def _graph_time(dev, ts, fn, reps):
+    import torch
+    fn()  # eager warm-up: workspaces grow here
+    dev.sync()
+    dev.capture.open()
+    fn()
+    dev.capture.save()
+    g = dev.capture.detach()
+    for _ in range(5):
+        g.run()
+    dev.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ts)
+    for _ in range(reps):
+        g.run()
+    e1.record(ts)
+    dev.sync()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    n = g.kernel_count()
+    g.free()
+    return us, n
+
+
+def _cpu_time(fn, reps, warm=2):
+    for _ in range(warm):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    return (time.perf_counter() - t0) / reps * 1e6
+
+
+def run(configs, cpu=True, reps=200):
+    import torch
+    from . import synthetic
+    from .device import CudaDevice
+    from .dqn import DqnTrainer
+    from .gcn import GcnTrainer
+    from .mlp import MlpTrainer, kaiming_uniform
+
+    ts = torch.cuda.Stream()
+    dev = CudaDevice(0, stream=ts.cuda_stream)
+    cores = os.cpu_count() or 1
+    if cpu:
+        import oracle
+        from oracle.nets import DqnOracle, GcnOracle
+        oracle.lib()
+        oracle.set_threads(cores)
+    out = []
+
+    if "c1" in configs:
+        dims, B = [784, 128, 64, 10], 64
+        Ws, bs = kaiming_uniform(dims, 81761)
+        X, T, _ = synthetic.mlp_batch(B, 784, 10, 1)
+        tr = MlpTrainer(dev, dims, B, Ws, bs, "sgd", lr=0.01)
+        Xd, Td = dev.from_numpy(X), dev.from_numpy(T)
+        us, n = _graph_time(dev, ts, lambda: tr.step(Xd, Td), reps * 5 if reps >= 50 else reps)
+        row = {"config": "c1 MLP 784-128-64-10 b64 fp32 SGD", "us_per_step": us, "samples_per_s": B / us * 1e6, "kernels": n}
+        if cpu:
+            m = oracle.MlpOracle(dims, Ws, bs, "sgd", lr=0.01)
+            cus = _cpu_time(lambda: m.step(X, T), 200)
+            row.update(cpu_us_per_step=cus, cpu_samples_per_s=B / cus * 1e6, cpu_cores=cores)
+        out.append(row)
+        tr.free()
+
+    if "c3" in configs:
+        dims, B = [4096, 4096, 4096, 4096, 1000], 8192
+        Ws, bs = kaiming_uniform(dims, 5)
+        g = np.random.Generator(np.random.PCG64(2))
+        X = g.standard_normal((B, dims[0])).astype(np.float32)
+        lab = g.integers(0, 1000, B).astype(np.uint64)
+        tr = MlpTrainer(dev, dims, B, Ws, bs, "adam", lr=1e-3, clip=True, bf16=True, loss_div=65536)
+        xf = dev.from_numpy(X)
+        from .abi import BF16
+        Xd = dev.mem_cache_alloc(BF16, X.size)
+        dev.cast(xf, Xd)
+        Td = dev.from_numpy(lab)
+        us, n = _graph_time(dev, ts, lambda: tr.step(Xd, Td), min(reps, 20))
+        flops = 293011456.0 * B  # fwd + dW + dX, algorithmic
+        row = {"config": "c3 MLP 4096x3-1000 bf16/fp32-acc Adam, 8192-row shard of global 65536", "us_per_step": us,
+               "samples_per_s": B / us * 1e6, "TFLOPs": flops / us * 1e-6, "kernels": n}
+        out.append(row)
+        tr.free()
+
+    if "c4" in configs:
+        N, F, H, C, M = 2708, 1433, 16, 7, 140
+        src, tgt = synthetic.gcn_graph(N, 10556, 81761)
+        A = synthetic.gcn_dense_adjacency(src, tgt, N)
+        X = synthetic.gcn_features(N, F)
+        (W1, W2), (b1, b2) = kaiming_uniform([F, H, C], 11)
+        g = np.random.Generator(np.random.PCG64(12))
+        mask = np.sort(g.permutation(N)[:M]).astype(np.int64)
+        T = np.eye(C, dtype=np.float32)[g.integers(0, C, M)]
+        tr = GcnTrainer(dev, A, X, W1, b1, W2, b2, mask)
+        Td = dev.from_numpy(T)
+        us, n = _graph_time(dev, ts, lambda: tr.step(Td), reps)
+        row = {"config": "c4 GCN dense 2708 nodes, 1433-16-7, Adam", "us_per_step": us, "steps_per_s": 1e6 / us,
+               "GFLOPs": 924.8e6 / us * 1e-3, "kernels": n}
+        if cpu:
+            m = GcnOracle(A, W1, b1, W2, b2)
+            cus = _cpu_time(lambda: m.step(X, T, mask), 20)
+            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        out.append(row)
+        tr.free()
+
+    if "c5" in configs:
+        dims = [4, 128, 128, 2]
+        Ws, bs = kaiming_uniform(dims, 21)
+        batch = synthetic.dqn_batch(256, 3)
+        tr = DqnTrainer(dev, dims, 256, Ws, bs)
+        devb = [dev.from_numpy(x) for x in batch]
+        us, n = _graph_time(dev, ts, lambda: tr.step(*devb), reps * 5 if reps >= 50 else reps)
+        row = {"config": "c5 DQN 4-128-128-2 x2 nets, b256, Huber, Adam", "us_per_step": us, "kernels": n}
+        if cpu:
+            m = DqnOracle(dims, Ws, bs)
+            cus = _cpu_time(lambda: m.step(*batch), 200)
+            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        out.append(row)
+        tr.free()
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--configs", default="c1,c3,c4,c5")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--reps", type=int, default=200, help="graph replays per timing")
+    a = ap.parse_args()
+    for r in run(a.configs.split(","), cpu=not a.no_cpu, reps=a.reps):
+        print(json.dumps(r), flush=True)

@@ -49,6 +49,9 @@ int sm_count();  // SMs of the current device (cached)
 // unsigned counters that a kernel must leave at zero when it finishes.
 void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot = 0);
 
+// y[col] = column sums of x[row, col] (fp32, two-stage, deterministic; uses workspace slot 0)
+void fold_rows_f32(cudaStream_t s, const float* x, float* y, size_t row, size_t col);
+
 // gemm.cu: reads (and clears) the per-device flag that a tensor-core kernel
 // raises when one of its bounded waits runs out; allocates the flag on first use.
 void check_tc_errors();

@@ -294,7 +294,62 @@ __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __re
 }
 __global__ void __launch_bounds__(kThreads) bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t n) {
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
+  if (aligned16(src) && aligned16(dst)) {  // 8 elements per trip: one 128-bit load, two 128-bit stores
+    const size_t nv = n / 8;
+    auto put = [&](const uint4& q, size_t v) {  // a bfloat16 is the upper half of the fp32 with the same value
+      float4 lo, hi;
+      lo.x = __uint_as_float(q.x << 16); lo.y = __uint_as_float(q.x & 0xffff0000u);
+      lo.z = __uint_as_float(q.y << 16); lo.w = __uint_as_float(q.y & 0xffff0000u);
+      hi.x = __uint_as_float(q.z << 16); hi.y = __uint_as_float(q.z & 0xffff0000u);
+      hi.z = __uint_as_float(q.w << 16); hi.w = __uint_as_float(q.w & 0xffff0000u);
+      reinterpret_cast<float4*>(dst)[2 * v] = lo;
+      reinterpret_cast<float4*>(dst)[2 * v + 1] = hi;
+    };
+    size_t v = tid;
+    for (; v + 3 * nth < nv; v += 4 * nth) {
+      const uint4 q0 = reinterpret_cast<const uint4*>(src)[v], q1 = reinterpret_cast<const uint4*>(src)[v + nth];
+      const uint4 q2 = reinterpret_cast<const uint4*>(src)[v + 2 * nth], q3 = reinterpret_cast<const uint4*>(src)[v + 3 * nth];
+      put(q0, v); put(q1, v + nth); put(q2, v + 2 * nth); put(q3, v + 3 * nth);
+    }
+    for (; v < nv; v += nth) put(reinterpret_cast<const uint4*>(src)[v], v);
+    for (size_t i = nv * 8 + tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
+  } else {
+    for (size_t i = tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
+  }
+}
+
+// B[n, m] = A[m, n]^T + alpha * B through a 64x64 shared tile: 128-bit loads
+// along A's rows, 128-bit stores along B's rows (needs m % 4 == n % 4 == 0
+// and 16-byte aligned bases; fp32 only).
+__global__ void __launch_bounds__(256) transpose64_kernel(const float* __restrict__ A, float* __restrict__ B, size_t m, size_t n, float alpha) {
+  __shared__ float tile[64][65];
+  const size_t bx = (size_t)blockIdx.x * 64, by = (size_t)blockIdx.y * 64;
+  const int q = threadIdx.x & 15, r0 = threadIdx.x >> 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = r0 + 16 * k;
+    const size_t i = by + r, j = bx + 4 * q;
+    if (i < m && j < n) {
+      const float4 v = *reinterpret_cast<const float4*>(A + i * n + j);
+      tile[r][4 * q] = v.x; tile[r][4 * q + 1] = v.y; tile[r][4 * q + 2] = v.z; tile[r][4 * q + 3] = v.w;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = r0 + 16 * k;                       // row of B inside the tile = column of A
+    const size_t j = bx + r, i = by + 4 * q;
+    if (j < n && i < m) {
+      float4 v;
+      v.x = tile[4 * q][r]; v.y = tile[4 * q + 1][r]; v.z = tile[4 * q + 2][r]; v.w = tile[4 * q + 3][r];
+      float4* dst = reinterpret_cast<float4*>(B + j * m + i);
+      if (alpha != 0.f) {
+        const float4 o = *dst;
+        v.x += alpha * o.x; v.y += alpha * o.y; v.z += alpha * o.z; v.w += alpha * o.w;
+      }
+      *dst = v;
+    }
+  }
 }
 
 template <typename T>
@@ -409,6 +464,12 @@ extern "C" void zg_cast(dtype src_id, dtype dst_id, StreamWrapper w, const void*
 
 extern "C" void zg_transpose(dtype id, StreamWrapper w, const void* A, void* B, len_t m, len_t n, double alpha) {
   if (m == 0 || n == 0) return;
+  if (id == SINGLE && m % 4 == 0 && n % 4 == 0 && host_aligned16(A) && host_aligned16(B) && (m + 63) / 64 <= 65535) {
+    dim3 grid64((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
+    transpose64_kernel<<<grid64, 256, 0, as_stream(w)>>>((const float*)A, (float*)B, m, n, (float)alpha);
+    ZG_LAUNCH_CHECK();
+    return;
+  }
   dim3 grid((unsigned)((n + 31) / 32), (unsigned)((m + 31) / 32)), block(32, 8);
   ZG_FLOAT_SWITCH("zg_transpose", id, (transpose_kernel<T><<<grid, block, 0, as_stream(w)>>>((const T*)A, (T*)B, m, n, (T)alpha)));
   ZG_LAUNCH_CHECK();

@@ -1,7 +1,9 @@
 // Losses: fused row-softmax + cross-entropy (forward and backward in one
 // pass over the logits), smooth-L1, and the softmax / NLL entry points of
 // include/nn_conflux.h.  Semantics: src/nn/loss.zig:130-215, :259-305.
+#include <algorithm>
 #include <cfloat>
+#include <cmath>
 #include <cstring>
 
 #include "common.cuh"
@@ -39,12 +41,15 @@ struct SmceArgs {
   int C;
   size_t ld;             // row stride of logits / dlogits / probs, in elements
   float divisor;
+  float inv_divisor;     // 1 / divisor
+  int exact_inv;         // divisor is a power of two: multiplying by inv_divisor equals dividing
   float* loss_out;
   float* dlogits;        // [rows, ld] or nullptr
   int accumulate;
   float* probs_out;      // [rows, ld] or nullptr
   float* dbias;          // [C] or nullptr: column sums of (p - t)/divisor
   float* partial;        // workspace: gridDim.x loss partials, then gridDim.x * C bias partials
+  int fold_bias_inline;  // the last CTA folds the bias partials into dbias (else a later launch does)
   unsigned* counter;
 };
 
@@ -92,7 +97,7 @@ __device__ __forceinline__ void smce_finish(const SmceArgs& a, float loss_acc, f
   for (unsigned k = threadIdx.x; k < gridDim.x; k += blockDim.x) s += __ldcg(a.partial + k);
   s = block_sum<float>(s, sm32);
   if (threadIdx.x == 0 && a.loss_out) *a.loss_out = s / a.divisor;
-  if (a.dbias) {
+  if (a.dbias && a.fold_bias_inline) {
     // `parts` threads per column, each over every parts-th CTA partial, then a shuffle tree
     const unsigned parts = (C * 8 <= (int)blockDim.x) ? 8u : ((C * 4 <= (int)blockDim.x) ? 4u : ((C * 2 <= (int)blockDim.x) ? 2u : 1u));
     const unsigned part = threadIdx.x % parts;
@@ -108,9 +113,13 @@ __device__ __forceinline__ void smce_finish(const SmceArgs& a, float loss_acc, f
   }
 }
 
-// One warp per row; ITEMS = ceil(C/32) logits per lane held in registers, so
-// the logits are read from memory exactly once and dlogits written once.
-template <int ITEMS, bool INDEX_LABELS>
+__device__ __forceinline__ float grad_scale(const SmceArgs& a, float d) { return a.exact_inv ? d * a.inv_divisor : d / a.divisor; }
+
+// One warp per row, ROWS rows per trip; ITEMS = ceil(C/32) logits per lane and
+// row held in registers, so the logits are read from memory exactly once and
+// dlogits written once.  All loads of a trip are issued before the first
+// shuffle, and the ROWS independent reductions overlap.
+template <int ITEMS, int ROWS, bool INDEX_LABELS>
 __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a) {
   __shared__ float sm32[32];
   __shared__ float colsum[32 * ITEMS];
@@ -121,38 +130,67 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
   float bias_acc[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) bias_acc[i] = 0.f;
-  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < a.rows; r += warps) {
-    const float* xr = a.logits + r * a.ld;
-    float x[ITEMS];
-    float mx = -INFINITY;
+  for (size_t r0 = (((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * ROWS; r0 < a.rows; r0 += warps * ROWS) {
+    float x[ROWS][ITEMS];
+    float mx[ROWS], se[ROWS];
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      const int j = lane + 32 * i;
-      x[i] = (j < C) ? xr[j] : -INFINITY;
-      mx = fmaxf(mx, x[i]);
+    for (int k = 0; k < ROWS; ++k) {
+      const bool ok = r0 + k < a.rows;
+      const float* xr = a.logits + (r0 + k) * a.ld;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int j = lane + 32 * i;
+        x[k][i] = (ok && j < C) ? xr[j] : -INFINITY;
+      }
     }
-    mx = warp_max(mx);
-    float se = 0.f;
+    size_t label_idx[ROWS];
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) se += (lane + 32 * i < C) ? expf(x[i] - mx) : 0.f;
-    se = warp_sum(se);
-    const float lse = mx + logf(se);
-    size_t label_idx = 0;
-    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
-    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
+    for (int k = 0; k < ROWS; ++k) label_idx[k] = (INDEX_LABELS && r0 + k < a.rows) ? static_cast<const len_t*>(a.labels)[r0 + k] : 0;
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      const int j = lane + 32 * i;
-      if (j < C) {
-        const float p = expf(x[i] - lse);
-        const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
-        const float safe = fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f);
-        if (t != 0.f) loss_acc -= t * logf(safe);
-        const size_t o = r * a.ld + j;
-        if (a.probs_out) a.probs_out[o] = p;
-        const float g = (p - t) / a.divisor;
-        bias_acc[i] += g;
-        if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g : g;
+    for (int k = 0; k < ROWS; ++k) {
+      float m = x[k][0];
+#pragma unroll
+      for (int i = 1; i < ITEMS; ++i) m = fmaxf(m, x[k][i]);
+      mx[k] = m;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      float sacc = 0.f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const bool live = (r0 + k < a.rows) && (lane + 32 * i < C);
+        x[k][i] = live ? expf(x[k][i] - mx[k]) : 0.f;
+        sacc += x[k][i];
+      }
+      se[k] = sacc;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) se[k] += __shfl_xor_sync(0xffffffffu, se[k], o);
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      if (r0 + k >= a.rows) continue;
+      const size_t r = r0 + k;
+      const float inv = 1.f / se[k];
+      const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < C) {
+          const float p = x[k][i] * inv;
+          const float t = INDEX_LABELS ? ((size_t)j == label_idx[k] ? 1.f : 0.f) : tr[j];
+          if (t != 0.f) loss_acc -= t * logf(fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f));
+          const size_t o = r * a.ld + j;
+          if (a.probs_out) a.probs_out[o] = p;
+          const float g = grad_scale(a, p - t);
+          bias_acc[i] += g;
+          if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g : g;
+        }
       }
     }
   }
@@ -161,69 +199,160 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
   smce_finish(a, loss_acc, sm32);
 }
 
-// Narrow rows (C <= 32): one THREAD per row.  All loads of a row are issued at
-// once, the exponentials run without cross-lane traffic, and the bias gradient
-// of the CTA comes from one 32x32 exchange-reduce per warp.
-template <bool INDEX_LABELS>
-__global__ void __launch_bounds__(128) softmax_ce_row_kernel(const SmceArgs a) {
-  __shared__ float sm32[32];
-  __shared__ float wsum[4][32];
-  const int C = a.C;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool ok = r < a.rows;
-  float g[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) g[j] = 0.f;
-  float loss_acc = 0.f;
-  if (ok) {
-    const float* xr = a.logits + r * a.ld;
-    float x[32];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      x[j] = (j < C) ? xr[j] : -INFINITY;
-      mx = fmaxf(mx, x[j]);
+// Narrow rows (C <= 32): one THREAD per row, rows staged through shared memory.
+// A CTA walks blocks of 128 rows: the block is copied in with coalesced
+// (128-bit where the layout allows) loads into a shared array whose odd row
+// stride keeps the thread-per-row reads conflict-free, every thread computes
+// its row in registers, the gradient goes back through the same array and out
+// with coalesced stores.  The bias gradient is kept per thread over all blocks
+// and folded once per CTA by a 32x32 exchange-reduce per warp.
+constexpr int kRowThreads = 128;
+constexpr int kRowMaxW = 36;  // widest staged row: C <= 32 plus padding up to ld = 36
+
+// global [nrows x W] (row stride ld; one contiguous block when ld == W) -> shared (row stride S)
+__device__ __forceinline__ void stage_load(float* sm, int S, const float* __restrict__ g, size_t ld, int W, int nrows) {
+  const int total = nrows * W;
+  if (ld == (size_t)W && aligned16(g)) {
+    const int nv = total >> 2;
+    int r = (threadIdx.x * 4) / W, j = (threadIdx.x * 4) % W;
+    const int dj = (kRowThreads * 4) % W, dr = (kRowThreads * 4) / W;
+    for (int v = threadIdx.x; v < nv; v += kRowThreads) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(g) + v);
+      int rr = r, jj = j;
+      sm[rr * S + jj] = q.x; if (++jj == W) { jj = 0; ++rr; }
+      sm[rr * S + jj] = q.y; if (++jj == W) { jj = 0; ++rr; }
+      sm[rr * S + jj] = q.z; if (++jj == W) { jj = 0; ++rr; }
+      sm[rr * S + jj] = q.w;
+      j += dj; r += dr;
+      if (j >= W) { j -= W; ++r; }
     }
-    float se = 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < C) se += expf(x[j] - mx);
-    const float lse = mx + logf(se);
-    size_t label_idx = 0;
-    if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
-    const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < C) {
-        const float p = expf(x[j] - lse);
-        const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
-        const float safe = fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f);
-        if (t != 0.f) loss_acc -= t * logf(safe);
-        const size_t o = r * a.ld + j;
-        if (a.probs_out) a.probs_out[o] = p;
-        g[j] = (p - t) / a.divisor;
-        if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g[j] : g[j];
-      }
+    for (int e = (nv << 2) + threadIdx.x; e < total; e += kRowThreads) sm[(e / W) * S + e % W] = g[e];
+  } else {
+    int r = threadIdx.x / W, j = threadIdx.x % W;
+    const int dj = kRowThreads % W, dr = kRowThreads / W;
+    for (int e = threadIdx.x; e < total; e += kRowThreads) {
+      sm[r * S + j] = g[(size_t)r * ld + j];
+      j += dj; r += dr;
+      if (j >= W) { j -= W; ++r; }
     }
   }
-  if (a.dbias) {
-    // five exchange rounds: lane j ends with the warp's sum of column j
+}
+
+// shared (row stride S) -> global [nrows x C] (row stride ld); adds into global when `accumulate`
+__device__ __forceinline__ void stage_store(const float* sm, int S, float* g, size_t ld, int C, int nrows, bool accumulate) {
+  const int total = nrows * C;
+  if (ld == (size_t)C && aligned16(g)) {
+    const int nv = total >> 2;
+    int r = (threadIdx.x * 4) / C, j = (threadIdx.x * 4) % C;
+    const int dj = (kRowThreads * 4) % C, dr = (kRowThreads * 4) / C;
+    for (int v = threadIdx.x; v < nv; v += kRowThreads) {
+      float4 q;
+      int rr = r, jj = j;
+      q.x = sm[rr * S + jj]; if (++jj == C) { jj = 0; ++rr; }
+      q.y = sm[rr * S + jj]; if (++jj == C) { jj = 0; ++rr; }
+      q.z = sm[rr * S + jj]; if (++jj == C) { jj = 0; ++rr; }
+      q.w = sm[rr * S + jj];
+      float4* dst = reinterpret_cast<float4*>(g) + v;
+      if (accumulate) { const float4 o = *dst; q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w; }
+      *dst = q;
+      j += dj; r += dr;
+      if (j >= C) { j -= C; ++r; }
+    }
+    for (int e = (nv << 2) + threadIdx.x; e < total; e += kRowThreads) {
+      const float v = sm[(e / C) * S + e % C];
+      g[e] = accumulate ? g[e] + v : v;
+    }
+  } else {
+    int r = threadIdx.x / C, j = threadIdx.x % C;
+    const int dj = kRowThreads % C, dr = kRowThreads / C;
+    for (int e = threadIdx.x; e < total; e += kRowThreads) {
+      const size_t o = (size_t)r * ld + j;
+      const float v = sm[r * S + j];
+      g[o] = accumulate ? g[o] + v : v;
+      j += dj; r += dr;
+      if (j >= C) { j -= C; ++r; }
+    }
+  }
+}
+
+template <int CP, bool INDEX_LABELS>  // CP: C rounded up to 8, 16 or 32
+__global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceArgs a) {
+  __shared__ float sm32[32];
+  __shared__ float wsum[kRowThreads / 32][32];
+  __shared__ __align__(16) float stage[kRowThreads * (kRowMaxW + 1)];
+  __shared__ __align__(16) float tstage[INDEX_LABELS ? 4 : kRowThreads * 33];
+  const int C = a.C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool block_rows = a.ld <= (size_t)kRowMaxW;  // rows and their padding form one contiguous block
+  const int W = block_rows ? (int)a.ld : C;
+  const int S = W | 1, ST = C | 1;
+  float gacc[CP];
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
+  for (int j = 0; j < CP; ++j) gacc[j] = 0.f;
+  float loss_acc = 0.f;
+  for (size_t base = (size_t)blockIdx.x * kRowThreads; base < a.rows; base += (size_t)gridDim.x * kRowThreads) {
+    const int nrows = (int)((a.rows - base) < (size_t)kRowThreads ? (a.rows - base) : (size_t)kRowThreads);
+    stage_load(stage, S, a.logits + base * a.ld, a.ld, W, nrows);
+    if (!INDEX_LABELS) stage_load(tstage, ST, static_cast<const float*>(a.labels) + base * (size_t)C, (size_t)C, C, nrows);
+    __syncthreads();
+    if ((int)threadIdx.x < nrows) {
+      const size_t r = base + threadIdx.x;
+      float* xs = stage + threadIdx.x * S;
+      const float* tr = tstage + threadIdx.x * ST;
+      float x[CP];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        x[j] = (j < C) ? xs[j] : -INFINITY;
+        mx = fmaxf(mx, x[j]);
+      }
+      float se = 0.f;
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        x[j] = (j < C) ? expf(x[j] - mx) : 0.f;
+        se += x[j];
+      }
+      const float inv = 1.f / se;
+      size_t label_idx = 0;
+      if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        if (j < C) {
+          const float p = x[j] * inv;
+          const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
+          if (t != 0.f) loss_acc -= t * logf(fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f));
+          if (a.probs_out) a.probs_out[r * a.ld + j] = p;
+          const float g = grad_scale(a, p - t);
+          gacc[j] += g;
+          xs[j] = g;
+        }
+      }
+    }
+    __syncthreads();
+    if (a.dlogits) stage_store(stage, S, a.dlogits + base * a.ld, a.ld, C, nrows, a.accumulate != 0);
+    __syncthreads();
+  }
+  if (a.dbias) {
+    // log2(CP) exchange rounds: lane l ends with the sum of column (l mod CP)
+    // over the CP lanes of its group in gacc[0]
+#pragma unroll
+    for (int off = CP / 2; off >= 1; off >>= 1) {
       const bool upper = (lane & off) != 0;
 #pragma unroll
       for (int j = 0; j < off; ++j) {
-        const float send = upper ? g[j] : g[j + off];
-        const float keep = upper ? g[j + off] : g[j];
-        g[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        const float send = upper ? gacc[j] : gacc[j + off];
+        const float keep = upper ? gacc[j + off] : gacc[j];
+        gacc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
       }
     }
-    wsum[warp][lane] = g[0];
+    // groups (lanes that agree modulo CP) hold partial sums of the same column
+#pragma unroll
+    for (int off = 16; off >= CP; off >>= 1) gacc[0] += __shfl_xor_sync(0xffffffffu, gacc[0], off);
+    wsum[warp][lane] = gacc[0];
     __syncthreads();
     if ((int)threadIdx.x < C) {
       float s = 0.f;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += wsum[w][threadIdx.x];
+      for (int w = 0; w < kRowThreads / 32; ++w) s += wsum[w][threadIdx.x];
       a.partial[gridDim.x + (size_t)blockIdx.x * C + threadIdx.x] = s;
     }
   }
@@ -338,39 +467,76 @@ __global__ void __launch_bounds__(kLThreads) nll_bwd_kernel(const float* __restr
   }
 }
 
-template <bool IDX>
-static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
-  if (a.C <= 32 && a.rows <= (size_t)128 * 4096) {  // narrow rows: thread per row, grid covers the rows
-    const unsigned gr = (unsigned)((a.rows + 127) / 128);
-    unsigned* counters = nullptr;
-    float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)gr + (a.dbias ? (size_t)gr * a.C : 0)), &counters));
-    if (!partial) return;
-    a.partial = partial;
-    a.counter = counters;
-    softmax_ce_row_kernel<IDX><<<gr, 128, 0, s>>>(a);
-    ZG_LAUNCH_CHECK();
-    return;
+// CTAs of `kernel` that fit on the device at once (the kernels below walk
+// their rows with a grid-stride loop, so a grid of exactly this size runs as
+// one wave without a tail)
+template <typename K>
+static unsigned resident_ctas(K kernel, int threads) {
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, 0) != cudaSuccess || occ < 1) {
+    (void)cudaGetLastError();
+    occ = 1;
   }
-  // with a bias gradient the last CTA folds gridDim.x partial rows per column: keep the grid small
-  unsigned g = grid_for(a.rows, kLThreads / 32, 8);
-  const unsigned cap = a.dbias ? 128u : 2048u;
-  if (g > cap) g = cap;
+  return (unsigned)occ * (unsigned)sm_count();
+}
+
+template <int CP, bool IDX>
+static void launch_smce_rows(cudaStream_t s, SmceArgs a) {
+  static const unsigned resident = resident_ctas(softmax_ce_row_kernel<CP, IDX>, kRowThreads);
+  const unsigned gr = (unsigned)std::min<size_t>((a.rows + kRowThreads - 1) / kRowThreads, resident);
   unsigned* counters = nullptr;
-  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)g + (a.dbias ? (size_t)g * a.C : 0)), &counters));
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)gr + (a.dbias ? (size_t)gr * a.C : 0)), &counters));
   if (!partial) return;
   a.partial = partial;
   a.counter = counters;
+  a.fold_bias_inline = 1;
+  softmax_ce_row_kernel<CP, IDX><<<gr, kRowThreads, 0, s>>>(a);
+  ZG_LAUNCH_CHECK();
+}
+
+template <int ITEMS, int ROWS, bool IDX>
+static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
+  static const unsigned resident = resident_ctas(softmax_ce_kernel<ITEMS, ROWS, IDX>, kLThreads);
   const int C = a.C;
-#define ZG_SMCE(ITEMS) softmax_ce_kernel<ITEMS, IDX><<<g, kLThreads, 0, s>>>(a)
-  if (C <= 32) ZG_SMCE(1);
-  else if (C <= 64) ZG_SMCE(2);
-  else if (C <= 128) ZG_SMCE(4);
-  else if (C <= 256) ZG_SMCE(8);
-  else if (C <= 512) ZG_SMCE(16);
-  else if (C <= 1024) ZG_SMCE(32);
-  else if (a.dbias) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: the fused bias gradient supports C <= 1024"); return; }
-  else softmax_ce_wide_kernel<IDX><<<g, kLThreads, 0, s>>>(a);
-#undef ZG_SMCE
+  const size_t rows_per_cta = (size_t)(kLThreads / 32) * ROWS;
+  unsigned g = (unsigned)std::min<size_t>((a.rows + rows_per_cta - 1) / rows_per_cta, resident);
+  // The bias gradient leaves the kernel as one partial row per CTA.  Few of
+  // them are folded by the last CTA to finish; many (wide rows on a large grid)
+  // by a second, multi-CTA column-sum launch over the partials.
+  const bool separate_fold = a.dbias && (size_t)g * C > 32768;
+  unsigned* counters = nullptr;
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)g + (a.dbias ? (size_t)g * C : 0)), &counters, separate_fold ? 1 : 0));
+  if (!partial) return;
+  a.partial = partial;
+  a.counter = counters;
+  a.fold_bias_inline = separate_fold ? 0 : 1;
+  softmax_ce_kernel<ITEMS, ROWS, IDX><<<g, kLThreads, 0, s>>>(a);
+  if (!ZG_LAUNCH_CHECK()) return;
+  if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
+}
+
+template <bool IDX>
+static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
+  const int C = a.C;
+  int e = 0;
+  a.inv_divisor = 1.f / a.divisor;
+  a.exact_inv = (std::frexp(a.divisor, &e) == 0.5f && std::isnormal(a.inv_divisor)) ? 1 : 0;
+  if (C <= 8) return launch_smce_rows<8, IDX>(s, a);
+  if (C <= 16) return launch_smce_rows<16, IDX>(s, a);
+  if (C <= 32) return launch_smce_rows<32, IDX>(s, a);
+  if (C <= 64) return launch_smce_warps<2, 8, IDX>(s, a);
+  if (C <= 128) return launch_smce_warps<4, 4, IDX>(s, a);
+  if (C <= 256) return launch_smce_warps<8, 2, IDX>(s, a);
+  if (C <= 512) return launch_smce_warps<16, 2, IDX>(s, a);
+  if (C <= 1024) return launch_smce_warps<32, 1, IDX>(s, a);
+  if (a.dbias) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: the fused bias gradient supports C <= 1024"); return; }
+  unsigned g = grid_for(a.rows, kLThreads / 32, 8);
+  unsigned* counters = nullptr;
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * (size_t)g, &counters));
+  if (!partial) return;
+  a.partial = partial;
+  a.counter = counters;
+  softmax_ce_wide_kernel<IDX><<<g, kLThreads, 0, s>>>(a);
   ZG_LAUNCH_CHECK();
 }
 
@@ -389,7 +555,7 @@ extern "C" void zg_softmax_ce_fwd_bwd(dtype id, StreamWrapper w, const void* log
   SmceArgs a;
   a.logits = (const float*)logits; a.labels = labels; a.rows = rows; a.C = (int)C; a.ld = ld; a.divisor = (float)loss_div;
   a.loss_out = (float*)loss_out; a.dlogits = (float*)dlogits; a.accumulate = accumulate; a.probs_out = (float*)probs_out;
-  a.dbias = (float*)dbias; a.partial = nullptr; a.counter = nullptr;
+  a.dbias = (float*)dbias; a.partial = nullptr; a.counter = nullptr; a.fold_bias_inline = 1;
   cudaStream_t s = as_stream(w);
   if (label_kind == ZG_LABEL_INDEX) launch_softmax_ce<true>(s, a);
   else if (label_kind == ZG_LABEL_ONEHOT) launch_softmax_ce<false>(s, a);

@@ -19,6 +19,12 @@ struct SegTable {
   int first;  // index of the first segment of this launch in the caller's list
 };
 
+// fp32 elements from p up to the next 16-byte boundary
+__device__ __forceinline__ size_t misalign_elems(const void* p) { return ((16u - (unsigned)(reinterpret_cast<uintptr_t>(p) & 15u)) & 15u) >> 2; }
+__device__ __forceinline__ bool same_phase(const void* a, const void* b) {
+  return ((reinterpret_cast<uintptr_t>(a) ^ reinterpret_cast<uintptr_t>(b)) & 15u) == 0;
+}
+
 // norms[first + j] = ||g_j||_2 for every segment of the table.  grid = (chunks, n);
 // chunk partials are folded by the last CTA of each segment in index order.
 __global__ void __launch_bounds__(kOThreads) seg_nrm2_kernel(const float* __restrict__ g, const __grid_constant__ SegTable tab,
@@ -27,8 +33,28 @@ __global__ void __launch_bounds__(kOThreads) seg_nrm2_kernel(const float* __rest
   const int seg = blockIdx.y;
   const float* p = g + tab.offset[seg];
   const size_t n = tab.len[seg];
-  float acc = 0.f;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) acc += p[i] * p[i];
+  const size_t nth = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // scalar head up to the first 16-byte boundary, 128-bit body (4 loads in flight per thread), scalar tail
+  size_t head = misalign_elems(p);
+  if (head > n) head = n;
+  float acc = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (size_t i = tid; i < head; i += nth) acc += p[i] * p[i];
+  const float4* pv = reinterpret_cast<const float4*>(p + head);
+  const size_t nv = (n - head) / 4;
+  size_t v = tid;
+  for (; v + 3 * nth < nv; v += 4 * nth) {
+    const float4 q0 = pv[v], q1 = pv[v + nth], q2 = pv[v + 2 * nth], q3 = pv[v + 3 * nth];
+    acc += q0.x * q0.x + q0.y * q0.y + q0.z * q0.z + q0.w * q0.w;
+    a1 += q1.x * q1.x + q1.y * q1.y + q1.z * q1.z + q1.w * q1.w;
+    a2 += q2.x * q2.x + q2.y * q2.y + q2.z * q2.z + q2.w * q2.w;
+    a3 += q3.x * q3.x + q3.y * q3.y + q3.z * q3.z + q3.w * q3.w;
+  }
+  for (; v < nv; v += nth) {
+    const float4 q0 = pv[v];
+    acc += q0.x * q0.x + q0.y * q0.y + q0.z * q0.z + q0.w * q0.w;
+  }
+  for (size_t i = head + nv * 4 + tid; i < n; i += nth) acc += p[i] * p[i];
+  acc = (acc + a1) + (a2 + a3);
   const double bs = block_sum<double>((double)acc, sm);
   double* mine = partial + (size_t)seg * gridDim.x;
   if (threadIdx.x == 0) mine[blockIdx.x] = bs;
@@ -68,20 +94,28 @@ __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* gr
   if (CLIP) f = clip_factor(norms, tab.first + seg, max_norm, delta, &on);
   const size_t nth = (size_t)gridDim.x * blockDim.x;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool vec = aligned16(p) && aligned16(g);
-  if (vec) {
-    const size_t nv = n / 4;
+  if (same_phase(p, g) && (reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+    size_t head = misalign_elems(p);
+    if (head > n) head = n;
+    const size_t nv = (n - head) / 4;
+    for (size_t i = tid; i < head; i += nth) {
+      float gi = g[i];
+      if (CLIP && on) { gi *= f; g[i] = gi; }
+      p[i] = fmaf(nlr, gi, p[i]);
+    }
+    float4* gq = reinterpret_cast<float4*>(g + head);
+    float4* pq = reinterpret_cast<float4*>(p + head);
     for (size_t v = tid; v < nv; v += nth) {
-      float4 gv = reinterpret_cast<float4*>(g)[v];
-      float4 pv = reinterpret_cast<float4*>(p)[v];
+      float4 gv = gq[v];
+      float4 pv = pq[v];
       if (CLIP && on) {
         gv.x *= f; gv.y *= f; gv.z *= f; gv.w *= f;
-        reinterpret_cast<float4*>(g)[v] = gv;
+        gq[v] = gv;
       }
       pv.x = fmaf(nlr, gv.x, pv.x); pv.y = fmaf(nlr, gv.y, pv.y); pv.z = fmaf(nlr, gv.z, pv.z); pv.w = fmaf(nlr, gv.w, pv.w);
-      reinterpret_cast<float4*>(p)[v] = pv;
+      pq[v] = pv;
     }
-    for (size_t i = nv * 4 + tid; i < n; i += nth) {
+    for (size_t i = head + nv * 4 + tid; i < n; i += nth) {
       float gi = g[i];
       if (CLIP && on) { gi *= f; g[i] = gi; }
       p[i] = fmaf(nlr, gi, p[i]);
@@ -117,18 +151,52 @@ __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* g
   bool on = false;
   float f = 1.f;
   if (CLIP) f = clip_factor(norms, tab.first + seg, max_norm, delta, &on);
-  const size_t nth = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) {
-    float gi = g[i];
-    if (CLIP && on) { gi *= f; g[i] = gi; }
-    const float mi = b1 * m[i] + omb1 * gi;
-    const float vi = b2 * v[i] + omb2 * gi * gi;
-    m[i] = mi;
-    v[i] = vi;
-    const float pi = p[i] - lr_t * mi / (sqrtf(vi) + eps);
-    p[i] = pi;
+  const size_t nth = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // one element, operation for operation as the host loop (no contraction: the file is built with --fmad=false)
+  auto one = [&](float& gi, float& mi, float& vi, float& pi) {
+    if (CLIP && on) gi *= f;
+    mi = b1 * mi + omb1 * gi;
+    vi = b2 * vi + omb2 * gi * gi;
+    pi = pi - lr_t * mi / (sqrtf(vi) + eps);
+  };
+  auto scalar = [&](size_t i) {
+    float gi = g[i], mi = m[i], vi = v[i], pi = p[i];
+    one(gi, mi, vi, pi);
+    if (CLIP && on) g[i] = gi;
+    m[i] = mi; v[i] = vi; p[i] = pi;
     if (BF16COPY) copy[off + i] = __float2bfloat16_rn(pi);
+  };
+  size_t head = misalign_elems(p);
+  if (head > n) head = n;
+  bool vec = same_phase(p, g) && same_phase(p, m) && same_phase(p, v) && (reinterpret_cast<uintptr_t>(p) & 3u) == 0;
+  if (BF16COPY) vec = vec && (reinterpret_cast<uintptr_t>(copy + off + head) & 7u) == 0;
+  if (!vec) {
+    for (size_t i = tid; i < n; i += nth) scalar(i);
+    return;
   }
+  const size_t nv = (n - head) / 4;
+  for (size_t i = tid; i < head; i += nth) scalar(i);
+  float4* gq = reinterpret_cast<float4*>(g + head);
+  float4* mq = reinterpret_cast<float4*>(m + head);
+  float4* vq = reinterpret_cast<float4*>(v + head);
+  float4* pq = reinterpret_cast<float4*>(p + head);
+  for (size_t k = tid; k < nv; k += nth) {
+    float4 gv = gq[k], mv = mq[k], vv = vq[k], pv = pq[k];
+    one(gv.x, mv.x, vv.x, pv.x);
+    one(gv.y, mv.y, vv.y, pv.y);
+    one(gv.z, mv.z, vv.z, pv.z);
+    one(gv.w, mv.w, vv.w, pv.w);
+    if (CLIP && on) gq[k] = gv;
+    mq[k] = mv; vq[k] = vv; pq[k] = pv;
+    if (BF16COPY) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(pv.x, pv.y), hi = __floats2bfloat162_rn(pv.z, pv.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t*>(&lo);
+      o.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(copy + off + head + 4 * k) = o;
+    }
+  }
+  for (size_t i = head + nv * 4 + tid; i < n; i += nth) scalar(i);
 }
 
 __global__ void counter_add_kernel(unsigned long long* c, unsigned long long inc) { *c += inc; }
@@ -136,8 +204,9 @@ __global__ void counter_add_kernel(unsigned long long* c, unsigned long long inc
 static unsigned chunks_for(const zg_segment* seg, size_t n_seg) {
   size_t mx = 0;
   for (size_t j = 0; j < n_seg; ++j) mx = seg[j].len > mx ? seg[j].len : mx;
-  size_t c = (mx + (size_t)kOThreads * 8 - 1) / ((size_t)kOThreads * 8);
-  const size_t cap = (size_t)sm_count() * 4;
+  size_t c = (mx + (size_t)kOThreads * 4 - 1) / ((size_t)kOThreads * 4);
+  size_t cap = (size_t)sm_count() * 8 / (n_seg ? n_seg : 1);
+  if (cap < 8) cap = 8;
   if (c > cap) c = cap;
   return (unsigned)(c < 1 ? 1 : c);
 }

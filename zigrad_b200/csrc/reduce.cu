@@ -148,6 +148,8 @@ void fold_rows_launch(cudaStream_t s, const T* x, T* y, size_t batch, size_t row
   ZG_LAUNCH_CHECK();
 }
 
+void fold_rows_f32(cudaStream_t s, const float* x, float* y, size_t row, size_t col) { fold_rows_launch<float>(s, x, y, 1, row, col, 1.f, 0.f); }
+
 // ------------------------------------------------------------ fold_cols
 // [row, col] -> [row]: a warp per row (wide rows) or a thread per row.
 template <typename T>
@@ -197,6 +199,53 @@ __global__ void __launch_bounds__(kRThreads) max_along_kernel(const T* __restric
   }
 }
 
+// inner == 1 (the reduced dimension is the contiguous one), d > 8: a warp per
+// output, lanes stride the row with 128-bit loads where the row allows.
+template <typename T>
+__global__ void __launch_bounds__(kRThreads) max_along_rows_kernel(const T* __restrict__ x, T* __restrict__ y, size_t rows, size_t d) {
+  constexpr int V = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const bool vec = aligned16(x) && d % V == 0;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    const T* xr = x + r * d;
+    T mx = -INFINITY;
+    if (vec) {
+      const uint4* xv = reinterpret_cast<const uint4*>(xr);
+      const size_t nv = d / V;
+      size_t v = lane;
+      for (; v + 96 < nv; v += 128) {
+        const uint4 q[4] = {xv[v], xv[v + 32], xv[v + 64], xv[v + 96]};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const T* e = reinterpret_cast<const T*>(&q[u]);
+#pragma unroll
+          for (int k = 0; k < V; ++k)
+            if (e[k] > mx) mx = e[k];
+        }
+      }
+      for (; v < nv; v += 32) {
+        const uint4 q = xv[v];
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int k = 0; k < V; ++k)
+          if (e[k] > mx) mx = e[k];
+      }
+    } else {
+      for (size_t j = lane; j < d; j += 32) {
+        const T v = xr[j];
+        if (v > mx) mx = v;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const T other = __shfl_xor_sync(0xffffffffu, mx, o);
+      if (other > mx) mx = other;
+    }
+    if (lane == 0) y[r] = mx;
+  }
+}
+
 // ------------------------------------------------- full reductions (scalars)
 enum ScalarOp { kSum = 0, kAsum = 1, kNrm2 = 2, kDot = 3 };
 
@@ -207,14 +256,43 @@ __global__ void __launch_bounds__(kRThreads) scalar_reduce_kernel(const T* __res
                                                                   double* __restrict__ partial, unsigned* counters, T* out,
                                                                   T alpha, T beta) {
   __shared__ double sm[32];
-  const size_t nth = (size_t)gridDim.x * blockDim.x;
-  T acc = T(0);
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) {
-    const T v = a[i];
-    if (OP == kSum) acc += v;
-    else if (OP == kAsum) acc += (v < T(0) ? -v : v);
-    else if (OP == kNrm2) acc += v * v;
-    else acc += v * b[i];
+  const size_t nth = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  auto term = [](T v, T w) -> T {
+    if (OP == kSum) return v;
+    if (OP == kAsum) return v < T(0) ? -v : v;
+    if (OP == kNrm2) return v * v;
+    return v * w;
+  };
+  constexpr int V = 16 / sizeof(T);
+  T acc = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+  if (aligned16(a) && (OP != kDot || aligned16(b))) {
+    // 128-bit loads, four per operand in flight per thread
+    const uint4* av = reinterpret_cast<const uint4*>(a);
+    const uint4* bv = reinterpret_cast<const uint4*>(OP == kDot ? b : a);
+    const size_t nv = n / V;
+    auto fold = [&](const uint4& qa, const uint4& qb, T& dst) {
+      const T* ea = reinterpret_cast<const T*>(&qa);
+      const T* eb = reinterpret_cast<const T*>(&qb);
+#pragma unroll
+      for (int e = 0; e < V; ++e) dst += term(ea[e], eb[e]);
+    };
+    size_t v = tid;
+    for (; v + 3 * nth < nv; v += 4 * nth) {
+      const uint4 q0 = av[v], q1 = av[v + nth], q2 = av[v + 2 * nth], q3 = av[v + 3 * nth];
+      uint4 r0 = q0, r1 = q1, r2 = q2, r3 = q3;
+      if (OP == kDot) { r0 = bv[v]; r1 = bv[v + nth]; r2 = bv[v + 2 * nth]; r3 = bv[v + 3 * nth]; }
+      fold(q0, r0, acc); fold(q1, r1, a1); fold(q2, r2, a2); fold(q3, r3, a3);
+    }
+    for (; v < nv; v += nth) {
+      const uint4 q0 = av[v];
+      uint4 r0 = q0;
+      if (OP == kDot) r0 = bv[v];
+      fold(q0, r0, acc);
+    }
+    for (size_t i = nv * V + tid; i < n; i += nth) acc += term(a[i], OP == kDot ? b[i] : a[i]);
+    acc = (acc + a1) + (a2 + a3);
+  } else {
+    for (size_t i = tid; i < n; i += nth) acc += term(a[i], OP == kDot ? b[i] : a[i]);
   }
   const double bs = block_sum<double>((double)acc, sm);
   if (threadIdx.x == 0) partial[blockIdx.x] = bs;
@@ -239,8 +317,7 @@ __global__ void __launch_bounds__(kRThreads) scalar_reduce_kernel(const T* __res
 
 template <typename T, int OP>
 void scalar_reduce_launch(cudaStream_t s, const T* a, const T* b, size_t n, T* out, T alpha = T(1), T beta = T(0)) {
-  unsigned g = grid_for(n ? n : 1, (size_t)kRThreads * 16, 2);
-  if (g > 1024) g = 1024;
+  unsigned g = grid_for(n ? n : 1, (size_t)kRThreads * 16, 8);
   unsigned* counters = nullptr;
   double* partial = static_cast<double*>(workspace(s, sizeof(double) * g, &counters));
   if (!partial) return;
@@ -255,12 +332,38 @@ __global__ void __launch_bounds__(kRThreads) amax_kernel(const T* __restrict__ x
                                                          unsigned long long* __restrict__ pidx, unsigned* counters, T* out) {
   __shared__ T sv[kRThreads];
   __shared__ unsigned long long si[kRThreads];
-  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  const size_t nth = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   T best = T(-1);
   unsigned long long bi = ~0ull;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) {
-    const T m = x[i] < T(0) ? -x[i] : x[i];
+  // a thread visits its elements in increasing index order, so '>' keeps the first index on ties
+  auto see = [&](T v, size_t i) {
+    const T m = v < T(0) ? -v : v;
     if (m > best) { best = m; bi = i; }
+  };
+  constexpr int V = 16 / sizeof(T);
+  if (aligned16(x)) {
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    const size_t nv = n / V;
+    size_t v = tid;
+    for (; v + 3 * nth < nv; v += 4 * nth) {
+      const uint4 q[4] = {xv[v], xv[v + nth], xv[v + 2 * nth], xv[v + 3 * nth]};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&q[u]);
+#pragma unroll
+        for (int k = 0; k < V; ++k) see(e[k], (v + u * nth) * V + k);
+      }
+    }
+    for (; v < nv; v += nth) {
+      const uint4 q = xv[v];
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int k = 0; k < V; ++k) see(e[k], v * V + k);
+    }
+    // the tail holds the largest indices of all: visiting it last keeps the order
+    for (size_t i = nv * V + tid; i < n; i += nth) see(x[i], i);
+  } else {
+    for (size_t i = tid; i < n; i += nth) see(x[i], i);
   }
   sv[threadIdx.x] = best; si[threadIdx.x] = bi;
   __syncthreads();
@@ -283,16 +386,26 @@ __global__ void __launch_bounds__(kRThreads) amax_kernel(const T* __restrict__ x
   __syncthreads();
   if (!last) return;
   __threadfence();
-  if (threadIdx.x == 0) {
-    T b = T(-1);
-    unsigned long long i0 = ~0ull;
-    for (unsigned k = 0; k < gridDim.x; ++k) {
-      const T v = __ldcg(pval + k);
-      const unsigned long long ii = __ldcg(pidx + k);
-      if (v > b || (v == b && ii < i0)) { b = v; i0 = ii; }
-    }
-    *out = (i0 == ~0ull) ? x[0] : x[i0];
+  // fold the CTA partials with the whole CTA: strided pick, then the same tree
+  T b = T(-1);
+  unsigned long long i0 = ~0ull;
+  for (unsigned k = threadIdx.x; k < gridDim.x; k += blockDim.x) {
+    const T v = __ldcg(pval + k);
+    const unsigned long long ii = __ldcg(pidx + k);
+    if (v > b || (v == b && ii < i0)) { b = v; i0 = ii; }
   }
+  __syncthreads();
+  sv[threadIdx.x] = b; si[threadIdx.x] = i0;
+  __syncthreads();
+  for (int o = kRThreads / 2; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) {
+      const T ov = sv[threadIdx.x + o];
+      const unsigned long long oi = si[threadIdx.x + o];
+      if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) { sv[threadIdx.x] = ov; si[threadIdx.x] = oi; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = (si[0] == ~0ull) ? x[0] : x[si[0]];
 }
 
 template <typename T>
@@ -350,7 +463,9 @@ void max_along_impl(cudaStream_t s, const T* x, const len_t* xs, size_t nd, size
   const size_t total = prod(xs, 0, nd);
   if (total == 0) return;
   const size_t ylen = total / xs[dim];
-  max_along_kernel<T><<<grid_for(ylen, kRThreads), kRThreads, 0, s>>>(x, y, ylen, xs[dim], prod(xs, dim + 1, nd));
+  const size_t inner = prod(xs, dim + 1, nd);
+  if (inner == 1 && xs[dim] > 8) max_along_rows_kernel<T><<<grid_for(ylen, kRThreads / 32), kRThreads, 0, s>>>(x, y, ylen, xs[dim]);
+  else max_along_kernel<T><<<grid_for(ylen, kRThreads), kRThreads, 0, s>>>(x, y, ylen, xs[dim], inner);
   ZG_LAUNCH_CHECK();
 }
 
@@ -485,8 +600,7 @@ extern "C" void clip_nrm2(dtype id, CublasWrapper w, void* x, void* cur_nrm2, le
 template <typename T>
 static void max_fwd_impl(cudaStream_t s, const T* x, T* y, size_t n) {
   if (n == 0) return;
-  unsigned g = grid_for(n, (size_t)kRThreads * 16, 2);
-  if (g > 1024) g = 1024;
+  unsigned g = grid_for(n, (size_t)kRThreads * 16, 8);
   unsigned* counters = nullptr;
   char* ws = static_cast<char*>(workspace(s, (sizeof(T) + 8) * g + 16, &counters));
   if (!ws) return;
