@@ -113,13 +113,30 @@ __device__ __forceinline__ void smce_finish(const SmceArgs& a, float loss_acc, f
   }
 }
 
-__device__ __forceinline__ float grad_scale(const SmceArgs& a, float d) { return a.exact_inv ? d * a.inv_divisor : d / a.divisor; }
+// log of the probability clamp of the reference loss (p limited to [1e-7, 1 - 1e-7]):
+// log(clamp(p)) == clamp(log p), and log p = (x - max) - log(sum exp) needs no log per element
+constexpr float kLogPMin = -16.11809565f;     // logf(1e-7f)
+constexpr float kLogPMax = -1.1920929e-07f;   // logf(1.0f - 1e-7f)
+__device__ __forceinline__ float clamp_logp(float lp) { return fminf(fmaxf(lp, kLogPMin), kLogPMax); }
+
+// exp of a non-positive shifted logit: one multiply and the hardware base-2
+// exponential (relative error about 2^-22 plus 2^-24 |d| from the rounded
+// product; the softmax that comes out agrees with an exact one to ~1e-6)
+__device__ __forceinline__ float fast_exp(float d) { return __expf(d); }
+
+// FAST: dlogits written (not accumulated), no probabilities wanted, divisor a power of two
+template <bool FAST>
+__device__ __forceinline__ float grad_scale(const SmceArgs& a, float d) {
+  if (FAST) return d * a.inv_divisor;
+  return a.exact_inv ? d * a.inv_divisor : d / a.divisor;
+}
 
 // One warp per row, ROWS rows per trip; ITEMS = ceil(C/32) logits per lane and
 // row held in registers, so the logits are read from memory exactly once and
 // dlogits written once.  All loads of a trip are issued before the first
-// shuffle, and the ROWS independent reductions overlap.
-template <int ITEMS, int ROWS, bool INDEX_LABELS>
+// shuffle, the ROWS independent reductions overlap, and the element loops are
+// branch-free (index labels) so that the compiler can interleave them.
+template <int ITEMS, int ROWS, bool INDEX_LABELS, bool FAST>
 __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a) {
   __shared__ float sm32[32];
   __shared__ float colsum[32 * ITEMS];
@@ -132,7 +149,8 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
   for (int i = 0; i < ITEMS; ++i) bias_acc[i] = 0.f;
   for (size_t r0 = (((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * ROWS; r0 < a.rows; r0 += warps * ROWS) {
     float x[ROWS][ITEMS];
-    float mx[ROWS], se[ROWS];
+    float mx[ROWS], se[ROWS], dlab[ROWS];
+    int lab[ROWS];
 #pragma unroll
     for (int k = 0; k < ROWS; ++k) {
       const bool ok = r0 + k < a.rows;
@@ -143,9 +161,14 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
         x[k][i] = (ok && j < C) ? xr[j] : -INFINITY;
       }
     }
-    size_t label_idx[ROWS];
 #pragma unroll
-    for (int k = 0; k < ROWS; ++k) label_idx[k] = (INDEX_LABELS && r0 + k < a.rows) ? static_cast<const len_t*>(a.labels)[r0 + k] : 0;
+    for (int k = 0; k < ROWS; ++k) {
+      lab[k] = -1;
+      if (INDEX_LABELS && r0 + k < a.rows) {
+        const len_t l = static_cast<const len_t*>(a.labels)[r0 + k];
+        lab[k] = l < (len_t)C ? (int)l : -1;
+      }
+    }
 #pragma unroll
     for (int k = 0; k < ROWS; ++k) {
       float m = x[k][0];
@@ -162,11 +185,16 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
       float sacc = 0.f;
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
-        const bool live = (r0 + k < a.rows) && (lane + 32 * i < C);
-        x[k][i] = live ? expf(x[k][i] - mx[k]) : 0.f;
+        x[k][i] = fast_exp(x[k][i] - mx[k]);          // -inf in the padding lanes gives 0
         sacc += x[k][i];
       }
       se[k] = sacc;
+    }
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      // the lane that owns the label column fetches that logit again (a cache hit)
+      dlab[k] = 0.f;
+      if (INDEX_LABELS && lab[k] >= 0 && (lab[k] & 31) == lane) dlab[k] = a.logits[(r0 + k) * a.ld + lab[k]] - mx[k];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -177,19 +205,34 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
       if (r0 + k >= a.rows) continue;
       const size_t r = r0 + k;
       const float inv = 1.f / se[k];
+      const float lse = logf(se[k]);
+      if (INDEX_LABELS && lab[k] >= 0 && (lab[k] & 31) == lane) loss_acc -= clamp_logp(dlab[k] - lse);
       const float* tr = INDEX_LABELS ? nullptr : static_cast<const float*>(a.labels) + r * (size_t)C;
+      float* dl = a.dlogits + r * a.ld;
+      // FAST: the divisor is a power of two, so (e * inv - t) * 2^-k == e * (inv * 2^-k) - t * 2^-k bit for bit
+      const float sc = inv * a.inv_divisor;
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
         const int j = lane + 32 * i;
         if (j < C) {
-          const float p = x[k][i] * inv;
-          const float t = INDEX_LABELS ? ((size_t)j == label_idx[k] ? 1.f : 0.f) : tr[j];
-          if (t != 0.f) loss_acc -= t * logf(fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f));
-          const size_t o = r * a.ld + j;
-          if (a.probs_out) a.probs_out[o] = p;
-          const float g = grad_scale(a, p - t);
+          float g;
+          if (FAST && INDEX_LABELS) {
+            g = x[k][i] * sc;
+            if (j == lab[k]) g -= a.inv_divisor;
+          } else {
+            const float p = x[k][i] * inv;
+            float t;
+            if (INDEX_LABELS) t = (j == lab[k]) ? 1.f : 0.f;
+            else {
+              t = tr[j];
+              if (t != 0.f) loss_acc -= t * clamp_logp(logf(p));
+            }
+            g = grad_scale<FAST>(a, p - t);
+            if (!FAST && a.probs_out) a.probs_out[r * a.ld + j] = p;
+          }
           bias_acc[i] += g;
-          if (a.dlogits) a.dlogits[o] = a.accumulate ? a.dlogits[o] + g : g;
+          if (FAST) dl[j] = g;
+          else if (a.dlogits) dl[j] = a.accumulate ? dl[j] + g : g;
         }
       }
     }
@@ -275,8 +318,11 @@ __device__ __forceinline__ void stage_store(const float* sm, int S, float* g, si
   }
 }
 
-template <int CP, bool INDEX_LABELS>  // CP: C rounded up to 8, 16 or 32
+__host__ __device__ constexpr int pow2_at_least(int v) { return v <= 4 ? 4 : (v <= 8 ? 8 : (v <= 16 ? 16 : 32)); }
+
+template <int CP, bool INDEX_LABELS, bool FAST>  // CP: C rounded up to 4, 8, 12, 16, 24 or 32
 __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceArgs a) {
+  constexpr int P2 = pow2_at_least(CP);
   __shared__ float sm32[32];
   __shared__ float wsum[kRowThreads / 32][32];
   __shared__ __align__(16) float stage[kRowThreads * (kRowMaxW + 1)];
@@ -286,9 +332,9 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceA
   const bool block_rows = a.ld <= (size_t)kRowMaxW;  // rows and their padding form one contiguous block
   const int W = block_rows ? (int)a.ld : C;
   const int S = W | 1, ST = C | 1;
-  float gacc[CP];
+  float gacc[P2];
 #pragma unroll
-  for (int j = 0; j < CP; ++j) gacc[j] = 0.f;
+  for (int j = 0; j < P2; ++j) gacc[j] = 0.f;
   float loss_acc = 0.f;
   for (size_t base = (size_t)blockIdx.x * kRowThreads; base < a.rows; base += (size_t)gridDim.x * kRowThreads) {
     const int nrows = (int)((a.rows - base) < (size_t)kRowThreads ? (a.rows - base) : (size_t)kRowThreads);
@@ -299,44 +345,62 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceA
       const size_t r = base + threadIdx.x;
       float* xs = stage + threadIdx.x * S;
       const float* tr = tstage + threadIdx.x * ST;
-      float x[CP];
+      float d[CP], e[CP];
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < CP; ++j) {
-        x[j] = (j < C) ? xs[j] : -INFINITY;
-        mx = fmaxf(mx, x[j]);
+        d[j] = (j < C) ? xs[j] : -INFINITY;
+        mx = fmaxf(mx, d[j]);
+      }
+      int lab = -1;
+      if (INDEX_LABELS) {
+        const len_t l = static_cast<const len_t*>(a.labels)[r];
+        lab = l < (len_t)C ? (int)l : -1;
       }
       float se = 0.f;
+      const float dlab = (INDEX_LABELS && lab >= 0) ? xs[lab] - mx : 0.f;
 #pragma unroll
       for (int j = 0; j < CP; ++j) {
-        x[j] = (j < C) ? expf(x[j] - mx) : 0.f;
-        se += x[j];
+        d[j] -= mx;                       // -inf in the padding columns: exp gives 0
+        e[j] = fast_exp(d[j]);
+        se += e[j];
       }
       const float inv = 1.f / se;
-      size_t label_idx = 0;
-      if (INDEX_LABELS) label_idx = static_cast<const len_t*>(a.labels)[r];
+      const float lse = logf(se);
+      if (INDEX_LABELS && lab >= 0) loss_acc -= clamp_logp(dlab - lse);
+      const float sc = inv * a.inv_divisor;  // FAST: exact power-of-two scaling (see the warp kernel)
 #pragma unroll
       for (int j = 0; j < CP; ++j) {
         if (j < C) {
-          const float p = x[j] * inv;
-          const float t = INDEX_LABELS ? ((size_t)j == label_idx ? 1.f : 0.f) : tr[j];
-          if (t != 0.f) loss_acc -= t * logf(fminf(fmaxf(p, 1e-7f), 1.0f - 1e-7f));
-          if (a.probs_out) a.probs_out[r * a.ld + j] = p;
-          const float g = grad_scale(a, p - t);
+          float g;
+          if (FAST && INDEX_LABELS) {
+            g = e[j] * sc;
+            if (j == lab) g -= a.inv_divisor;
+          } else {
+            const float p = e[j] * inv;
+            float t;
+            if (INDEX_LABELS) t = (j == lab) ? 1.f : 0.f;
+            else {
+              t = tr[j];
+              loss_acc -= t * clamp_logp(d[j] - lse);
+            }
+            if (!FAST && a.probs_out) a.probs_out[r * a.ld + j] = p;
+            g = grad_scale<FAST>(a, p - t);
+          }
           gacc[j] += g;
           xs[j] = g;
         }
       }
     }
     __syncthreads();
-    if (a.dlogits) stage_store(stage, S, a.dlogits + base * a.ld, a.ld, C, nrows, a.accumulate != 0);
+    if (FAST || a.dlogits) stage_store(stage, S, a.dlogits + base * a.ld, a.ld, C, nrows, FAST ? false : a.accumulate != 0);
     __syncthreads();
   }
   if (a.dbias) {
-    // log2(CP) exchange rounds: lane l ends with the sum of column (l mod CP)
-    // over the CP lanes of its group in gacc[0]
+    // log2(P2) exchange rounds: lane l ends with the sum of column (l mod P2)
+    // over the P2 lanes of its group in gacc[0]
 #pragma unroll
-    for (int off = CP / 2; off >= 1; off >>= 1) {
+    for (int off = P2 / 2; off >= 1; off >>= 1) {
       const bool upper = (lane & off) != 0;
 #pragma unroll
       for (int j = 0; j < off; ++j) {
@@ -345,9 +409,9 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceA
         gacc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
       }
     }
-    // groups (lanes that agree modulo CP) hold partial sums of the same column
+    // groups (lanes that agree modulo P2) hold partial sums of the same column
 #pragma unroll
-    for (int off = 16; off >= CP; off >>= 1) gacc[0] += __shfl_xor_sync(0xffffffffu, gacc[0], off);
+    for (int off = 16; off >= P2; off >>= 1) gacc[0] += __shfl_xor_sync(0xffffffffu, gacc[0], off);
     wsum[warp][lane] = gacc[0];
     __syncthreads();
     if ((int)threadIdx.x < C) {
@@ -480,9 +544,9 @@ static unsigned resident_ctas(K kernel, int threads) {
   return (unsigned)occ * (unsigned)sm_count();
 }
 
-template <int CP, bool IDX>
+template <int CP, bool IDX, bool FAST>
 static void launch_smce_rows(cudaStream_t s, SmceArgs a) {
-  static const unsigned resident = resident_ctas(softmax_ce_row_kernel<CP, IDX>, kRowThreads);
+  static const unsigned resident = resident_ctas(softmax_ce_row_kernel<CP, IDX, FAST>, kRowThreads);
   const unsigned gr = (unsigned)std::min<size_t>((a.rows + kRowThreads - 1) / kRowThreads, resident);
   unsigned* counters = nullptr;
   float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)gr + (a.dbias ? (size_t)gr * a.C : 0)), &counters));
@@ -490,13 +554,13 @@ static void launch_smce_rows(cudaStream_t s, SmceArgs a) {
   a.partial = partial;
   a.counter = counters;
   a.fold_bias_inline = 1;
-  softmax_ce_row_kernel<CP, IDX><<<gr, kRowThreads, 0, s>>>(a);
+  softmax_ce_row_kernel<CP, IDX, FAST><<<gr, kRowThreads, 0, s>>>(a);
   ZG_LAUNCH_CHECK();
 }
 
-template <int ITEMS, int ROWS, bool IDX>
+template <int ITEMS, int ROWS, bool IDX, bool FAST>
 static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
-  static const unsigned resident = resident_ctas(softmax_ce_kernel<ITEMS, ROWS, IDX>, kLThreads);
+  static const unsigned resident = resident_ctas(softmax_ce_kernel<ITEMS, ROWS, IDX, FAST>, kLThreads);
   const int C = a.C;
   const size_t rows_per_cta = (size_t)(kLThreads / 32) * ROWS;
   unsigned g = (unsigned)std::min<size_t>((a.rows + rows_per_cta - 1) / rows_per_cta, resident);
@@ -510,7 +574,7 @@ static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
   a.partial = partial;
   a.counter = counters;
   a.fold_bias_inline = separate_fold ? 0 : 1;
-  softmax_ce_kernel<ITEMS, ROWS, IDX><<<g, kLThreads, 0, s>>>(a);
+  softmax_ce_kernel<ITEMS, ROWS, IDX, FAST><<<g, kLThreads, 0, s>>>(a);
   if (!ZG_LAUNCH_CHECK()) return;
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
@@ -521,14 +585,22 @@ static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
   int e = 0;
   a.inv_divisor = 1.f / a.divisor;
   a.exact_inv = (std::frexp(a.divisor, &e) == 0.5f && std::isnormal(a.inv_divisor)) ? 1 : 0;
-  if (C <= 8) return launch_smce_rows<8, IDX>(s, a);
-  if (C <= 16) return launch_smce_rows<16, IDX>(s, a);
-  if (C <= 32) return launch_smce_rows<32, IDX>(s, a);
-  if (C <= 64) return launch_smce_warps<2, 8, IDX>(s, a);
-  if (C <= 128) return launch_smce_warps<4, 4, IDX>(s, a);
-  if (C <= 256) return launch_smce_warps<8, 2, IDX>(s, a);
-  if (C <= 512) return launch_smce_warps<16, 2, IDX>(s, a);
-  if (C <= 1024) return launch_smce_warps<32, 1, IDX>(s, a);
+  const bool fast = a.exact_inv && a.dlogits && !a.accumulate && !a.probs_out;
+#define ZG_ROWS(CPV) return fast ? launch_smce_rows<CPV, IDX, true>(s, a) : launch_smce_rows<CPV, IDX, false>(s, a)
+#define ZG_WARPS(I, R) return fast ? launch_smce_warps<I, R, IDX, true>(s, a) : launch_smce_warps<I, R, IDX, false>(s, a)
+  if (C <= 4) ZG_ROWS(4);
+  if (C <= 8) ZG_ROWS(8);
+  if (C <= 12) ZG_ROWS(12);
+  if (C <= 16) ZG_ROWS(16);
+  if (C <= 24) ZG_ROWS(24);
+  if (C <= 32) ZG_ROWS(32);
+  if (C <= 64) ZG_WARPS(2, 8);
+  if (C <= 128) ZG_WARPS(4, 4);
+  if (C <= 256) ZG_WARPS(8, 2);
+  if (C <= 512) ZG_WARPS(16, 2);
+  if (C <= 1024) ZG_WARPS(32, 1);
+#undef ZG_ROWS
+#undef ZG_WARPS
   if (a.dbias) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: the fused bias gradient supports C <= 1024"); return; }
   unsigned g = grid_for(a.rows, kLThreads / 32, 8);
   unsigned* counters = nullptr;
