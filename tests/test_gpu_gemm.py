@@ -207,3 +207,92 @@ def test_large_gemm_linearity_property(gpu):
     assert rel_err(c1, c2) <= 2e-5
     for s in (A1, A2, B, S, C1, C2):
         d.mem_cache_free(s)
+
+
+# ---------------------------------------------------------------- persistent kernel
+# Shapes with at least one 128 x 256 tile per SM take the persistent kernel
+# (bf16 and single-pass TF32): 40 x 4 = 160 tiles, ragged m / n / k edges.
+PERSISTENT_SHAPES = [(5120, 1024, 512), (5000, 1000, 520)]
+
+
+@pytest.mark.parametrize("trans", list(TRANS))
+@pytest.mark.parametrize("shape", PERSISTENT_SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("c_bf16", [False, True])
+def test_persistent_gemm_bf16(gpu, trans, shape, c_bf16):
+    m, n, k = shape
+    ta, tb = TRANS[trans]
+    g = rng(m + 2 * n + 3 * k + 1)
+    a_shape, b_shape = ((k, m) if ta else (m, k)), ((n, k) if tb else (k, n))
+    A, B = g.standard_normal(a_shape).astype(np.float32), g.standard_normal(b_shape).astype(np.float32)
+    Ar, Br = oracle.round_bf16(A.ravel()).reshape(a_shape), oracle.round_bf16(B.ravel()).reshape(b_shape)
+    want = ORC.bmm_acc(Ar, Br, np.zeros((m, n), np.float32), (1, m, k), (1, k, n), (1, m, n), ta, tb, a_shape[1], b_shape[1], n, 1.0, 0.0)
+    be = GpuBackend(gpu)
+    a, b = be.up(to_bf16_bits(A), np.uint16), be.up(to_bf16_bits(B), np.uint16)
+    c = be.up(np.zeros(m * n, np.uint16), np.uint16) if c_bf16 else be.up(np.zeros(m * n, np.float32))
+    gpu.dispatch(opspec.linear(a, b, c, m, n, k, ta, tb, a_shape[1], b_shape[1], n))
+    out = be.down(c)
+    if c_bf16:
+        out = (out.astype(np.uint32) << 16).view(np.float32)
+    assert rel_err(out.reshape(m, n), want) <= (4e-3 if c_bf16 else 1e-5), rel_err(out.reshape(m, n), want)
+
+
+@pytest.mark.parametrize("trans", list(TRANS))
+def test_persistent_gemm_tf32_and_accumulate(gpu, trans):
+    m, n, k = 5000, 1000, 520
+    ta, tb = TRANS[trans]
+    got, want = run_gemm(gpu, abi.MATH_TF32, m, n, k, ta, tb, alpha=0.5, beta=1.0, seed=11)
+    assert rel_err(got, want) <= 2e-3, rel_err(got, want)
+
+
+def test_persistent_gemm_bf16_epilogues(gpu):
+    """The mixed-precision layer shapes: bias+ReLU with bf16 output, ReLU mask
+    with bf16 mask/output plus column sums, fp32 accumulation into dW."""
+    m, n, k = 5120, 768, 512
+    g = rng(77)
+    X, W = g.standard_normal((m, k)).astype(np.float32), g.standard_normal((n, k)).astype(np.float32) * 0.05
+    b = g.standard_normal(n).astype(np.float32)
+    r16 = lambda a: oracle.round_bf16(np.ascontiguousarray(a, np.float32).ravel()).reshape(a.shape)
+    Xr, Wr = r16(X), r16(W)
+    be = GpuBackend(gpu)
+    x, w = be.up(to_bf16_bits(X), np.uint16), be.up(to_bf16_bits(W), np.uint16)
+    bias = be.up(b)
+    # forward: relu(X W^T + b) -> bf16
+    y = be.up(np.zeros(m * n, np.uint16), np.uint16)
+    gpu.dispatch(opspec.linear(x, w, y, m, n, k, False, True, k, k, n, 1.0, 0.0, "bias_relu", bias))
+    want = np.maximum(ORC.bmm_acc(Xr, Wr, np.zeros((m, n), np.float32), (1, m, k), (1, k, n), (1, m, n), False, True, k, k, n, 1.0, 0.0) + b, 0)
+    got = (gpu.to_numpy(y).astype(np.uint32) << 16).view(np.float32).reshape(m, n)
+    assert rel_err(got, want) <= 4e-3
+    # dX = dY W masked by the layer input activation (bf16), column sums added to db
+    dY = g.standard_normal((m, n)).astype(np.float32)
+    prev = np.maximum(g.standard_normal((m, k)).astype(np.float32), 0)
+    dy, pv = be.up(to_bf16_bits(dY), np.uint16), be.up(to_bf16_bits(prev), np.uint16)
+    dx = be.up(np.zeros(m * k, np.uint16), np.uint16)
+    db = be.up(np.zeros(k, np.float32))
+    gpu.dispatch(opspec.linear(dy, w, dx, m, k, n, False, False, n, k, k, 1.0, 0.0, "relu_mask", None, pv, colsum=db))
+    wdx = ORC.bmm_acc(r16(dY), Wr, np.zeros((m, k), np.float32), (1, m, n), (1, n, k), (1, m, k), False, False, n, k, k, 1.0, 0.0)
+    wdx[r16(prev) <= 0] = 0
+    gdx = (gpu.to_numpy(dx).astype(np.uint32) << 16).view(np.float32).reshape(m, k)
+    assert rel_err(gdx, wdx) <= 4e-3
+    assert rel_err(gpu.to_numpy(db), wdx.sum(0)) <= 1e-3
+    # dW += dY^T X in fp32 (m = n_out, n = k_in, contraction over the batch)
+    dw0 = g.standard_normal((n, k)).astype(np.float32)
+    dw = be.up(dw0)
+    gpu.dispatch(opspec.linear(dy, x, dw, n, k, m, True, False, n, k, k, 1.0, 1.0))
+    wdw = ORC.bmm_acc(r16(dY), Xr, dw0.copy(), (1, n, m), (1, m, k), (1, n, k), True, False, n, k, k, 1.0, 1.0)
+    assert rel_err(be.down(dw).reshape(n, k), wdw) <= 1e-5
+
+
+@pytest.mark.parametrize("beta", [1.0, 0.0, 0.5])
+def test_persistent_gemm_split_k_weight_gradient(gpu, beta):
+    """160 tiles of 128 x 256 on 148 SMs: the K ranges become work items
+    (vector reductions into C, pre-scaled by beta)."""
+    m, n, k = 2560, 2048, 4096
+    g = rng(5)
+    A, B = g.standard_normal((k, m)).astype(np.float32), g.standard_normal((k, n)).astype(np.float32)
+    C0 = g.standard_normal((m, n)).astype(np.float32)
+    r16 = lambda a: oracle.round_bf16(np.ascontiguousarray(a, np.float32).ravel()).reshape(a.shape)
+    want = ORC.bmm_acc(r16(A), r16(B), C0.copy(), (1, m, k), (1, k, n), (1, m, n), True, False, m, n, n, 1.0, beta)
+    be = GpuBackend(gpu)
+    a, b, c = be.up(to_bf16_bits(A), np.uint16), be.up(to_bf16_bits(B), np.uint16), be.up(C0)
+    gpu.dispatch(opspec.linear(a, b, c, m, n, k, True, False, m, n, n, 1.0, beta))
+    assert rel_err(be.down(c).reshape(m, n), want) <= 1e-5

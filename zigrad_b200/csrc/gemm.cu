@@ -2,12 +2,14 @@
 // (include/blas_conflux.h).  Large, TMA-addressable problems go to the
 // tcgen05 kernel (gemm_tc.cuh); everything else (tiny shapes, rows whose byte
 // stride is not a multiple of 16, fp64) runs on a register-tiled FFMA kernel.
+#include <cmath>
 #include <cstring>
 #include <mutex>
 
 #include "common.cuh"
 #include "driver_api.h"
 #include "gemm_tc.cuh"
+#include "gemm_tc_persistent.cuh"
 #include "../../include/blas_conflux.h"
 
 namespace zg {
@@ -234,6 +236,30 @@ static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor,
   return false;
 }
 
+template <bool AK, bool BK_, int MODE>
+static bool launch_persistent_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tb, const tc::Params& p, uint32_t tiles_m,
+                                   uint32_t tiles_n, uint32_t n_tiles) {
+  using SL = tc::PersistentSmem<MODE>;
+  auto kern = tc::gemm_tc_persistent_kernel<AK, BK_, MODE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::kTotal))) return false;
+    attr_set = true;
+  }
+  const unsigned grid = n_tiles < (uint32_t)sm_count() ? n_tiles : (unsigned)sm_count();
+  kern<<<grid, tc::kThreadsPersistent, SL::kTotal, s>>>(ta, tb, p, tiles_m, tiles_n, n_tiles);
+  return ZG_LAUNCH_CHECK();
+}
+
+template <int MODE>
+static bool launch_persistent(cudaStream_t s, bool a_kmajor, bool b_kmajor, const CUtensorMap& ta, const CUtensorMap& tb,
+                              const tc::Params& p, uint32_t tiles_m, uint32_t tiles_n, uint32_t n_tiles) {
+  if (a_kmajor && b_kmajor) return launch_persistent_inst<true, true, MODE>(s, ta, tb, p, tiles_m, tiles_n, n_tiles);
+  if (a_kmajor && !b_kmajor) return launch_persistent_inst<true, false, MODE>(s, ta, tb, p, tiles_m, tiles_n, n_tiles);
+  if (!a_kmajor && b_kmajor) return launch_persistent_inst<false, true, MODE>(s, ta, tb, p, tiles_m, tiles_n, n_tiles);
+  return launch_persistent_inst<false, false, MODE>(s, ta, tb, p, tiles_m, tiles_n, n_tiles);
+}
+
 // Returns true when the tensor-core path took the problem.
 static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                             len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
@@ -255,20 +281,37 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   const int bk = bf16 ? 64 : 32;
   const bool a_kmajor = !ta;              // A stored [m,k] -> K contiguous
   const bool b_kmajor = tb;               // B stored [n,k] -> K contiguous
-  int bn = n <= 32 ? 32 : (n <= 64 ? 64 : 128);
+  // Large single-pass problems: persistent kernel over 128 x 256 tiles
+  // (at least one tile per SM, k deep enough to amortise the tile hand-over).
+  const char* no_persist = getenv("ZG_GEMM_NO_PERSISTENT");
+  const size_t ptiles = ((m + 127) / 128) * ((n + 255) / 256) * nC;
+  const bool persistent = mode != tc::kFP32X3 && n > 128 && k >= 8 * (size_t)bk && ptiles * 2 >= (size_t)sm_count() &&
+                          ptiles <= 0x3fffffffu && !(no_persist && no_persist[0] == '1');
+  int bn = persistent ? 256 : (n <= 32 ? 32 : (n <= 64 ? 64 : 128));
   if (bn < atom) bn = atom;               // MN-major B needs whole column blocks; bf16 has no BN=32 instance
   size_t tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
   // Deep-k problems with a plain epilogue (weight gradients) get their
   // parallelism from K splits, so they keep the wide tile (fewer operand bytes
   // per flop through shared memory); everything else halves BN when there are
   // too few tiles to occupy the SMs.
-  const bool can_split = epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 1024;
+  const bool can_split = !persistent && epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 1024;
   if (!can_split && bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) {
     bn = 64;
     tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
   }
 
   unsigned splits = 1;
+  if (persistent && epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE) {
+    // K ranges as work items when that fills the last wave better (>= 16 k-slabs per range)
+    const double sms = (double)sm_count();
+    double best = 0.0;
+    for (unsigned sp = 1; sp <= 4; sp *= 2) {
+      if (sp > 1 && k / sp < 16 * (size_t)bk) break;
+      const double items = (double)ptiles * sp;
+      const double eff = items / (std::ceil(items / sms) * sms);
+      if (eff > best + 0.03) { best = eff; splits = sp; }
+    }
+  }
   if (can_split && tiles * 2 <= (size_t)sm_count()) {
     size_t want = (size_t)sm_count() / tiles;
     size_t maxs = k / (4 * (size_t)bk);  // at least four k-slabs per split
@@ -307,6 +350,14 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
     p.vec_ok = ok ? 1 : 0;
   }
   p.error_flag = tc_error_flag();
+  if (persistent) {
+    const uint32_t tiles_m = (uint32_t)((m + 127) / 128), tiles_n = (uint32_t)((n + 255) / 256);
+    const uint32_t items = (uint32_t)(ptiles * splits);
+    if (splits > 1) prescale_c<float>(s, static_cast<float*>(C), nC, m, n, ldc, m * ldc, beta);
+    if (mode == tc::kBF16) launch_persistent<tc::kBF16>(s, a_kmajor, b_kmajor, tmA, tmB, p, tiles_m, tiles_n, items);
+    else launch_persistent<tc::kTF32>(s, a_kmajor, b_kmajor, tmA, tmB, p, tiles_m, tiles_n, items);
+    return true;
+  }
   if (splits > 1) prescale_c<float>(s, static_cast<float*>(C), nC, m, n, ldc, m * ldc, beta);
   dim3 grid((unsigned)((n + bn - 1) / bn), (unsigned)((m + 127) / 128), (unsigned)(nC * splits));
   if (grid.y > 65535 || grid.z > 65535) return false;

@@ -198,6 +198,141 @@ struct ModeTraits {
   static constexpr int kBufs = (MODE == kFP32X3) ? 2 : 1;  // hi (+ lo) copies of each operand slab
 };
 
+// Epilogue of one 32-column chunk of one accumulator row (registers r, raw
+// fp32 bits): alpha/beta/bias/ReLU/mask, the store (or the split-K reduction
+// into C), and the optional column sums.  `o` = element offset of (row, col0)
+// in C; warp-collective when p.colsum is set.
+__device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (&r)[32], bool row_ok, uint64_t o, uint32_t col0, int lane) {
+  if (!row_ok && !p.colsum) return;
+  const bool need_c = p.beta != 0.f, need_m = p.epilogue == ZG_EPI_RELU_MASK;
+  const bool has_bias = p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+  const bool full = p.vec_ok && (col0 + 32 <= p.n);
+  if (!row_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+  } else if (full) {
+    if (p.splits > 1) {
+      // C was pre-scaled by beta on the host side; no fused epilogue with split-K
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.C + o + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
+      return;
+    }
+    if (p.C) {  // fp32 C / mask
+      if (need_c) {
+        float4 cv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cv[j] = *reinterpret_cast<const float4*>(p.C + o + 4 * j);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[4 * j] += p.beta * cv[j].x; v[4 * j + 1] += p.beta * cv[j].y; v[4 * j + 2] += p.beta * cv[j].z; v[4 * j + 3] += p.beta * cv[j].w; }
+      }
+      if (has_bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+          v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+        }
+        if (p.epilogue == ZG_EPI_BIAS_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+        }
+      } else if (need_m) {
+        float4 mv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mv[j] = *reinterpret_cast<const float4*>(p.mask + o + 4 * j);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (mv[j].x <= 0.f) v[4 * j] = 0.f;
+          if (mv[j].y <= 0.f) v[4 * j + 1] = 0.f;
+          if (mv[j].z <= 0.f) v[4 * j + 2] = 0.f;
+          if (mv[j].w <= 0.f) v[4 * j + 3] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(p.C + o + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {  // bf16 C / mask: 32 values = 64 bytes = 4 x 16-byte accesses
+      if (need_c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = *reinterpret_cast<const uint4*>(p.Cb + o + 8 * j);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) { const float2 f = __bfloat1622float2(h[t]); v[8 * j + 2 * t] += p.beta * f.x; v[8 * j + 2 * t + 1] += p.beta * f.y; }
+        }
+      }
+      if (has_bias) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+          v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+        }
+        if (p.epilogue == ZG_EPI_BIAS_RELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+        }
+      } else if (need_m) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = *reinterpret_cast<const uint4*>(p.maskb + o + 8 * j);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = __bfloat1622float2(h[t]);
+            if (f.x <= 0.f) v[8 * j + 2 * t] = 0.f;
+            if (f.y <= 0.f) v[8 * j + 2 * t + 1] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+        *reinterpret_cast<uint4*>(p.Cb + o + 8 * j) = u;
+      }
+    }
+  } else {
+    // ragged edge or unaligned C: element-wise with a column bound
+    const uint32_t ncol = (p.n - col0) < 32u ? (p.n - col0) : 32u;
+#pragma unroll
+    for (uint32_t j = 0; j < 32; ++j) {
+      if (j < ncol) {
+        float x = v[j];
+        if (p.splits > 1) { atomicAdd(p.C + o + j, x); continue; }
+        if (need_c) x += p.beta * (p.C ? p.C[o + j] : __bfloat162float(p.Cb[o + j]));
+        if (has_bias) { x += p.bias[col0 + j]; if (p.epilogue == ZG_EPI_BIAS_RELU) x = x > 0.f ? x : 0.f; }
+        else if (need_m) { if ((p.mask ? p.mask[o + j] : __bfloat162float(p.maskb[o + j])) <= 0.f) x = 0.f; }
+        if (p.C) p.C[o + j] = x;
+        else p.Cb[o + j] = __float2bfloat16_rn(x);
+        v[j] = x;
+      } else {
+        v[j] = 0.f;
+      }
+    }
+  }
+  if (p.colsum) {
+    // Column sums of this warp's 32 x 32 block without shared memory: five
+    // exchange rounds, each halving the columns a lane still carries (a lane
+    // keeps the half selected by its own bit); lane j ends with column j.
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int j = 0; j < off; ++j) {
+        const float send = upper ? v[j] : v[j + off];
+        const float keep = upper ? v[j + off] : v[j];
+        v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    if (col0 + lane < p.n) atomicAdd(p.colsum + col0 + lane, v[0]);
+  }
+}
+
 template <int BN, int MODE>
 struct SmemLayout {
   using MT = ModeTraits<MODE>;
@@ -377,8 +512,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t row = tile_m * kBM + q * 32 + lane;
     const uint64_t c_off = (uint64_t)batch * p.c_batch_stride + (uint64_t)row * p.ldc;
     const bool row_ok = row < p.m;
-    const bool need_c = p.beta != 0.f, need_m = p.epilogue == ZG_EPI_RELU_MASK;
-    const bool has_bias = p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU;
     if (KT == 0 || have_acc) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -392,133 +525,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (!row_ok && !p.colsum) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
-        const uint64_t o = c_off + col0;
-        const bool full = p.vec_ok && (col0 + 32 <= p.n);
-        if (!row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        } else if (full) {
-          if (p.splits > 1) {
-            // C was pre-scaled by beta on the host side; no fused epilogue with split-K
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.C + o + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
-            continue;
-          }
-          if (p.C) {  // fp32 C / mask
-            if (need_c) {
-              float4 cv[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) cv[j] = *reinterpret_cast<const float4*>(p.C + o + 4 * j);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { v[4 * j] += p.beta * cv[j].x; v[4 * j + 1] += p.beta * cv[j].y; v[4 * j + 2] += p.beta * cv[j].z; v[4 * j + 3] += p.beta * cv[j].w; }
-            }
-            if (has_bias) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
-                v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
-              }
-              if (p.epilogue == ZG_EPI_BIAS_RELU) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-              }
-            } else if (need_m) {
-              float4 mv[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) mv[j] = *reinterpret_cast<const float4*>(p.mask + o + 4 * j);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (mv[j].x <= 0.f) v[4 * j] = 0.f;
-                if (mv[j].y <= 0.f) v[4 * j + 1] = 0.f;
-                if (mv[j].z <= 0.f) v[4 * j + 2] = 0.f;
-                if (mv[j].w <= 0.f) v[4 * j + 3] = 0.f;
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<float4*>(p.C + o + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {  // bf16 C / mask: 32 values = 64 bytes = 4 x 16-byte accesses
-            if (need_c) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 u = *reinterpret_cast<const uint4*>(p.Cb + o + 8 * j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-                for (int t = 0; t < 4; ++t) { const float2 f = __bfloat1622float2(h[t]); v[8 * j + 2 * t] += p.beta * f.x; v[8 * j + 2 * t + 1] += p.beta * f.y; }
-              }
-            }
-            if (has_bias) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
-                v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
-              }
-              if (p.epilogue == ZG_EPI_BIAS_RELU) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
-              }
-            } else if (need_m) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 u = *reinterpret_cast<const uint4*>(p.maskb + o + 8 * j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  const float2 f = __bfloat1622float2(h[t]);
-                  if (f.x <= 0.f) v[8 * j + 2 * t] = 0.f;
-                  if (f.y <= 0.f) v[8 * j + 2 * t + 1] = 0.f;
-                }
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 u;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-              for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
-              *reinterpret_cast<uint4*>(p.Cb + o + 8 * j) = u;
-            }
-          }
-        } else {
-          // ragged edge or unaligned C: element-wise with a column bound
-          const uint32_t ncol = (p.n - col0) < 32u ? (p.n - col0) : 32u;
-#pragma unroll
-          for (uint32_t j = 0; j < 32; ++j) {
-            if (j < ncol) {
-              float x = v[j];
-              if (p.splits > 1) { atomicAdd(p.C + o + j, x); continue; }
-              if (need_c) x += p.beta * (p.C ? p.C[o + j] : __bfloat162float(p.Cb[o + j]));
-              if (has_bias) { x += p.bias[col0 + j]; if (p.epilogue == ZG_EPI_BIAS_RELU) x = x > 0.f ? x : 0.f; }
-              else if (need_m) { if ((p.mask ? p.mask[o + j] : __bfloat162float(p.maskb[o + j])) <= 0.f) x = 0.f; }
-              if (p.C) p.C[o + j] = x;
-              else p.Cb[o + j] = __float2bfloat16_rn(x);
-              v[j] = x;
-            } else {
-              v[j] = 0.f;
-            }
-          }
-        }
-        if (p.colsum) {
-          // Column sums of this warp's 32 x 32 block without shared memory: five
-          // exchange rounds, each halving the columns a lane still carries (a lane
-          // keeps the half selected by its own bit); lane j ends with column j.
-#pragma unroll
-          for (int off = 16; off >= 1; off >>= 1) {
-            const bool upper = (lane & off) != 0;
-#pragma unroll
-            for (int j = 0; j < off; ++j) {
-              const float send = upper ? v[j] : v[j + off];
-              const float keep = upper ? v[j + off] : v[j];
-              v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-            }
-          }
-          if (col0 + lane < p.n) atomicAdd(p.colsum + col0 + lane, v[0]);
-        }
+        epilogue_chunk(p, r, row_ok, c_off + col0, col0, lane);
       }
     }
   }

@@ -1,0 +1,233 @@
+// Persistent tcgen05 GEMM for large problems (bf16 and single-pass TF32).
+//
+// One CTA per SM walks a list of 128 x 256 output tiles.  Compared with the
+// one-tile-per-CTA kernel of gemm_tc.cuh:
+//   * the tile is twice as wide, so one k-slab of operands (A 16 KB + B 32 KB)
+//     feeds twice the tensor work: shared-memory traffic per flop drops by a
+//     quarter, which is what bounds the narrower tile;
+//   * the accumulator is double-buffered in tensor memory (2 x 256 columns =
+//     all 512): the epilogue warps drain tile i while the MMA warp already
+//     accumulates tile i+1, and the TMA ring never drains between tiles;
+//   * set-up (barriers, TMEM allocation, descriptor prefetch) is paid once per
+//     SM instead of once per tile.
+// Tiles are visited in groups of kGroupM row-tiles x all column-tiles so that
+// the CTAs running at the same time share operand slabs in L2.
+//
+// K may be split (weight gradients: fp32 C, no fused epilogue): a work item is
+// then one K range of one tile and its epilogue adds into C with vector
+// reductions, which evens out the last wave when the tile count is a poor
+// multiple of the SM count.
+//
+// Roles (12 warps): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
+// warps 4-11 epilogue in two groups (warp w drains TMEM lanes 32(w%4)..+31;
+// group 0 takes the even 32-column chunks of a tile, group 1 the odd ones, so
+// two chunks' global loads and stores are in flight at once).  Every mbarrier
+// wait is bounded (see mbar_wait); after a failed wait all roles stop and the
+// CTA still frees its tensor memory.
+#pragma once
+
+#include "gemm_tc.cuh"
+
+namespace zg {
+namespace tc {
+
+constexpr int kPBN = 256;      // tile width
+constexpr int kGroupM = 16;    // row-tiles per scheduling group
+constexpr int kThreadsPersistent = 384;
+constexpr int kEpiThreads = kThreadsPersistent - 128;
+
+template <int MODE>
+struct PersistentSmem {
+  using MT = ModeTraits<MODE>;
+  static constexpr int kABytes = kBM * kSlabBytes;    // 16 KB
+  static constexpr int kBBytes = kPBN * kSlabBytes;   // 32 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 4;
+  static constexpr int kTotal = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct TileCoord { uint32_t m, n, batch, split; };
+
+// tile index -> (row-tile, column-tile, batch); groups of kGroupM row-tiles, row-tile fastest inside a group
+__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t splits) {
+  TileCoord c;
+  c.split = t % splits;  // the K ranges of a tile are neighbours in the list: they run at the same time
+  t /= splits;
+  const uint32_t per_batch = tiles_m * tiles_n;
+  c.batch = t / per_batch;
+  t -= c.batch * per_batch;
+  const uint32_t group_sz = kGroupM * tiles_n;
+  const uint32_t g = t / group_sz, in_g = t - g * group_sz;
+  const uint32_t m0 = g * kGroupM;
+  const uint32_t gm = (tiles_m - m0) < (uint32_t)kGroupM ? (tiles_m - m0) : (uint32_t)kGroupM;
+  c.n = in_g / gm;
+  c.m = m0 + (in_g - c.n * gm);
+  return c;
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR, int MODE>
+__global__ void __launch_bounds__(kThreadsPersistent, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+                          const uint32_t tiles_m, const uint32_t tiles_n, const uint32_t n_tiles) {
+  static_assert(MODE == kBF16 || MODE == kTF32, "the persistent kernel has no operand-split warps");
+  using MT = ModeTraits<MODE>;
+  using SL = PersistentSmem<MODE>;
+  constexpr int S = SL::kStages;
+  constexpr int BN = kPBN;
+  constexpr uint32_t kIdesc = make_idesc(MT::kBf16, !A_KMAJOR, !B_KMAJOR, BN);
+  constexpr uint32_t kTmemCols = 512;  // two 256-column accumulators
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * SL::kStageBytes);
+  uint64_t* full = bars;                 // [S] TMA bytes landed
+  uint64_t* empty = bars + S;            // [S] MMAs that read the stage retired
+  uint64_t* acc_full = bars + 2 * S;     // [2] accumulator complete
+  uint64_t* acc_empty = bars + 2 * S + 2;  // [2] accumulator drained by the epilogue
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ volatile int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // k-slabs of K range `split` (p.k_per_split is a multiple of the slab depth)
+  auto slabs_of = [&](uint32_t split) -> int {
+    const uint32_t kb = split * p.k_per_split;
+    if (kb >= p.k) return 0;
+    const uint32_t ke = (kb + p.k_per_split < p.k) ? kb + p.k_per_split : p.k;
+    return (int)((ke - kb + MT::kBK - 1) / MT::kBK);
+  };
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], kEpiThreads);  // every epilogue thread arrives
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;  // k-slabs issued so far (ring position)
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.splits);
+        const int za = (int)(tc.batch % p.nA), zb = (int)(tc.batch % p.nB);
+        const int KT = slabs_of(tc.split);
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = (int)(it % S);
+          if (it >= (uint32_t)S && !mbar_wait(&empty[s], ((it / S) & 1) ^ 1, &failed)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * SL::kStageBytes;
+          uint8_t* b_dst = a_dst + SL::kABytes;
+          mbar_expect_tx(&full[s], SL::kStageBytes);
+          const int k0 = (int)(tc.split * p.k_per_split) + kt * MT::kBK;
+          if (A_KMAJOR) {
+            tma_load_3d(a_dst, &tmA, &full[s], k0, (int)(tc.m * kBM), za);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / MT::kAtomMN; ++j)
+              tma_load_3d(a_dst + j * MT::kBK * kSlabBytes, &tmA, &full[s], (int)(tc.m * kBM) + j * MT::kAtomMN, k0, za);
+          }
+          if (B_KMAJOR) {
+            // a TMA box holds at most 256 rows: one load for the whole 256-row slab
+            tma_load_3d(b_dst, &tmB, &full[s], k0, (int)(tc.n * BN), zb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / MT::kAtomMN; ++j)
+              tma_load_3d(b_dst + j * MT::kBK * kSlabBytes, &tmB, &full[s], (int)(tc.n * BN) + j * MT::kAtomMN, k0, zb);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++tcount) {
+        const uint32_t buf = tcount & 1;
+        if (tcount >= 2 && !mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1) ^ 1, &failed)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        const int KT = slabs_of(tile_coord(t, tiles_m, tiles_n, p.splits).split);
+        for (int kt = 0; kt < KT; ++kt, ++it) {
+          const int s = (int)(it % S);
+          if (!mbar_wait(&full[s], (it / S) & 1, &failed)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_s = smem_u32(smem + s * SL::kStageBytes), b_s = a_s + SL::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk) {
+            const uint32_t a_off = A_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
+            const uint32_t b_off = B_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
+            const uint32_t a_lbo = A_KMAJOR ? 16 : MT::kBK * kSlabBytes;
+            const uint32_t b_lbo = B_KMAJOR ? 16 : MT::kBK * kSlabBytes;
+            constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
+            constexpr uint32_t a_sbo = (a_lay == 1u) ? 512u : 1024u, b_sbo = (b_lay == 1u) ? 512u : 1024u;
+            const uint64_t da = make_desc(a_s + a_off, a_lbo, a_sbo, a_lay);
+            const uint64_t db = make_desc(b_s + b_off, b_lbo, b_sbo, b_lay);
+            umma<MT::kBf16>(tmem_d, da, db, kIdesc, (kt > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3, group = (warp - 4) >> 2;
+    uint32_t tcount = 0;
+    for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tcount) {
+      const uint32_t buf = tcount & 1;
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.splits);
+      const int KT = slabs_of(tc.split);
+      if (!mbar_wait(&acc_full[buf], (tcount >> 1) & 1, &failed)) break;
+      tc_fence_after();
+      const uint32_t row = tc.m * kBM + q * 32 + lane;
+      const uint64_t c_off = (uint64_t)tc.batch * p.c_batch_stride + (uint64_t)row * p.ldc;
+      const bool row_ok = row < p.m;
+#pragma unroll 1
+      for (int c = group; c < BN / 32; c += 2) {
+        const uint32_t col0 = tc.n * BN + c * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        if (KT > 0) {
+          tmem_ld32(tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        epilogue_chunk(p, r, row_ok, c_off + col0, col0, lane);
+      }
+      // all tcgen05.ld of this thread have completed (wait::ld): hand the accumulator back
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && failed && p.error_flag) *p.error_flag = 1;
+}
+
+}  // namespace tc
+}  // namespace zg
