@@ -25,6 +25,16 @@ EXTERN_C int zg_device_available(void);
 /* Binds the calling thread to a device ordinal (multi-device processes). */
 EXTERN_C void zg_set_device(unsigned device_number);
 
+/* Orders `waiter` after everything enqueued on `signaller` so far (an event
+ * recorded on one stream and waited on by the other).  Lets independent
+ * kernels of one step run side by side -- the weight-gradient GEMMs next to the
+ * dX chain -- and, while `signaller` is being captured, pulls `waiter` into the
+ * same capture so that the branch becomes a parallel branch of the graph (join
+ * it back with the arguments swapped before the capture is saved).  No
+ * counterpart in the reference, whose device owns a single stream
+ * (src/device/cuda_device.zig:24-33). */
+EXTERN_C void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller);
+
 /* Number of kernel nodes in a saved capture (cuda_utils.h: open_capture /
  * save_capture): what one run_capture launches. */
 EXTERN_C len_t zg_capture_kernel_count(GraphWrapper graph);

@@ -106,6 +106,7 @@ SIGNATURES = {
     "init_stream": (S, []),
     "deinit_stream": (None, [S]),
     "stream_synchronize": (None, [S]),
+    "zg_stream_wait": (None, [S, S]),
     "init_cublas_handle": (CB, [S]),
     "deinit_cublas_handle": (None, [CB]),
     "init_cudnn_handle": (CD, [S]),

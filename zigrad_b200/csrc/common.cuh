@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 
 #include "../../include/decls.h"
 #include "../../include/zg_b200.h"
@@ -65,7 +66,37 @@ static inline unsigned grid_for(size_t work_items, size_t per_cta, int ctas_per_
   return (unsigned)(want < cap ? want : cap);
 }
 
+// ------------------------------------------- programmatic dependent launch
+// Kernels launched through launch_pdl() may begin (block scheduling, their
+// prologue up to pdl_wait()) while the previous kernel of the stream is still
+// draining; pdl_wait() returns once that kernel has completed and its writes
+// are visible.  A kernel launched this way must call pdl_wait() before its
+// first global-memory access of data another kernel produces or still reads,
+// and pdl_trigger() after it, so that at most one successor is resident early.
+// Inside a captured graph the edge becomes a programmatic dependency.
+bool pdl_enabled();  // runtime.cu; off with ZG_PDL=0 in the environment
+
 #ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+static inline bool launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), "kernel launch", __FILE__, __LINE__);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() { pdl_wait(); pdl_trigger(); }
+
 // ------------------------------------------------------------- device side
 template <typename T>
 __device__ __forceinline__ T warp_sum(T v) {

@@ -45,6 +45,7 @@ template <typename TI, typename TC>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A, const TI* __restrict__ B, TC* C, const SimtParams p) {
   using AT = typename Acc<TI>::type;
   constexpr int TM = 64, TN = 64, TK = 16;
+  pdl_sync();
   __shared__ AT As[TK][TM + 1];
   __shared__ AT Bs[TK][TN + 1];
   const unsigned batch = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A
 // C[b][i][j] *= beta over an [m, n] window with leading dimension ldc
 template <typename T>
 __global__ void scale_c_kernel(T* C, size_t batches, size_t m, size_t n, size_t ldc, size_t c_stride, T beta) {
+  pdl_sync();
   const size_t total = batches * m * n, nth = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nth) {
     const size_t b = i / (m * n), r = (i % (m * n)) / n, cidx = i % n;
@@ -137,8 +139,7 @@ __global__ void scale_c_kernel(T* C, size_t batches, size_t m, size_t n, size_t 
 template <typename T>
 static void prescale_c(cudaStream_t s, T* C, size_t batches, size_t m, size_t n, size_t ldc, size_t c_stride, double beta) {
   if (beta == 1.0) return;
-  scale_c_kernel<T><<<grid_for(batches * m * n, 1024), 256, 0, s>>>(C, batches, m, n, ldc, c_stride, (T)beta);
-  ZG_LAUNCH_CHECK();
+  launch_pdl(scale_c_kernel<T>, dim3(grid_for(batches * m * n, 1024)), dim3(256), 0, s, C, batches, m, n, ldc, c_stride, (T)beta);
 }
 
 template <typename TI, typename TC>
@@ -167,8 +168,7 @@ static void launch_simt(cudaStream_t s, const void* A, const void* B, void* C, l
   }
   dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), (unsigned)(nC * splits));
   if (grid.y > 65535 || grid.z > 65535) { set_error(kBadArgument, "gemm: grid too large (m=%lu, batches=%lu)", m, nC); return; }
-  gemm_simt_kernel<TI, TC><<<grid, 256, 0, s>>>(static_cast<const TI*>(A), static_cast<const TI*>(B), static_cast<TC*>(C), p);
-  ZG_LAUNCH_CHECK();
+  launch_pdl(gemm_simt_kernel<TI, TC>, grid, dim3(256), 0, s, static_cast<const TI*>(A), static_cast<const TI*>(B), static_cast<TC*>(C), p);
 }
 
 // =====================================================================
@@ -214,8 +214,7 @@ static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensor
     if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::kTotal))) return false;
     attr_set = true;
   }
-  kern<<<grid, tc::kThreadsTc, SL::kTotal, s>>>(ta, tb, p);
-  return ZG_LAUNCH_CHECK();
+  return launch_pdl(kern, grid, dim3(tc::kThreadsTc), (size_t)SL::kTotal, s, ta, tb, p);
 }
 
 template <int MODE>
@@ -247,8 +246,7 @@ static bool launch_persistent_inst(cudaStream_t s, const CUtensorMap& ta, const 
     attr_set = true;
   }
   const unsigned grid = n_tiles < (uint32_t)sm_count() ? n_tiles : (unsigned)sm_count();
-  kern<<<grid, tc::kThreadsPersistent, SL::kTotal, s>>>(ta, tb, p, tiles_m, tiles_n, n_tiles);
-  return ZG_LAUNCH_CHECK();
+  return launch_pdl(kern, dim3(grid), dim3(tc::kThreadsPersistent), (size_t)SL::kTotal, s, ta, tb, p, tiles_m, tiles_n, n_tiles);
 }
 
 template <int MODE>

@@ -118,6 +118,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_sync();  // everything above overlaps the previous kernel's tail
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer

@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
   const int lane = threadIdx.x & 31;
   const int C = a.C;
   const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  pdl_sync();
   float loss_acc = 0.f;
   float bias_acc[ITEMS];
 #pragma unroll
@@ -332,6 +333,7 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceA
   const bool block_rows = a.ld <= (size_t)kRowMaxW;  // rows and their padding form one contiguous block
   const int W = block_rows ? (int)a.ld : C;
   const int S = W | 1, ST = C | 1;
+  pdl_sync();
   float gacc[P2];
 #pragma unroll
   for (int j = 0; j < P2; ++j) gacc[j] = 0.f;
@@ -554,8 +556,7 @@ static void launch_smce_rows(cudaStream_t s, SmceArgs a) {
   a.partial = partial;
   a.counter = counters;
   a.fold_bias_inline = 1;
-  softmax_ce_row_kernel<CP, IDX, FAST><<<gr, kRowThreads, 0, s>>>(a);
-  ZG_LAUNCH_CHECK();
+  launch_pdl(softmax_ce_row_kernel<CP, IDX, FAST>, dim3(gr), dim3(kRowThreads), 0, s, a);
 }
 
 template <int ITEMS, int ROWS, bool IDX, bool FAST>
@@ -574,8 +575,7 @@ static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
   a.partial = partial;
   a.counter = counters;
   a.fold_bias_inline = separate_fold ? 0 : 1;
-  softmax_ce_kernel<ITEMS, ROWS, IDX, FAST><<<g, kLThreads, 0, s>>>(a);
-  if (!ZG_LAUNCH_CHECK()) return;
+  if (!launch_pdl(softmax_ce_kernel<ITEMS, ROWS, IDX, FAST>, dim3(g), dim3(kLThreads), 0, s, a)) return;
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
 

@@ -30,6 +30,7 @@ __device__ __forceinline__ bool same_phase(const void* a, const void* b) {
 __global__ void __launch_bounds__(kOThreads) seg_nrm2_kernel(const float* __restrict__ g, const __grid_constant__ SegTable tab,
                                                              float* norms, double* partial, unsigned* counters) {
   __shared__ double sm[32];
+  pdl_sync();
   const int seg = blockIdx.y;
   const float* p = g + tab.offset[seg];
   const size_t n = tab.len[seg];
@@ -85,6 +86,7 @@ __device__ __forceinline__ float clip_factor(const float* norms, int idx, float 
 template <bool CLIP>
 __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* grads, const __grid_constant__ SegTable tab, float nlr,
                                                         const float* __restrict__ norms, float max_norm, float delta) {
+  pdl_sync();
   const int seg = blockIdx.y;
   float* p = params + tab.offset[seg];
   float* g = grads + tab.offset[seg];
@@ -135,6 +137,7 @@ template <bool CLIP, bool BF16COPY>
 __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* grads, float* ms, float* vs, const __grid_constant__ SegTable tab,
                                                          float b1, float b2, float eps, const float* __restrict__ norms, float max_norm,
                                                          float delta, __nv_bfloat16* copy, const unsigned long long* t_dev, float lr) {
+  pdl_sync();
   const int seg = blockIdx.y;
   const size_t off = tab.offset[seg];
   float* p = params + off;
@@ -199,7 +202,10 @@ __global__ void __launch_bounds__(kOThreads) adam_kernel(float* params, float* g
   for (size_t i = head + nv * 4 + tid; i < n; i += nth) scalar(i);
 }
 
-__global__ void counter_add_kernel(unsigned long long* c, unsigned long long inc) { *c += inc; }
+__global__ void counter_add_kernel(unsigned long long* c, unsigned long long inc) {
+  pdl_sync();
+  *c += inc;
+}
 
 static unsigned chunks_for(const zg_segment* seg, size_t n_seg) {
   size_t mx = 0;
@@ -224,8 +230,7 @@ static bool compute_norms(cudaStream_t s, const float* grads, const zg_segment* 
     unsigned* counters = nullptr;
     double* partial = static_cast<double*>(workspace(s, sizeof(double) * chunks * tab.n, &counters));
     if (!partial) return false;
-    seg_nrm2_kernel<<<dim3(chunks, tab.n), kOThreads, 0, s>>>(grads, tab, norms, partial, counters);
-    if (!ZG_LAUNCH_CHECK()) return false;
+    if (!launch_pdl(seg_nrm2_kernel, dim3(chunks, tab.n), dim3(kOThreads), 0, s, grads, tab, norms, partial, counters)) return false;
   }
   return true;
 }
@@ -248,9 +253,8 @@ extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads
     tab.first = (int)first;
     for (int j = 0; j < tab.n; ++j) { tab.offset[j] = seg[first + j].offset; tab.len[j] = seg[first + j].len; }
     const dim3 grid(chunks_for(seg + first, tab.n), tab.n);
-    if (clip) sgd_kernel<true><<<grid, kOThreads, 0, s>>>((float*)params, (float*)grads, tab, nlr, (const float*)norms, (float)max_norm, (float)delta);
-    else sgd_kernel<false><<<grid, kOThreads, 0, s>>>((float*)params, (float*)grads, tab, nlr, nullptr, 0.f, 0.f);
-    ZG_LAUNCH_CHECK();
+    if (clip) launch_pdl(sgd_kernel<true>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)norms, (float)max_norm, (float)delta);
+    else launch_pdl(sgd_kernel<false>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)nullptr, 0.f, 0.f);
   }
 }
 
@@ -277,14 +281,15 @@ extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grad
     const dim3 grid(chunks_for(seg + first, tab.n), tab.n);
     float* P = (float*)params; float* G = (float*)grads; float* M = (float*)m; float* V = (float*)v;
     __nv_bfloat16* cp = (__nv_bfloat16*)bf16_copy;
-    if (clip && cp) adam_kernel<true, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, cp, TD, lr);
-    else if (clip) adam_kernel<true, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, (const float*)norms, (float)max_norm, (float)delta, nullptr, TD, lr);
-    else if (cp) adam_kernel<false, true><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, cp, TD, lr);
-    else adam_kernel<false, false><<<grid, kOThreads, 0, s>>>(P, G, M, V, tab, beta1, beta2, eps, nullptr, 0.f, 0.f, nullptr, TD, lr);
-    ZG_LAUNCH_CHECK();
+    const float* NR = (const float*)norms;
+    __nv_bfloat16* no_copy = nullptr;
+    const dim3 blk(kOThreads);
+    if (clip && cp) launch_pdl(adam_kernel<true, true>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, NR, (float)max_norm, (float)delta, cp, TD, lr);
+    else if (clip) launch_pdl(adam_kernel<true, false>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, NR, (float)max_norm, (float)delta, no_copy, TD, lr);
+    else if (cp) launch_pdl(adam_kernel<false, true>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, (const float*)nullptr, 0.f, 0.f, cp, TD, lr);
+    else launch_pdl(adam_kernel<false, false>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, (const float*)nullptr, 0.f, 0.f, no_copy, TD, lr);
   }
   if (step_counter) {  // advance the device counter once per tensor, after every update kernel has read it
-    counter_add_kernel<<<1, 1, 0, s>>>(static_cast<unsigned long long*>(step_counter), (unsigned long long)n_seg);
-    ZG_LAUNCH_CHECK();
+    launch_pdl(counter_add_kernel, dim3(1), dim3(1), 0, s, static_cast<unsigned long long*>(step_counter), (unsigned long long)n_seg);
   }
 }

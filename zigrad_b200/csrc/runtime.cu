@@ -2,6 +2,7 @@
 // (include/cuda_utils.h) and the sticky error status (include/zg_b200.h).
 #include <cmath>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -74,6 +75,7 @@ void* driver_symbol(const char* name) {
 // --------------------------------------------------------- fill / sequence
 template <typename T>
 __global__ void fill_kernel(T* __restrict__ p, size_t n, T v) {
+  pdl_sync();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if constexpr (sizeof(T) == 4) {
@@ -166,6 +168,14 @@ struct Workspace {
 };
 static std::mutex g_ws_mu;
 static std::map<std::pair<std::pair<int, int>, cudaStream_t>, Workspace> g_ws;
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ZG_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot) {
   int dev = 0;
@@ -293,6 +303,30 @@ extern "C" StreamWrapper init_stream(void) {
 extern "C" void deinit_stream(StreamWrapper stream) {
   if (stream.ptr) ZG_CUDA(cudaStreamDestroy(as_stream(stream)));
 }
+extern "C" void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller) {
+  // events come from a ring that lives as long as the process: a wait only
+  // needs its event until the wait has been enqueued (or captured)
+  static std::mutex mu;
+  static cudaEvent_t ring[64][32];
+  static bool made[64] = {false};
+  static unsigned next[64] = {0};
+  int dev = 0;
+  if (!ZG_CUDA(cudaGetDevice(&dev))) return;
+  if (dev < 0 || dev >= 64) { set_error(kBadArgument, "zg_stream_wait: device ordinal %d out of range", dev); return; }
+  cudaEvent_t ev;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!made[dev]) {
+      for (int i = 0; i < 32; ++i)
+        if (!ZG_CUDA(cudaEventCreateWithFlags(&ring[dev][i], cudaEventDisableTiming))) return;
+      made[dev] = true;
+    }
+    ev = ring[dev][next[dev]++ % 32];
+  }
+  if (!ZG_CUDA(cudaEventRecord(ev, as_stream(signaller)))) return;
+  ZG_CUDA(cudaStreamWaitEvent(as_stream(waiter), ev, 0));
+}
+
 extern "C" void stream_synchronize(StreamWrapper stream) {
   if (ZG_CUDA(cudaStreamSynchronize(as_stream(stream)))) check_tc_errors();
 }
@@ -377,15 +411,17 @@ extern "C" void mem_fill(dtype id, void* data, len_t n, const void* value, Strea
   if (id == SINGLE) {
     float v;
     memcpy(&v, value, 4);
-    if (v == 0.f && !std::signbit(v)) {  // zero fill: let the copy engine / memset path do it
+    // zero fill of a large buffer: the memset path; small ones stay kernels so
+    // that a captured step is an unbroken chain of kernel nodes
+    if (v == 0.f && !std::signbit(v) && n > ((size_t)1 << 22)) {
       ZG_CUDA(cudaMemsetAsync(data, 0, n * 4, s));
       return;
     }
-    fill_kernel<float><<<grid_for(n, 256 * 16), 256, 0, s>>>(static_cast<float*>(data), n, v);
+    launch_pdl(fill_kernel<float>, dim3(grid_for(n, 256 * 4)), dim3(256), 0, s, static_cast<float*>(data), (size_t)n, v);
   } else if (id == DOUBLE) {
     double v;
     memcpy(&v, value, 8);
-    fill_kernel<double><<<grid_for(n, 256 * 8), 256, 0, s>>>(static_cast<double*>(data), n, v);
+    launch_pdl(fill_kernel<double>, dim3(grid_for(n, 256 * 8)), dim3(256), 0, s, static_cast<double*>(data), (size_t)n, v);
   } else {
     set_error(kUnsupported, "mem_fill: unsupported dtype %d", (int)id);
     return;

@@ -9,6 +9,8 @@ other implementation behind it: without the library or without a GPU it raises.
 """
 from __future__ import annotations
 
+import contextlib
+
 import ctypes as C
 from dataclasses import dataclass
 from typing import Optional, Sequence
@@ -128,6 +130,7 @@ class CudaDevice:
         self.cutensor = self.L.init_cutensor_handle(self.stream)
         self.cache = self.L.zg_cache_create(self.device_number, cache_max_bytes)
         self.capture = ExecutionGraph(self)
+        self._side = None  # second stream for branches of independent work, created on first use
         abi.check()
 
     # ------------------------------------------------------------ lifecycle
@@ -140,6 +143,9 @@ class CudaDevice:
         self.L.deinit_cudnn_handle(self.cudnn)
         self.L.deinit_cublas_handle(self.cublas)
         self.L.deinit_cutensor_handle(self.cutensor)
+        if self._side is not None:
+            self.L.deinit_stream(self._side)
+            self._side = None
         if self._own_stream:
             self.L.deinit_stream(self.stream)
         self.L = None
@@ -156,6 +162,26 @@ class CudaDevice:
 
     def make_current(self):
         self.L.zg_set_device(self.device_number)
+
+    @contextlib.contextmanager
+    def branch(self):
+        """Ops issued inside the block go to the device's side stream, ordered
+        after everything issued so far on the main stream; they may overlap what
+        the main stream runs next.  `join()` makes the main stream wait for them
+        (required before the results are used and before a capture is saved)."""
+        if self._side is None:
+            self._side = self.L.init_stream()
+        main = self.stream
+        self.L.zg_stream_wait(self._side, main)
+        self.stream = self._side
+        try:
+            yield
+        finally:
+            self.stream = main
+
+    def join(self):
+        if self._side is not None:
+            self.L.zg_stream_wait(self.stream, self._side)
 
     # --------------------------------------------------------------- memory
     def mem_cache_alloc(self, dtype: int, n: int) -> DeviceSlice:

@@ -164,11 +164,15 @@ class MlpTrainer:
                 # bias gradients: db[L-1] came out of the loss kernel; db[l-1] is the
                 # column sum of the masked dX that this layer's dX GEMM stores
                 # (added by its epilogue into the zero-filled gradient buffer)
+                # The weight gradient does not feed the dX chain: it goes to the side
+                # stream (a parallel branch of a captured step), forked here where dY
+                # is ready, and runs next to this layer's dX GEMM.
+                with d.branch():
+                    d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, ldy, K, K, 1.0, 1.0))
                 if l > 0:  # dX = dY . W, zeroed where the previous activation is <= 0
                     W = self.Wb[l] if self.bf16 else self.W[l]
                     d.dispatch(opspec.linear(dy, W, self.dact[l - 1], B, K, N, False, False, ldy, K, K, 1.0, 0.0,
                                              "relu_mask", None, self.act[l - 1], colsum=self.db[l - 1]))
-                d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, ldy, K, K, 1.0, 1.0))
             else:
                 if l + 1 < self.L:
                     d.dispatch(opspec.relu_inplace_bwd(self.act[l], dy))
@@ -179,6 +183,8 @@ class MlpTrainer:
                     d.dispatch(opspec.bmm_acc(dy, self.W[l], self.dact[l - 1], (1, B, N), (1, N, K), (1, B, K), False, False, N, K, K, 1.0, 1.0))
                 d.mem_fill(self.dW[l], 0.0)
                 d.dispatch(opspec.bmm_acc(dy, a_in, self.dW[l], (1, N, B), (1, B, K), (1, N, K), True, False, N, K, K, 1.0, 1.0))
+        if self.fused:
+            d.join()  # the weight gradients are complete before anything that follows on the main stream
 
     def update(self):
         d = self.dev
