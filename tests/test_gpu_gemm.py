@@ -100,7 +100,7 @@ def test_bmm_batch_broadcast(gpu, mode):
 
 
 @pytest.mark.parametrize("mode", ["ffma", "fp32x3"])
-@pytest.mark.parametrize("m,n,k", [(64, 128, 784), (1024, 64, 128), (1024, 10, 64), (33, 17, 9)])
+@pytest.mark.parametrize("m,n,k", [(64, 128, 784), (1024, 64, 128), (1024, 10, 64), (33, 17, 9), (2708, 16, 2708), (200, 100, 3000)])
 def test_linear_fused_epilogues_equal_separate_ops(gpu, mode, m, n, k):
     """bias / bias+ReLU / ReLU-mask epilogues against the reference's separate
     device calls (bmm_acc, add, relu_fwd; relu_inplace_bwd) run by the oracle."""
@@ -130,7 +130,7 @@ def test_linear_fused_epilogues_equal_separate_ops(gpu, mode, m, n, k):
 
 
 @pytest.mark.parametrize("mode", ["ffma", "fp32x3"])
-@pytest.mark.parametrize("m,n,k", [(8192, 128, 64), (1024, 64, 12), (300, 100, 40), (33, 17, 9)])
+@pytest.mark.parametrize("m,n,k", [(8192, 128, 64), (1024, 64, 12), (300, 100, 40), (33, 17, 9), (300, 100, 2048), (2708, 16, 1536)])
 def test_gemm_epilogue_column_sums_are_the_bias_gradient(gpu, mode, m, n, k):
     """dX GEMM with the ReLU mask AND the column sums of what it stores, added to
     a pre-existing vector: equals relu_inplace_bwd followed by unbroadcast

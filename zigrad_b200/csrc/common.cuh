@@ -48,6 +48,8 @@ int sm_count();  // SMs of the current device (cached)
 // Per-stream scratch owned by the library (runtime.cu).  Returns a 256-byte
 // aligned buffer of at least `bytes`; *counters points at 64 zero-initialised
 // unsigned counters that a kernel must leave at zero when it finishes.
+// Slots 0 and 1 are scratch; slot 2 is zero when handed out and every kernel
+// that uses it leaves it zero (arrival counters of multi-CTA reductions).
 void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot = 0);
 
 // y[col] = column sums of x[row, col] (fp32, two-stage, deterministic; uses workspace slot 0)

@@ -62,26 +62,38 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ A
   const size_t kb = split * p.k_per_split;
   size_t ke = kb + p.k_per_split;
   if (ke > p.k) ke = p.k;
-  for (size_t k0 = kb; k0 < ke; k0 += TK) {
-    // cooperative loads: 1024 elements per operand slab, 4 per thread; the
-    // fastest-varying thread index follows the contiguous dimension in memory
-    for (int e = threadIdx.x; e < TM * TK; e += 256) {
+  // Cooperative loads: 1024 elements per operand slab, 4 per thread; the
+  // fastest-varying thread index follows the contiguous dimension in memory.
+  // The next slab is fetched into registers while the current one is being
+  // multiplied, so a trip costs the arithmetic, not a round trip to memory.
+  AT ar[4], br[4];
+  auto fetch = [&](size_t k0) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = threadIdx.x + q * 256;
       int mm, kk;
       if (p.ta) { mm = e % TM; kk = e / TM; } else { kk = e % TK; mm = e / TK; }
       const size_t gm = m0 + mm, gk = k0 + kk;
-      AT v = AT(0);
-      if (gm < p.m && gk < ke) v = to_acc<TI>(p.ta ? a[gk * p.lda + gm] : a[gm * p.lda + gk]);
-      As[kk][mm] = v;
-    }
-    for (int e = threadIdx.x; e < TN * TK; e += 256) {
-      int nn, kk;
+      ar[q] = (gm < p.m && gk < ke) ? to_acc<TI>(p.ta ? a[gk * p.lda + gm] : a[gm * p.lda + gk]) : AT(0);
+      int nn;
       if (p.tb) { kk = e % TK; nn = e / TK; } else { nn = e % TN; kk = e / TN; }
-      const size_t gn = n0 + nn, gk = k0 + kk;
-      AT v = AT(0);
-      if (gn < p.n && gk < ke) v = to_acc<TI>(p.tb ? b[gn * p.ldb + gk] : b[gk * p.ldb + gn]);
-      Bs[kk][nn] = v;
+      const size_t gn = n0 + nn, gk2 = k0 + kk;
+      br[q] = (gn < p.n && gk2 < ke) ? to_acc<TI>(p.tb ? b[gn * p.ldb + gk2] : b[gk2 * p.ldb + gn]) : AT(0);
+    }
+  };
+  if (kb < ke) fetch(kb);
+  for (size_t k0 = kb; k0 < ke; k0 += TK) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = threadIdx.x + q * 256;
+      int mm, kk, nn;
+      if (p.ta) { mm = e % TM; kk = e / TM; } else { kk = e % TK; mm = e / TK; }
+      As[kk][mm] = ar[q];
+      if (p.tb) { kk = e % TK; nn = e / TK; } else { nn = e % TN; kk = e / TN; }
+      Bs[kk][nn] = br[q];
     }
     __syncthreads();
+    if (k0 + TK < ke) fetch(k0 + TK);
 #pragma unroll
     for (int kk = 0; kk < TK; ++kk) {
       AT av[4], bv[4];
@@ -155,9 +167,9 @@ static void launch_simt(cudaStream_t s, const void* A, const void* B, void* C, l
   const size_t tiles = ((m + 63) / 64) * ((n + 63) / 64) * nC;
   unsigned splits = 1;
   // deep-k, few-tile problems (weight gradients): split K over more CTAs
-  if (epilogue == ZG_EPI_NONE && !colsum && sizeof(TC) >= 4 && k >= 1024 && tiles * 2 <= (size_t)sm_count()) {
+  if (epilogue == ZG_EPI_NONE && !colsum && sizeof(TC) >= 4 && k >= 128 && tiles * 2 <= (size_t)sm_count()) {
     size_t want = (size_t)sm_count() * 2 / tiles;
-    size_t maxs = k / 256;
+    size_t maxs = k / 32;  // at least two 16-deep slabs per split
     splits = (unsigned)(want < maxs ? want : maxs);
     if (splits < 1) splits = 1;
   }
@@ -292,7 +304,10 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   // parallelism from K splits, so they keep the wide tile (fewer operand bytes
   // per flop through shared memory); everything else halves BN when there are
   // too few tiles to occupy the SMs.
-  const bool can_split = !persistent && epilogue == ZG_EPI_NONE && !colsum && c_id == SINGLE && k >= 1024;
+  // (with a fused epilogue or column sums the last CTA of a tile applies them to the finished sums)
+  // and that costs a second pass over the tile, so it is kept for problems with very few tiles)
+  const bool deferred = epilogue != ZG_EPI_NONE || colsum;
+  const bool can_split = !persistent && c_id == SINGLE && k >= 512 && (!deferred || tiles * 4 <= (size_t)sm_count());
   if (!can_split && bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) {
     bn = 64;
     tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
@@ -357,6 +372,15 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
     return true;
   }
   if (splits > 1) prescale_c<float>(s, static_cast<float*>(C), nC, m, n, ldc, m * ldc, beta);
+  if (splits > 1 && deferred) {
+    unsigned* unused = nullptr;
+    p.tile_tickets = static_cast<unsigned*>(workspace(s, sizeof(unsigned) * tiles, &unused, 2));
+    if (!p.tile_tickets) return true;
+    p.deferred_epilogue = epilogue;
+    p.deferred_colsum = p.colsum;
+    p.epilogue = ZG_EPI_NONE;
+    p.colsum = nullptr;
+  }
   dim3 grid((unsigned)((n + bn - 1) / bn), (unsigned)((m + 127) / 128), (unsigned)(nC * splits));
   if (grid.y > 65535 || grid.z > 65535) return false;
   if (mode == tc::kBF16) launch_tc_mode<tc::kBF16>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);

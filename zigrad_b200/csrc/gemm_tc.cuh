@@ -69,6 +69,14 @@ struct Params {
   int epilogue;
   int vec_ok;           // C (and mask, bias) rows allow 16-byte accesses at every 32-column boundary
   int* error_flag;      // set to 1 when a bounded wait ran out
+  // Split-K with a fused epilogue: the partial products are added into C (which
+  // the launcher scaled by beta first) with the epilogue switched off; every CTA
+  // then takes a ticket of its tile, and the one that draws the last applies
+  // bias / ReLU / mask / column sums to the finished sums.  One counter per
+  // output tile, zero before and after the launch.
+  unsigned* tile_tickets;
+  int deferred_epilogue;  // what to apply at the end (epilogue is NONE and colsum NULL during accumulation)
+  float* deferred_colsum;
 };
 
 // ------------------------------------------------------------------ PTX
@@ -527,6 +535,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
         epilogue_chunk(p, r, row_ok, c_off + col0, col0, lane);
+      }
+      if (p.tile_tickets) {
+        // ---- deferred epilogue of a split-K tile (warps 4-7 only: named barrier 1)
+        __shared__ int is_last;
+        __threadfence();  // this thread's reductions into C are visible device-wide
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 128) {
+          unsigned* ticket = p.tile_tickets + ((size_t)batch * gridDim.y + tile_m) * gridDim.x + tile_n;
+          const unsigned t = atomicAdd(ticket, 1u);
+          is_last = (t == p.splits - 1) ? 1 : 0;
+          if (is_last) *ticket = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (is_last) {
+          __threadfence();
+          Params q = p;
+          q.alpha = 1.f; q.beta = 0.f; q.splits = 1; q.epilogue = p.deferred_epilogue; q.colsum = p.deferred_colsum;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const uint32_t col0 = tile_n * BN + c * 32;
+            if (col0 >= p.n) break;
+            uint32_t r[32];
+            const uint64_t o = c_off + col0;
+            if (row_ok && p.vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(p.C + o) + j);
+                r[4 * j] = __float_as_uint(v.x); r[4 * j + 1] = __float_as_uint(v.y);
+                r[4 * j + 2] = __float_as_uint(v.z); r[4 * j + 3] = __float_as_uint(v.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = (row_ok && col0 + j < p.n) ? __float_as_uint(__ldcg(p.C + o + j)) : 0u;
+            }
+            epilogue_chunk(q, r, row_ok, o, col0, lane);
+          }
+        }
       }
     }
   }

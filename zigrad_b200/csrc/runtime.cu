@@ -194,7 +194,7 @@ void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot) {
     }
     void* p = nullptr;
     if (!ZG_CUDA(cudaMalloc(&p, cap))) return nullptr;
-    if (!ZG_CUDA(cudaMemset(p, 0, 256))) return nullptr;
+    if (!ZG_CUDA(cudaMemset(p, 0, cap))) return nullptr;  // counters (and slot 2, which its users keep at zero) start cleared
     if (w.base) {
       cudaStreamSynchronize(s);  // earlier kernels may still read the old buffer
       cudaFree(w.base);
