@@ -2,6 +2,7 @@
 repository root covers the headline one, the batch-8192 MLP).
 
     python -m zigrad_b200.configs_bench [--configs c1,c3,c4,c5] [--no-cpu]
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m zigrad_b200.configs_bench --dp
 
   c1  MLP 784-128-64-10, batch 64, fp32 (3xTF32), SGD           -> samples/s, us/step
   c3  MLP 4096-4096-4096-4096-1000, bf16 + fp32 master, Adam, one GPU's 8192-row
@@ -147,11 +148,90 @@ def run(configs, cpu=True, reps=200):
     return out
 
 
+def run_c3_dp(steps=20, warmup=5):
+    """Config c3 data-parallel: one process per GPU (torchrun), 8192 rows per
+    GPU (the global batch of 65536 at 8 GPUs; weak scaling below that), the
+    gradient of each layer all-reduced over NCCL as soon as its weight-gradient
+    GEMM has been issued, Adam after the last reduction.  Eager launches (17
+    kernels of ~0.1 ms each per step).  Rank 0 prints one JSON line; the time
+    is the maximum over ranks of the CUDA-event time of `steps` steps."""
+    import torch
+    import torch.distributed as dist
+    from .abi import BF16
+    from .device import CudaDevice
+    from .dp import OverlappedGradAllReduce
+    from .mlp import MlpTrainer, kaiming_uniform
+
+    rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ts = torch.cuda.Stream()
+    dev = CudaDevice(local, stream=ts.cuda_stream)
+    with dev.branch():
+        pass
+    side = torch.cuda.ExternalStream(dev._side.ptr)
+    dims, B = [4096, 4096, 4096, 4096, 1000], 8192
+    Ws, bs = kaiming_uniform(dims, 5)  # same seed on every rank: replicated parameters
+    g = np.random.Generator(np.random.PCG64(100 + rank))
+    X = g.standard_normal((B, dims[0])).astype(np.float32)
+    lab = g.integers(0, 1000, B).astype(np.uint64)
+    tr = MlpTrainer(dev, dims, B, Ws, bs, "adam", lr=1e-3, clip=True, bf16=True, loss_div=B * world)
+    xf = dev.from_numpy(X)
+    Xd = dev.mem_cache_alloc(BF16, X.size)
+    dev.cast(xf, Xd)
+    Td = dev.from_numpy(lab)
+    red = OverlappedGradAllReduce() if world > 1 else None
+
+    def step():
+        tr.forward(Xd)
+        tr.loss_and_grad(Td)
+        tr.backward(Xd, on_layer_grads=(lambda l: red.start(tr.layer_grads(l), side)) if red else None)
+        if red:
+            red.finish(ts)
+        tr.update()
+
+    def barrier():
+        dev.sync()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ts)
+    for _ in range(steps):
+        step()
+    e1.record(ts)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    loss = tr.read_loss()
+    if rank == 0:
+        us = ms * 1e3 / steps
+        print(json.dumps({"config": "c3 data-parallel, bf16 + fp32 master, Adam, per-layer NCCL all-reduce overlapped with backward",
+                          "n_gpus": world, "global_batch": B * world, "us_per_step": us, "samples_per_s": B * world / us * 1e6,
+                          "TFLOPs_per_gpu": 293011456.0 * B / us * 1e-6, "allreduce_bytes_per_step": 4 * tr.n_params,
+                          "loss": loss, "scaling": "weak"}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c3,c4,c5")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--reps", type=int, default=200, help="graph replays per timing")
+    ap.add_argument("--dp", action="store_true", help="config c3 data-parallel under torchrun (one process per GPU)")
     a = ap.parse_args()
+    if a.dp:
+        run_c3_dp()
+        raise SystemExit(0)
     for r in run(a.configs.split(","), cpu=not a.no_cpu, reps=a.reps):
         print(json.dumps(r), flush=True)

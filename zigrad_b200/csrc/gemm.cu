@@ -258,7 +258,11 @@ static bool launch_persistent_inst(cudaStream_t s, const CUtensorMap& ta, const 
     attr_set = true;
   }
   const unsigned grid = n_tiles < (uint32_t)sm_count() ? n_tiles : (unsigned)sm_count();
-  return launch_pdl(kern, dim3(grid), dim3(tc::kThreadsPersistent), (size_t)SL::kTotal, s, ta, tb, p, tiles_m, tiles_n, n_tiles);
+  // work-item counter: zero between launches (slot 2 of the stream's workspace)
+  unsigned* unused = nullptr;
+  unsigned* counter = static_cast<unsigned*>(workspace(s, 256, &unused, 2));
+  if (!counter) return false;
+  return launch_pdl(kern, dim3(grid), dim3(tc::kThreadsPersistent), (size_t)SL::kTotal, s, ta, tb, p, tiles_m, tiles_n, n_tiles, counter);
 }
 
 template <int MODE>

@@ -11,7 +11,13 @@
 //   * set-up (barriers, TMEM allocation, descriptor prefetch) is paid once per
 //     SM instead of once per tile.
 // Tiles are visited in groups of kGroupM row-tiles x all column-tiles so that
-// the CTAs running at the same time share operand slabs in L2.
+// the CTAs running at the same time share operand slabs in L2.  The schedule
+// is dynamic: the producer thread draws the next work item from a counter in
+// global memory and hands it to the other roles through a small ring in
+// shared memory, so a CTA that starts late (SMs held by a kernel of another
+// stream, e.g. a collective) simply finds less work left instead of delaying
+// a fixed share of the tiles.  The CTA that draws the last ticket of the
+// launch (n_items + gridDim.x - 1) resets the counter for the next launch.
 //
 // K may be split (weight gradients: fp32 C, no fused epilogue): a work item is
 // then one K range of one tile and its epilogue adds into C with vector
@@ -35,6 +41,8 @@ constexpr int kPBN = 256;      // tile width
 constexpr int kGroupM = 16;    // row-tiles per scheduling group
 constexpr int kThreadsPersistent = 384;
 constexpr int kEpiThreads = kThreadsPersistent - 128;
+constexpr int kSchedDepth = 4;                  // work items in flight between the roles
+constexpr uint32_t kNoTile = 0xFFFFFFFFu;       // end of work
 
 template <int MODE>
 struct PersistentSmem {
@@ -43,7 +51,7 @@ struct PersistentSmem {
   static constexpr int kBBytes = kPBN * kSlabBytes;   // 32 KB
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = 4;
-  static constexpr int kTotal = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kTotal = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 struct TileCoord { uint32_t m, n, batch, split; };
@@ -68,7 +76,7 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, ui
 template <bool A_KMAJOR, bool B_KMAJOR, int MODE>
 __global__ void __launch_bounds__(kThreadsPersistent, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
-                          const uint32_t tiles_m, const uint32_t tiles_n, const uint32_t n_tiles) {
+                          const uint32_t tiles_m, const uint32_t tiles_n, const uint32_t n_tiles, unsigned* sched_counter) {
   static_assert(MODE == kBF16 || MODE == kTF32, "the persistent kernel has no operand-split warps");
   using MT = ModeTraits<MODE>;
   using SL = PersistentSmem<MODE>;
@@ -84,6 +92,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   uint64_t* empty = bars + S;            // [S] MMAs that read the stage retired
   uint64_t* acc_full = bars + 2 * S;     // [2] accumulator complete
   uint64_t* acc_empty = bars + 2 * S + 2;  // [2] accumulator drained by the epilogue
+  uint64_t* sched_full = bars + 2 * S + 4;                 // [kSchedDepth] work item published
+  uint64_t* sched_empty = bars + 2 * S + 4 + kSchedDepth;  // [kSchedDepth] read by the MMA thread and every epilogue warp
+  __shared__ uint32_t sched_tile[kSchedDepth];
   __shared__ uint32_t tmem_base_slot;
   __shared__ volatile int failed;
 
@@ -106,6 +117,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], kEpiThreads);  // every epilogue thread arrives
     }
+    for (int j = 0; j < kSchedDepth; ++j) {
+      mbar_init(&sched_full[j], 1);
+      mbar_init(&sched_empty[j], 1 + kEpiThreads / 32);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -125,7 +140,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (lane == 0) {
       uint32_t it = 0;  // k-slabs issued so far (ring position)
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+      for (uint32_t i = 0; ok; ++i) {
+        const int j = (int)(i % kSchedDepth);
+        if (i >= (uint32_t)kSchedDepth && !mbar_wait(&sched_empty[j], ((i / kSchedDepth) & 1) ^ 1, &failed)) break;
+        uint32_t t = atomicAdd(sched_counter, 1u);
+        if (t == n_tiles + gridDim.x - 1) atomicExch(sched_counter, 0u);  // the last draw of the launch
+        if (t >= n_tiles) t = kNoTile;
+        sched_tile[j] = t;
+        mbar_arrive(&sched_full[j]);
+        if (t == kNoTile) break;
         const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.splits);
         const int za = (int)(tc.batch % p.nA), zb = (int)(tc.batch % p.nB);
         const int KT = slabs_of(tc.split);
@@ -159,7 +182,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++tcount) {
+      for (; ok; ++tcount) {
+        const int j = (int)(tcount % kSchedDepth);
+        if (!mbar_wait(&sched_full[j], (tcount / kSchedDepth) & 1, &failed)) break;
+        const uint32_t t = sched_tile[j];
+        mbar_arrive(&sched_empty[j]);
+        if (t == kNoTile) break;
         const uint32_t buf = tcount & 1;
         if (tcount >= 2 && !mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1) ^ 1, &failed)) break;
         tc_fence_after();
@@ -191,7 +219,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3, group = (warp - 4) >> 2;
     uint32_t tcount = 0;
-    for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tcount) {
+    for (;; ++tcount) {
+      const int j = (int)(tcount % kSchedDepth);
+      if (!mbar_wait(&sched_full[j], (tcount / kSchedDepth) & 1, &failed)) break;
+      const uint32_t t = sched_tile[j];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sched_empty[j]);
+      if (t == kNoTile) break;
       const uint32_t buf = tcount & 1;
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.splits);
       const int KT = slabs_of(tc.split);

@@ -63,3 +63,37 @@ class GradAllReduce:
             self._views[key] = t
         with torch.cuda.stream(torch_stream):
             self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+
+
+class OverlappedGradAllReduce:
+    """Per-layer all-reduce that overlaps the backward pass.
+
+    `start(slice, stream)` enqueues an asynchronous sum-all-reduce of one slice
+    of the gradient buffer, ordered after the work already on `stream` (the
+    device's side stream, where the layer's weight gradient was just issued);
+    the collective runs on the communication library's own stream, so neither
+    the side stream nor the main stream waits for it.  `finish(main_stream)`
+    makes the main stream wait for every started reduction -- call it before
+    the optimizer kernel."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self._views, self._pending = {}, []
+
+    def start(self, grads, torch_stream) -> None:
+        import torch
+        key = (grads.ptr, grads.len)
+        t = self._views.get(key)
+        if t is None:
+            t = torch.as_tensor(_CudaView(grads.ptr, grads.len, "<f4"), device=torch_stream.device)
+            self._views[key] = t
+        with torch.cuda.stream(torch_stream):
+            self._pending.append(self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self, torch_stream) -> None:
+        import torch
+        with torch.cuda.stream(torch_stream):
+            for w in self._pending:
+                w.wait()
+        self._pending = []

@@ -142,10 +142,14 @@ class MlpTrainer:
         else:
             d.dispatch(opspec.softmax_ce(self.act[-1], T, B, C, self.loss, self.dact[-1], self.loss_div, accumulate=True))
 
-    def backward(self, X: DeviceSlice, last_bias_done: bool = True):
+    def backward(self, X: DeviceSlice, last_bias_done: bool = True, on_layer_grads: Optional[Callable[[int], None]] = None):
         """Backward from dact[L-1].  `last_bias_done`: the bias gradient of the last
         layer was already produced by the loss kernel (fused path); pass False when
-        dact[L-1] comes from elsewhere (e.g. the DQN's gather backward)."""
+        dact[L-1] comes from elsewhere (e.g. the DQN's gather backward).
+        `on_layer_grads(l)` (fused path) is called on the side stream right after
+        layer l's weight gradient has been issued there -- dW[l] and db[l] are then
+        final in stream order, so a data-parallel caller can start reducing that
+        layer's slice of the gradient buffer while the backward pass goes on."""
         d, B = self.dev, self.B
         if self.fused and not last_bias_done:
             if self.ld_out != self.dims[-1]:
@@ -169,6 +173,8 @@ class MlpTrainer:
                 # is ready, and runs next to this layer's dX GEMM.
                 with d.branch():
                     d.dispatch(opspec.linear(dy, a_in, self.dW[l], N, K, B, True, False, ldy, K, K, 1.0, 1.0))
+                    if on_layer_grads is not None:
+                        on_layer_grads(l)
                 if l > 0:  # dX = dY . W, zeroed where the previous activation is <= 0
                     W = self.Wb[l] if self.bf16 else self.W[l]
                     d.dispatch(opspec.linear(dy, W, self.dact[l - 1], B, K, N, False, False, ldy, K, K, 1.0, 0.0,
@@ -199,6 +205,11 @@ class MlpTrainer:
             raise ValueError(self.opt)
 
     # -------------------------------------------------------------------- step
+    def layer_grads(self, l: int) -> DeviceSlice:
+        """The contiguous slice [dW_l ; db_l] of the flat gradient buffer."""
+        off = self.segments[2 * l][0]
+        return self.grads.view(off, self.segments[2 * l][1] + self.segments[2 * l + 1][1])
+
     def step(self, X: DeviceSlice, T: DeviceSlice, allreduce: Optional[Callable[[DeviceSlice], None]] = None):
         """forward + loss + backward [+ gradient all-reduce] + update, all
         asynchronous on the device stream.  The loss stays in ``self.loss``."""
