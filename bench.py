@@ -160,7 +160,7 @@ def run_gpu(args, rank, local_rank, world):
     from zigrad_b200 import opspec
     from zigrad_b200.abi import SINGLE
     from zigrad_b200.device import CudaDevice
-    from zigrad_b200.dp import GradAllReduce
+    from zigrad_b200.dp import GradAllReduce, PeerAllReduce
     from zigrad_b200.mlp import MlpTrainer, kaiming_uniform
 
     torch.cuda.set_device(local_rank)
@@ -176,12 +176,26 @@ def run_gpu(args, rank, local_rank, world):
     R = args.resident
     Ws, bs = kaiming_uniform(DIMS, SEED)
     tr = MlpTrainer(dev, DIMS, B, Ws, bs, "sgd", lr=LR, fused=True, loss_div=global_B)
-    reducer = GradAllReduce() if world > 1 else None
+    # N > 1: the flat gradient buffer (437 KB) is latency-bound, so it is reduced by the
+    # one-kernel peer-memory all-reduce, inside the same captured graph as the rest of the
+    # step; --allreduce nccl selects the library collective between two graphs instead
+    peer = args.allreduce == "peer"
+    reducer = None
+    if world > 1:
+        reducer = PeerAllReduce(dev, tr.n_params) if peer else GradAllReduce()
     host = [make_batch(B, 1000 + rank * 100 + i) for i in range(R)]
     resident = [(dev.from_numpy(X), dev.from_numpy(T)) for X, T in host]
 
     def allreduce(grads):
-        reducer.device(grads, ts)
+        if peer:
+            reducer(grads)
+        else:
+            reducer.device(grads, ts)
+
+    if peer and world > 1:
+        allreduce = reducer  # MlpTrainer.step then fuses the reduction with the SGD update (one kernel)
+
+    one_graph = world == 1 or peer
 
     # ---- capture: one graph per resident batch (N=1: the whole step; N>1: the
     # all-reduce runs between a forward+backward graph and an update graph)
@@ -196,17 +210,17 @@ def run_gpu(args, rank, local_rank, world):
         return dev.capture.detach()
 
     for X, T in resident:
-        if world == 1:
-            graphs.append(capture(lambda: tr.step(X, T)))
+        if one_graph:
+            graphs.append(capture(lambda: tr.step(X, T, allreduce if world > 1 else None)))
         else:
             graphs.append(capture(lambda: (tr.forward(X), tr.loss_and_grad(T), tr.backward(X))))
-    if world > 1:
+    if not one_graph:
         update_graph = capture(tr.update)
     kernels_per_step = graphs[0].kernel_count() + (update_graph.kernel_count() if update_graph else 0)
 
     def step(i):
         graphs[i % R].run()
-        if world > 1:
+        if not one_graph:
             allreduce(tr.grads)
             update_graph.run()
 
@@ -271,8 +285,8 @@ def run_gpu(args, rank, local_rank, world):
         dev.mem_fill(T, 0.1)
     slot_graphs = []
     for X, T in slots:
-        if world == 1:
-            slot_graphs.append(capture(lambda: tr.step(X, T)))
+        if one_graph:
+            slot_graphs.append(capture(lambda: tr.step(X, T, allreduce if world > 1 else None)))
         else:
             slot_graphs.append(capture(lambda: (tr.forward(X), tr.loss_and_grad(T), tr.backward(X))))
     copy_dev = CudaDevice.__new__(CudaDevice)  # a second view of the device on the copy stream, for memcpy only
@@ -294,7 +308,7 @@ def run_gpu(args, rank, local_rank, world):
         ready[s].record(cs)
         ts.wait_event(ready[s])
         slot_graphs[s].run()
-        if world > 1:
+        if not one_graph:
             allreduce(tr.grads)
             update_graph.run()
         dev.L.memcpy_DtoH(loss_host.data_ptr() + 4 * i, tr.loss.ptr, 4, dev.stream)
@@ -364,7 +378,9 @@ def run_gpu(args, rank, local_rank, world):
             "config": {"workload": "MLP 784-128-64-10 (Linear+ReLU, Linear+ReLU, Linear) softmax-CE SGD lr=0.01, fp32 (3xTF32 tensor-core GEMMs), batch %d per GPU" % B,
                        "global_batch": global_B, "per_gpu_batch": B, "parallelism": "dp%d" % world,
                        "l2_policy": "%d resident batches of %.1f MB rotate (%.0f MB > 126 MB L2)" % (R, h2d / 1e6, R * h2d / 1e6),
-                       "step_launch": "CUDA graph per resident batch" + ("" if world == 1 else " + NCCL all-reduce of the flat gradient buffer + update graph")},
+                       "step_launch": "CUDA graph per resident batch" + ("" if world == 1 else (
+                           " incl. the one-kernel peer-memory (NVLink) all-reduce of the flat gradient buffer" if peer else
+                           " + NCCL all-reduce of the flat gradient buffer + update graph"))},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps},
@@ -375,6 +391,11 @@ def run_gpu(args, rank, local_rank, world):
         }
         print(json.dumps(out), flush=True)
     if world > 1:
+        if peer:
+            err = reducer.error()
+            reducer.close()
+            if err:
+                raise RuntimeError("the peer all-reduce gave up waiting for another rank")
         dist.barrier()
         dist.destroy_process_group()
 
@@ -388,6 +409,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8192, help="rows per GPU")
     ap.add_argument("--resident", type=int, default=8, help="distinct batches kept in HBM and rotated")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"], help="N > 1: gradient all-reduce implementation")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

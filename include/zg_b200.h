@@ -215,6 +215,40 @@ EXTERN_C void zg_scatter_gcn_deg_scaled_bwd(dtype id, StreamWrapper stream, cons
                                             const void* deg, const len_t* src_idx, const len_t* tgt_idx,
                                             void* grad_h, void* grad_deg, len_t stride, len_t n_edge);
 
+/* ------------------------------------------------- peer-memory all-reduce
+ * Sum all-reduce of a small fp32 buffer (the data-parallel step's flat gradient
+ * buffer) across the GPUs of one box in ONE kernel per rank, over NVLink loads
+ * and stores to peer memory instead of a library collective.  The reference has
+ * no distributed code (docs/roadmap.norg:74-76 lists it as future work).
+ *
+ * Set-up, once per process group: every rank allocates a comm region
+ * (zg_comm_alloc: plain device memory, cleared, holding a control block and, per
+ * epoch parity and source rank, a receive slot of cap_elems {value, epoch}
+ * words; cap_elems even), exports its IPC handle (zg_ipc_export, 64 bytes),
+ * exchanges handles with the other ranks by any host channel, maps theirs
+ * (zg_ipc_open) and synchronises on the host before the first call.
+ *
+ * zg_allreduce_oneshot(stream, buf, n, rank, world, comm, cap_elems): comm[r] is
+ * rank r's region as mapped in THIS process (comm[rank] the local one).  After
+ * the kernel buf holds the sum over ranks, added in rank order on every rank
+ * (bit-identical replicas).  Every rank must launch it the same number of times
+ * (an epoch counter in device memory pairs the launches, so captured graphs can
+ * replay it); world <= 8; n <= cap_elems.  Waits on peers are bounded: when one
+ * runs out the kernel stops reducing and zg_comm_error() reports 1. */
+EXTERN_C void* zg_comm_alloc(len_t cap_elems, unsigned world);
+EXTERN_C void zg_comm_free(void* region);
+EXTERN_C void zg_ipc_export(void* dptr, unsigned char* handle_out64);
+EXTERN_C void* zg_ipc_open(const unsigned char* handle64);
+EXTERN_C void zg_ipc_close(void* dptr);
+EXTERN_C int zg_comm_error(void* region, StreamWrapper stream);
+EXTERN_C void zg_allreduce_oneshot(StreamWrapper stream, void* buf, len_t n, unsigned rank, unsigned world,
+                                   void* const* comm, len_t cap_elems);
+/* The same reduction with the SGD update of src/nn/optim.zig:100-122 (no
+ * clipping) applied to the reduced gradient in the same kernel:
+ * params[i] += (-lr) * sum_r grads_r[i]; grads receives the sum as well. */
+EXTERN_C void zg_allreduce_sgd_oneshot(StreamWrapper stream, void* grads, void* params, len_t n, double lr,
+                                       unsigned rank, unsigned world, void* const* comm, len_t cap_elems);
+
 /* --------------------------------------------- stream-ordered caching allocator
  * Device-side replacement for the Zig CachingAllocator + BlockPool
  * (src/allocators/caching_allocator.zig:15-162, block_pool.zig:103-412) behind

@@ -187,6 +187,15 @@ SIGNATURES = {
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp]),
     "zg_soft_update": (None, [dtype_t, S, vp, vp, len_t, dbl]),
     "zg_cast": (None, [dtype_t, dtype_t, S, vp, vp, len_t]),
+    # ---- peer-memory all-reduce
+    "zg_comm_alloc": (vp, [len_t, C.c_uint]),
+    "zg_comm_free": (None, [vp]),
+    "zg_ipc_export": (None, [vp, u8p]),
+    "zg_ipc_open": (vp, [u8p]),
+    "zg_ipc_close": (None, [vp]),
+    "zg_comm_error": (C.c_int, [vp, S]),
+    "zg_allreduce_oneshot": (None, [S, vp, len_t, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
+    "zg_allreduce_sgd_oneshot": (None, [S, vp, vp, len_t, dbl, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
     "zg_scatter_add": (None, [dtype_t, S, vp, vp, len_t, vp]),
     "zg_gather_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, vp, vp]),
     "zg_scatter_gcn_deg_scaled": (None, [dtype_t, S, vp, vp, vp, vp, vp, len_t, len_t]),

@@ -97,3 +97,66 @@ class OverlappedGradAllReduce:
             for w in self._pending:
                 w.wait()
         self._pending = []
+
+
+class PeerAllReduce:
+    """Sum all-reduce of a small gradient buffer in one kernel per rank over
+    peer memory (zg_allreduce_oneshot): for latency-bound buffers (up to a few
+    MB) on the GPUs of one box.  A plain kernel launch on the device stream, so
+    the whole data-parallel step -- backward, reduction, update -- can be
+    captured into one CUDA graph.  The host-side exchange of the IPC handles
+    goes through torch.distributed (any backend)."""
+
+    def __init__(self, dev, n_elems: int, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        self.dev, self.dist, self.group = dev, dist, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("PeerAllReduce supports up to 8 ranks")
+        self.cap = (int(n_elems) + 3) // 4 * 4
+        L = dev.L
+        dev.make_current()
+        self.region = L.zg_comm_alloc(self.cap, self.world)
+        if not self.region:
+            raise MemoryError("comm region")
+        handle = (C.c_ubyte * 64)()
+        L.zg_ipc_export(self.region, handle)
+        from . import abi
+        abi.check()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self._opened = []
+        ptrs = (C.c_void_p * self.world)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs[r] = self.region
+            else:
+                buf = (C.c_ubyte * 64).from_buffer_copy(h)
+                p = L.zg_ipc_open(buf)
+                abi.check()
+                self._opened.append(p)
+                ptrs[r] = p
+        self.ptrs = ptrs
+        dist.barrier(group=group)  # every region is cleared and mapped before the first launch
+
+    def __call__(self, grads) -> None:
+        self.dev.L.zg_allreduce_oneshot(self.dev.stream, grads.ptr, grads.len, self.rank, self.world, self.ptrs, self.cap)
+
+    def reduce_and_sgd(self, grads, params, lr: float) -> None:
+        """All-reduce fused with the plain SGD update (no clipping): one kernel."""
+        self.dev.L.zg_allreduce_sgd_oneshot(self.dev.stream, grads.ptr, params.ptr, grads.len, float(lr), self.rank, self.world,
+                                            self.ptrs, self.cap)
+
+    def error(self) -> int:
+        return int(self.dev.L.zg_comm_error(self.region, self.dev.stream))
+
+    def close(self) -> None:
+        self.dev.sync()
+        self.dist.barrier(group=self.group)  # nobody still reads a region that is about to go away
+        for p in self._opened:
+            self.dev.L.zg_ipc_close(p)
+        self._opened = []
+        if self.region:
+            self.dev.L.zg_comm_free(self.region)
+            self.region = None

@@ -217,6 +217,10 @@ class MlpTrainer:
         self.loss_and_grad(T)
         self.backward(X)
         if allreduce is not None:
+            fused = getattr(allreduce, "reduce_and_sgd", None)
+            if fused is not None and self.opt == "sgd" and not self.clip:
+                fused(self.grads, self.params, self.lr)  # reduction and update in one kernel
+                return
             allreduce(self.grads)
         self.update()
 
