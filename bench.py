@@ -44,8 +44,9 @@ LR = 0.01
 SEED = 81761  # the reference's global seed (src/zigrad.zig:66)
 METRIC = "train samples/sec (fwd+bwd+SGD)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of the
-# same full-size launch (profiles/gemm_tc_layer1_forward_8192x128x784_fp32x3.md); batch 8192 only
-NCU_DRAM_TRAFFIC = {"layer-1 forward GEMM+bias+ReLU [B,784]x[128,784]^T": 26160128}
+# same full-size launches (profiles/gemm_tc_fp32x3_mlp_step_gemms_b8192.md); batch 8192 only
+NCU_DRAM_TRAFFIC = {"layer-1 forward GEMM+bias+ReLU [B,784]x[128,784]^T": 26165248,
+                    "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]": 30363392}
 
 
 def make_batch(B, seed):
@@ -360,7 +361,7 @@ def run_gpu(args, rank, local_rank, world):
         top = max(kernel_table, key=lambda k: kernel_table[k]["us_per_op"])
         kt = kernel_table[top]
         roofline = {"kernel": top, "bound": "hbm", "achieved": kt["GBps"], "peak": hbm, "unit": "GB/s", "frac": kt["GBps"] / hbm,
-                    "traffic": NCU_DRAM_TRAFFIC.get(top), "peak_origin": "of " + origin, "us_per_launch": kt["us_per_op"],
+                    "traffic": NCU_DRAM_TRAFFIC.get(top) if B == 8192 else None, "peak_origin": "of " + origin, "us_per_launch": kt["us_per_op"],
                     "algorithmic_bytes": kt["bytes"], "tensor_TFLOPs_algorithmic": kt["TFLOPs"]}
 
     # ---- CPU baseline (bounded sample), rank 0 at N=1 only
