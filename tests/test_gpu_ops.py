@@ -6,6 +6,8 @@ specified to), usually far tighter and stated per test."""
 import numpy as np
 import pytest
 
+from zigrad_b200 import opspec
+
 from .backends import GpuBackend, OracleBackend
 
 pytestmark = pytest.mark.gpu
@@ -351,3 +353,27 @@ def test_plan_api_of_the_reference_shim(gpu):
                                 (abi.len_t * 2)(7, 5), (C.c_ubyte * 2)(*b"ji"), 2)
     L.permutate(d.cutensor, plan.plan, m_.ptr, t_.ptr, None, 0, C.byref(one))
     np.testing.assert_array_equal(be.down(t_).reshape(7, 5), M.T)
+
+
+@pytest.mark.parametrize("rows,C", [(3000, 1000), (20011, 64), (4100, 256), (2500, 512), (9000, 128)])
+def test_softmax_ce_fast_paths_large_index_labels(gpu, rows, C):
+    """The FAST form (index labels, power-of-two divisor, gradient written,
+    bias gradient fused) at sizes that take the staged kernel; the last row group
+    is ragged.  Oracle: the reference's softmax-CE on one-hot rows."""
+    g = rng(rows + C)
+    x = (g.standard_normal((rows, C)) * 3).astype(np.float32)
+    lab = g.integers(0, C, rows)
+    t = np.zeros((rows, C), np.float32)
+    t[np.arange(rows), lab] = 1.0
+    div = 4096
+    wl, wg, _ = ORC.softmax_ce(x, t, loss_div=div)
+    d = gpu
+    X, T = d.from_numpy(x), d.from_numpy(lab.astype(np.uint64))
+    G, Ls, Bg = d.from_numpy(np.full((rows, C), 7.0, np.float32)), d.from_numpy(np.zeros(1, np.float32)), d.from_numpy(np.ones(C, np.float32))
+    d.dispatch(opspec.softmax_ce(X, T, rows, C, Ls, G, div, False, None, 0, Bg))
+    got_g, got_l, got_b = d.to_numpy(G, (rows, C)), float(d.to_numpy(Ls)[0]), d.to_numpy(Bg)
+    assert abs(got_l - wl) <= 2e-5 * abs(wl), (got_l, wl)
+    assert rel_err(got_g, wg) <= 1e-5, rel_err(got_g, wg)
+    assert rel_err(got_b, wg.astype(np.float64).sum(0)) <= 1e-4
+    for s in (X, T, G, Ls, Bg):
+        d.mem_cache_free(s)

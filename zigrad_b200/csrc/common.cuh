@@ -58,6 +58,8 @@ void fold_rows_f32(cudaStream_t s, const float* x, float* y, size_t row, size_t 
 // gemm.cu: reads (and clears) the per-device flag that a tensor-core kernel
 // raises when one of its bounded waits runs out; allocates the flag on first use.
 void check_tc_errors();
+// The same per-device flag (device memory, int): any kernel with bounded waits raises it when one runs out.
+int* kernel_timeout_flag();
 
 // Grid size for a grid-stride kernel: enough CTAs for `work_items` at
 // `per_cta` items each, capped at `waves` resident waves of the device.

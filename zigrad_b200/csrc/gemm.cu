@@ -410,14 +410,16 @@ void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const voi
   else set_error(kUnsupported, "bmm: unsupported dtype combination %d -> %d", (int)id, (int)c_id);
 }
 
-// Reads (and clears) the device flag that a timed-out tensor-core kernel raises.
+int* kernel_timeout_flag() { return tc_error_flag(); }
+
+// Reads (and clears) the device flag that a kernel raises when one of its bounded waits runs out.
 void check_tc_errors() {
   int* f = tc_error_flag();
   if (!f) return;
   int v = 0;
   if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && v) {
     cudaMemset(f, 0, sizeof(int));
-    set_error(kKernelTimeout, "a tensor-core GEMM gave up waiting on a pipeline barrier");
+    set_error(kKernelTimeout, "a kernel gave up waiting on a pipeline barrier");
   }
 }
 

@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "async_copy.cuh"
 #include "../../include/nn_conflux.h"
 
 namespace zg {
@@ -50,6 +51,7 @@ struct SmceArgs {
   float* dbias;          // [C] or nullptr: column sums of (p - t)/divisor
   float* partial;        // workspace: gridDim.x loss partials, then gridDim.x * C bias partials
   int fold_bias_inline;  // the last CTA folds the bias partials into dbias (else a later launch does)
+  unsigned* counter_error;  // raised when a bounded wait of the staged kernel runs out
   unsigned* counter;
 };
 
@@ -240,6 +242,185 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
   }
   float* bias_partial = a.partial + gridDim.x;
   if (a.dbias) cta_column_partials<ITEMS>(bias_acc, colsum, bias_partial + (size_t)blockIdx.x * C, C);
+  smce_finish(a, loss_acc, sm32);
+}
+
+// Wide rows with index labels, staged: the logits travel through a ring of
+// shared-memory stages filled by bulk asynchronous copies (a group of whole rows
+// per stage, several groups in flight per SM regardless of how many registers
+// the math needs), each warp works on rows of the current stage in place, and
+// the gradient leaves through a bulk store of the same stage.  Memory latency
+// is hidden by the ring instead of by occupancy.  FAST form only (dlogits
+// written, power-of-two divisor, no probabilities); rows must be 16-byte
+// aligned (ld % 4 == 0, base aligned).
+constexpr int kStThreads = 512;
+constexpr int kStStages = 3;
+
+template <int ITEMS, int ROWS>
+__global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const SmceArgs a, const int group_rows) {
+  extern __shared__ __align__(128) unsigned char st_raw[];
+  __shared__ uint64_t full[kStStages];
+  __shared__ float sm32[32];
+  __shared__ float colsum[32 * ITEMS];
+  __shared__ int failed;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kWarps = kStThreads / 32;
+  const int C = a.C;
+  const size_t ld = a.ld;
+  const size_t stage_floats = (size_t)group_rows * ld;
+  float* stage0 = reinterpret_cast<float*>(st_raw);
+  const size_t n_groups = (a.rows + group_rows - 1) / group_rows;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStStages; ++s) ac::mbar_init(&full[s], 1);
+    ac::mbar_fence_init();
+    failed = 0;
+  }
+  __syncthreads();
+  pdl_sync();
+  // rows of group g; a group whose byte count is not a multiple of 16 (the ragged last one) is copied by the threads
+  auto rows_of = [&](size_t g) -> int { const size_t r0 = g * group_rows; return (int)((a.rows - r0) < (size_t)group_rows ? (a.rows - r0) : (size_t)group_rows); };
+  auto bulk_ok = [&](int nrows) -> bool { return ((size_t)nrows * ld) % 4 == 0; };
+  auto issue_load = [&](size_t g, int s) {  // thread 0 only
+    const int nrows = rows_of(g);
+    if (!bulk_ok(nrows)) return;
+    const uint32_t bytes = (uint32_t)((size_t)nrows * ld * sizeof(float));
+    ac::mbar_expect_tx(&full[s], bytes);
+    ac::bulk_load(stage0 + (size_t)s * stage_floats, a.logits + g * (size_t)group_rows * ld, bytes, &full[s]);
+  };
+  float loss_acc = 0.f;
+  float bias_acc[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) bias_acc[i] = 0.f;
+  // prologue: the first kStStages - 1 groups of this CTA
+  if (threadIdx.x == 0) {
+    for (int k = 0; k < kStStages - 1; ++k) {
+      const size_t g = blockIdx.x + (size_t)k * gridDim.x;
+      if (g < n_groups) issue_load(g, k);
+    }
+  }
+  size_t it = 0;
+  for (size_t g = blockIdx.x; g < n_groups; g += gridDim.x, ++it) {
+    const int s = (int)(it % kStStages);
+    const int nrows = rows_of(g);
+    float* st = stage0 + (size_t)s * stage_floats;
+    if (threadIdx.x == 0) {
+      // refill the stage that group it-1 used: its bulk store must have finished reading it
+      const size_t gn = g + (size_t)(kStStages - 1) * gridDim.x;
+      if (gn < n_groups) {
+        ac::bulk_wait_read<0>();
+        issue_load(gn, (int)((it + kStStages - 1) % kStStages));
+      }
+    }
+    if (bulk_ok(nrows)) {
+      if (!ac::mbar_wait(&full[s], (uint32_t)((it / kStStages) & 1))) failed = 1;
+    } else {
+      const float* src = a.logits + g * (size_t)group_rows * ld;
+      for (size_t e = threadIdx.x; e < (size_t)nrows * ld; e += kStThreads) st[e] = src[e];
+    }
+    __syncthreads();
+    if (failed) break;
+    // ---- the rows of this stage, ROWS per warp and trip, in place
+    for (int r0 = warp * ROWS; r0 < nrows; r0 += kWarps * ROWS) {
+      float x[ROWS][ITEMS];
+      float mx[ROWS], se[ROWS];
+      int lab[ROWS];
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) {
+        const bool ok = r0 + k < nrows;
+        const float* xr = st + (size_t)(r0 + k) * ld;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int j = lane + 32 * i;
+          x[k][i] = (ok && j < C) ? xr[j] : -INFINITY;
+        }
+        lab[k] = -1;
+        if (ok) {
+          const len_t l = static_cast<const len_t*>(a.labels)[g * (size_t)group_rows + r0 + k];
+          lab[k] = l < (len_t)C ? (int)l : -1;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) {
+        float m = x[k][0];
+#pragma unroll
+        for (int i = 1; i < ITEMS; ++i) m = fmaxf(m, x[k][i]);
+        mx[k] = m;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < ROWS; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+      float dlab[ROWS];
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) {
+        float sacc = 0.f;
+        dlab[k] = 0.f;
+        if (lab[k] >= 0 && (lab[k] & 31) == lane) dlab[k] = st[(size_t)(r0 + k) * ld + lab[k]] - mx[k];
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          x[k][i] = fast_exp(x[k][i] - mx[k]);
+          sacc += x[k][i];
+        }
+        se[k] = sacc;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int k = 0; k < ROWS; ++k) se[k] += __shfl_xor_sync(0xffffffffu, se[k], o);
+#pragma unroll
+      for (int k = 0; k < ROWS; ++k) {
+        if (r0 + k >= nrows) continue;
+        const float lse = logf(se[k]);
+        if (lab[k] >= 0 && (lab[k] & 31) == lane) loss_acc -= clamp_logp(dlab[k] - lse);
+        const float sc = (1.f / se[k]) * a.inv_divisor;
+        float* out = st + (size_t)(r0 + k) * ld;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int j = lane + 32 * i;
+          if (j < C) {
+            float gv = x[k][i] * sc;
+            if (j == lab[k]) gv -= a.inv_divisor;
+            bias_acc[i] += gv;
+            out[j] = gv;
+          }
+        }
+      }
+    }
+    // ---- the stage leaves through one bulk store (the launcher takes unpadded rows only: ld == C)
+    if (bulk_ok(nrows) && (reinterpret_cast<uintptr_t>(a.dlogits) & 15u) == 0) {
+      ac::fence_async_smem();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        ac::bulk_store(a.dlogits + g * (size_t)group_rows * ld, st, (uint32_t)((size_t)nrows * ld * sizeof(float)));
+        ac::bulk_commit();
+      }
+    } else {
+      __syncthreads();
+      float* dst = a.dlogits + g * (size_t)group_rows * ld;
+      for (size_t e = threadIdx.x; e < (size_t)nrows * ld; e += kStThreads)
+        if ((int)(e % ld) < C) dst[e] = st[e];
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) {
+    ac::bulk_wait_all<0>();  // every store has landed before the CTA retires its shared memory
+    if (failed) *a.counter_error = 1;
+  }
+  float* bias_partial = a.partial + gridDim.x;
+  if (a.dbias) {
+    // per-CTA column partials, warps in a fixed order
+    for (int w = 0; w < kWarps; ++w) {
+      if (warp == w) {
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int j = lane + 32 * i;
+          if (j < C) colsum[j] = (w == 0 ? 0.f : colsum[j]) + bias_acc[i];
+        }
+      }
+      __syncthreads();
+    }
+    for (int j = threadIdx.x; j < C; j += blockDim.x) bias_partial[(size_t)blockIdx.x * C + j] = colsum[j];
+  }
   smce_finish(a, loss_acc, sm32);
 }
 
@@ -579,6 +760,36 @@ static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
 
+template <int ITEMS, int ROWS>
+static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
+  const int C = a.C;
+  constexpr int kWarps = kStThreads / 32;
+  // rows per stage: about 64 KB, a multiple of what the warps take per trip
+  int group_rows = (int)((size_t)65536 / ((size_t)a.ld * sizeof(float)));
+  group_rows = group_rows / (kWarps * ROWS) * (kWarps * ROWS);
+  if (group_rows < kWarps * ROWS) group_rows = kWarps * ROWS;
+  const size_t smem = (size_t)kStStages * group_rows * a.ld * sizeof(float);
+  auto kern = softmax_ce_staged_kernel<ITEMS, ROWS>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))) return;
+    attr_set = true;
+  }
+  const size_t n_groups = (a.rows + group_rows - 1) / group_rows;
+  const unsigned g = (unsigned)std::min<size_t>(n_groups, (size_t)sm_count());
+  const bool separate_fold = a.dbias && (size_t)g * C > 32768;
+  unsigned* counters = nullptr;
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)g + (a.dbias ? (size_t)g * C : 0)), &counters, separate_fold ? 1 : 0));
+  if (!partial) return;
+  a.partial = partial;
+  a.counter = counters;
+  a.fold_bias_inline = separate_fold ? 0 : 1;
+  a.counter_error = reinterpret_cast<unsigned*>(kernel_timeout_flag());
+  if (!a.counter_error) return;
+  if (!launch_pdl(kern, dim3(g), dim3(kStThreads), smem, s, a, group_rows)) return;
+  if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
+}
+
 template <bool IDX>
 static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
   const int C = a.C;
@@ -588,6 +799,15 @@ static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
   const bool fast = a.exact_inv && a.dlogits && !a.accumulate && !a.probs_out;
 #define ZG_ROWS(CPV) return fast ? launch_smce_rows<CPV, IDX, true>(s, a) : launch_smce_rows<CPV, IDX, false>(s, a)
 #define ZG_WARPS(I, R) return fast ? launch_smce_warps<I, R, IDX, true>(s, a) : launch_smce_warps<I, R, IDX, false>(s, a)
+  // large index-label problems with unpadded, 16-byte aligned rows: the staged kernel
+  if (IDX && fast && C > 32 && C <= 1024 && C % 4 == 0 && a.ld == (size_t)C && host_aligned16(a.logits) && host_aligned16(a.dlogits) &&
+      a.rows * (size_t)C >= ((size_t)1 << 20) && (size_t)kStStages * 16 * C * sizeof(float) <= 196 * 1024) {
+    if (C <= 64) return launch_smce_staged<2, 8>(s, a);
+    if (C <= 128) return launch_smce_staged<4, 4>(s, a);
+    if (C <= 256) return launch_smce_staged<8, 2>(s, a);
+    if (C <= 512) return launch_smce_staged<16, 1>(s, a);
+    return launch_smce_staged<32, 1>(s, a);
+  }
   if (C <= 4) ZG_ROWS(4);
   if (C <= 8) ZG_ROWS(8);
   if (C <= 12) ZG_ROWS(12);

@@ -100,8 +100,8 @@ def run(mib=1024, reps=10, only=None):
         dl = z.view(0, rows * C)
         db = f(C)
         time_op("softmax_ce_C%d" % C, 8 * rows * C + 8 * rows,
-                lambda: dev.dispatch(opspec.softmax_ce(lg, lab, rows, C, one, dl, float(rows), accumulate=False, bias_grad=db)),
-                "logits read + dlogits written, u64 labels, fused bias gradient")
+                lambda: dev.dispatch(opspec.softmax_ce(lg, lab, rows, C, one, dl, 65536.0, accumulate=False, bias_grad=db)),
+                "logits read + dlogits written, u64 labels, fused bias gradient, loss divisor 65536 (a global batch)")
         dev.mem_cache_free(lab)
         dev.mem_cache_free(db)
 
