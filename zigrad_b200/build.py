@@ -88,9 +88,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_EXAMPLE = os.path.join(HERE, "lib", "mlp_step_main")
+
+
+def build_host_example(force: bool = False) -> str:
+    """The C++ host side (zigrad_b200/host/*.hpp) linked against the library:
+    the MLP-step program that tests/test_gpu_cpp_host.py runs.  g++ only."""
+    src = os.path.join(os.path.dirname(HERE), "tests", "cpp", "mlp_step_main.cpp")
+    deps = [src, LIB] + [os.path.join(HERE, "host", f) for f in sorted(os.listdir(os.path.join(HERE, "host")))]
+    if not force and os.path.exists(HOST_EXAMPLE) and os.path.getmtime(HOST_EXAMPLE) >= max(os.path.getmtime(d) for d in deps):
+        return HOST_EXAMPLE
+    gxx = shutil.which("g++") or "g++"
+    cmd = [gxx, "-std=c++17", "-O2", "-Wall", "-I", os.path.dirname(HERE), src, "-o", HOST_EXAMPLE, "-L", os.path.dirname(LIB),
+           "-lamalgamate", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed for the C++ host example:\n%s\n%s" % (r.stdout, r.stderr))
+    return HOST_EXAMPLE
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="pass -Xptxas -v (registers, spills, shared memory)")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    print(build_host_example(a.force))
