@@ -23,6 +23,7 @@
 // captured graph.  The sum is formed in rank order on every rank: bit-identical
 // replicas.  Polls are bounded; a rank that gives up sets the error word and
 // leaves its buffer partly reduced.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -115,6 +116,105 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
   }
 }
 
+// Two-shot variant for larger worlds (same protocol words, a quarter of the
+// bytes at 8 ranks): the buffer is cut into `world` slices; (1) every rank pushes,
+// for each peer, its values of THAT PEER's slice; (2) the owner of a slice sums
+// the `world` contributions in rank order and pushes the result to every peer;
+// (3) every rank collects the other slices.  The reduced value of an element is
+// computed once, by its owner, so the replicas are bit-identical by
+// construction.  Slots in the comm region: [2 parities]{ scatter [world][S],
+// gather [world][S] } of 16-byte word pairs, S = pairs per slice.
+// Step (2) of a slice element depends on step (1) of the peers, and step (3)
+// on step (2) of the peers: no cycle as long as the CTAs that own step (2)
+// (the lowest-numbered ones) are resident, which the small grid guarantees.
+__global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArArgs a, const size_t S) {
+  pdl_sync();
+  unsigned* ctl = reinterpret_cast<unsigned*>(a.comm[a.rank]);
+  const unsigned e = *reinterpret_cast<volatile unsigned*>(ctl) + 1u;
+  const size_t nth = (size_t)gridDim.x * blockDim.x, tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t npairs = (a.n + 1) / 2;
+  const unsigned W = a.world;
+  auto scatter_slot = [&](unsigned dst, unsigned src) -> uint4* {
+    return reinterpret_cast<uint4*>(a.comm[dst] + kArHeader) + ((size_t)(e & 1u) * 2 * W + src) * S;
+  };
+  auto gather_slot = [&](unsigned dst, unsigned src) -> uint4* {
+    return reinterpret_cast<uint4*>(a.comm[dst] + kArHeader) + ((size_t)(e & 1u) * 2 * W + W + src) * S;
+  };
+  auto poll = [&](const uint4* src, uint4& w) -> bool {
+    w = ld_word_pair(src);
+    for (unsigned it = 0; (w.y != e || w.w != e) && it < kArSpinLimit; ++it) {
+      if (it > 64) __nanosleep(it > 4096 ? 200 : 20);
+      w = ld_word_pair(src);
+    }
+    return w.y == e && w.w == e;
+  };
+  auto local_pair = [&](size_t i, float& v0, float& v1) {
+    v0 = a.grads[2 * i];
+    v1 = (2 * i + 1 < a.n) ? a.grads[2 * i + 1] : 0.f;
+  };
+  auto store_result = [&](size_t i, float s0, float s1) {
+    a.grads[2 * i] = s0;
+    if (2 * i + 1 < a.n) a.grads[2 * i + 1] = s1;
+    if (a.params) {
+      a.params[2 * i] = fmaf(a.nlr, s0, a.params[2 * i]);
+      if (2 * i + 1 < a.n) a.params[2 * i + 1] = fmaf(a.nlr, s1, a.params[2 * i + 1]);
+    }
+  };
+  bool gave_up = false;
+  // ---- (2) first in program order for the threads that own slice elements, but it needs the
+  // peers' step (1): so every thread does its share of step (1) before anything that waits
+  for (size_t i = tid; i < npairs; i += nth) {
+    const unsigned owner = (unsigned)(i / S);
+    if (owner == a.rank) continue;
+    float v0, v1;
+    local_pair(i, v0, v1);
+    uint4 w;
+    w.x = __float_as_uint(v0); w.z = __float_as_uint(v1); w.y = w.w = e;
+    st_word_pair(scatter_slot(owner, a.rank) + (i - (size_t)owner * S), w);
+  }
+  // ---- (2) reduce my slice in rank order, push the result to every peer
+  const size_t my0 = (size_t)a.rank * S;
+  const size_t my_n = my0 < npairs ? ((npairs - my0) < S ? (npairs - my0) : S) : 0;
+  for (size_t j = tid; j < my_n && !gave_up; j += nth) {
+    float s0 = 0.f, s1 = 0.f;
+    for (unsigned p = 0; p < W; ++p) {
+      if (p == a.rank) {
+        float v0, v1;
+        local_pair(my0 + j, v0, v1);
+        s0 += v0; s1 += v1;
+      } else {
+        uint4 w;
+        if (!poll(scatter_slot(a.rank, p) + j, w)) { gave_up = true; break; }
+        s0 += __uint_as_float(w.x); s1 += __uint_as_float(w.z);
+      }
+    }
+    if (gave_up) break;
+    uint4 w;
+    w.x = __float_as_uint(s0); w.z = __float_as_uint(s1); w.y = w.w = e;
+    for (unsigned p = 0; p < W; ++p)
+      if (p != a.rank) st_word_pair(gather_slot(p, a.rank) + j, w);
+    store_result(my0 + j, s0, s1);
+  }
+  // ---- (3) collect the slices the peers reduced
+  for (size_t i = tid; i < npairs && !gave_up; i += nth) {
+    const unsigned owner = (unsigned)(i / S);
+    if (owner == a.rank) continue;
+    uint4 w;
+    if (!poll(gather_slot(a.rank, owner) + (i - (size_t)owner * S), w)) { gave_up = true; break; }
+    store_result(i, __uint_as_float(w.x), __uint_as_float(w.z));
+  }
+  if (gave_up) ctl[2] = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(&ctl[1], 1u);
+    if (t == gridDim.x - 1) {
+      ctl[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned*>(ctl) = e;
+    }
+  }
+}
+
 }  // namespace zg
 
 using namespace zg;
@@ -196,5 +296,15 @@ static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigne
   if (g < 1) g = 1;
   const unsigned cap = (unsigned)sm_count() * 2;
   if (g > cap) g = cap;
+  const size_t npairs = ((size_t)n + 1) / 2;
+  const size_t S = (npairs + world - 1) / world;
+  // two-shot at 8 ranks when the buffer is not tiny (its slots fit: 2 S <= capacity in pairs);
+  // ZG_ALLREDUCE=1 / 2 in the environment forces the one-shot / two-shot kernel
+  static const int force = [] { const char* v = getenv("ZG_ALLREDUCE"); return !v ? 0 : (v[0] == '1' ? 1 : (v[0] == '2' ? 2 : 0)); }();
+  const bool two_shot = force == 2 ? world >= 2 : (force == 1 ? false : world >= 8);
+  if (two_shot && n >= 16384 && 2 * S <= a.cap_pairs) {
+    launch_pdl(allreduce_twoshot_kernel, dim3(g), dim3(kArThreads), 0, as_stream(stream), a, S);
+    return;
+  }
   launch_pdl(allreduce_oneshot_kernel, dim3(g), dim3(kArThreads), 0, as_stream(stream), a);
 }

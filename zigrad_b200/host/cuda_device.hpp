@@ -112,7 +112,7 @@ class CudaDevice {
     d = DeviceData<T>();
   }
   template <typename T>
-  void mem_fill(Slice<T> s, T value) { ::mem_fill(dtype_of<T>(), s.ptr, s.len, &value, stream_); }
+  void mem_fill(Slice<T> s, T value) { ::mem_fill(dtype_of<T>(), s.ptr, s.len, &value, cur()); }
   template <typename T>
   void mem_copy(Slice<const T> src, Slice<T> dst) { memcpy_DtoD(dst.ptr, src.ptr, src.len * sizeof(T), stream_); }
   template <typename T>
