@@ -217,16 +217,22 @@ static bool make_tmap(CUtensorMap* map, bool bf16, const void* base, uint64_t in
   return ZG_CU(r);
 }
 
-template <int BN, bool AK, bool BK_, int MODE>
+template <int BN, bool AK, bool BK_, int MODE, bool ATM = false>
 static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tb, const tc::Params& p, dim3 grid) {
-  using SL = tc::SmemLayout<BN, MODE>;
-  auto kern = tc::gemm_tc_kernel<BN, AK, BK_, MODE>;
+  using SL = tc::SmemLayout<BN, MODE, ATM>;
+  auto kern = tc::gemm_tc_kernel<BN, AK, BK_, MODE, ATM>;
   static bool attr_set = false;
   if (!attr_set) {
     if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::kTotal))) return false;
     attr_set = true;
   }
-  return launch_pdl(kern, grid, dim3(tc::kThreadsTc), (size_t)SL::kTotal, s, ta, tb, p);
+  return launch_pdl(kern, grid, dim3(tc::tc_threads(MODE)), (size_t)SL::kTotal, s, ta, tb, p);
+}
+
+// FP32X3 with a K-major A: the hi/lo parts of A live in tensor memory (ZG_X3_TMEM_A=0 keeps them in shared memory)
+static bool x3_tmem_a() {
+  static const bool on = [] { const char* e = getenv("ZG_X3_TMEM_A"); return !(e && e[0] == '0'); }();
+  return on;
 }
 
 template <int MODE>
@@ -234,6 +240,12 @@ static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor,
                            const tc::Params& p, dim3 grid) {
 #define ZG_TC_CASE(BNV)                                                                       \
   if (bn == BNV) {                                                                            \
+    if constexpr (MODE == tc::kFP32X3) {                                                      \
+      if (a_kmajor && x3_tmem_a()) {                                                          \
+        if (b_kmajor) return launch_tc_inst<BNV, true, true, MODE, true>(s, ta, tb, p, grid); \
+        return launch_tc_inst<BNV, true, false, MODE, true>(s, ta, tb, p, grid);              \
+      }                                                                                       \
+    }                                                                                         \
     if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE>(s, ta, tb, p, grid);   \
     if (a_kmajor && !b_kmajor) return launch_tc_inst<BNV, true, false, MODE>(s, ta, tb, p, grid); \
     if (!a_kmajor && b_kmajor) return launch_tc_inst<BNV, false, true, MODE>(s, ta, tb, p, grid); \

@@ -47,6 +47,8 @@ namespace tc {
 
 constexpr int kBM = 128;
 constexpr int kThreadsTc = 256;
+constexpr int kSplitThreads = kThreadsTc - 64;  // warps 2-7
+__host__ __device__ constexpr int tc_threads(int /*mode*/) { return kThreadsTc; }
 constexpr int kSlabBytes = 128;          // bytes of the contiguous dimension per smem row
 constexpr uint32_t kSpinLimit = 1u << 24;  // polls per wait before giving up
 
@@ -174,6 +176,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes x 32 consecutive 32-bit columns: thread t writes row (lane base + t)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem desc], tf32: A is read from tensor memory (row m in lane m, one k element per column)
+__device__ __forceinline__ void umma_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // Shared-memory matrix descriptor (tcgen05): start address, leading-dimension
 // byte offset and stride byte offset in 16-byte units, descriptor version 1,
@@ -186,6 +209,23 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;  // version (Blackwell)
   d |= (uint64_t)layout << 61;
+  return d;
+}
+
+// The same descriptor as two 32-bit halves: the upper half is a compile-time
+// constant of the layout, the lower half is (address >> 4) | (LBO >> 4) << 16,
+// so stepping to the next MMA inside a slab is ONE integer add on the lower
+// half (the MMA-issuing thread is a single in-order thread; this keeps its
+// work per tcgen05.mma at a few instructions).
+__host__ __device__ constexpr uint32_t desc_hi32(uint32_t sbo_bytes, uint32_t layout) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);
+}
+__device__ __forceinline__ uint32_t desc_lo32(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t desc_pack(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
   return d;
 }
 
@@ -341,28 +381,40 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (
   }
 }
 
-template <int BN, int MODE>
+// ATM: FP32X3 with a K-major A operand keeps the hi and lo parts of A in TENSOR
+// MEMORY (written by the split warps with tcgen05.st, read by the MMA from
+// there): shared memory then holds A once per stage (the fetched slab) and no
+// MMA reads it, which takes 64 of the 144 KB per 128x64x32 slab off the
+// shared-memory data pipe -- the unit that bounds this mode.
+template <int BN, int MODE, bool ATM = false>
 struct SmemLayout {
   using MT = ModeTraits<MODE>;
   static constexpr int kABytes = kBM * kSlabBytes;   // 16 KB
   static constexpr int kBBytes = BN * kSlabBytes;
-  static constexpr int kStageBytes = (kABytes + kBBytes) * MT::kBufs;
+  static constexpr int kStageBytes = ATM ? (kABytes + 2 * kBBytes) : (kABytes + kBBytes) * MT::kBufs;
   static constexpr int kEpiBytes = 0;
   static constexpr int kBudget = 220 * 1024;
-  static constexpr int kStagesRaw = (kBudget - kEpiBytes - 1024) / kStageBytes;
+  static constexpr int kAccCols = BN < 32 ? 32 : BN;
+  static constexpr int kATmemCols = 64;              // per stage: 32 columns hi + 32 columns lo
+  static constexpr int kStagesSmem = (kBudget - kEpiBytes - 1024) / kStageBytes;
+  static constexpr int kStagesTmem = ATM ? (512 - kAccCols) / kATmemCols : 8;
+  static constexpr int kStagesRaw = kStagesSmem < kStagesTmem ? kStagesSmem : kStagesTmem;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemNeed = ATM ? kAccCols + kATmemCols * kStages : kAccCols;
+  static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : (kTmemNeed <= 64 ? 64 : (kTmemNeed <= 128 ? 128 : (kTmemNeed <= 256 ? 256 : 512)));
   static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE, bool ATM = false>
+__global__ void __launch_bounds__(tc_threads(MODE), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  static_assert(!ATM || (MODE == kFP32X3 && A_KMAJOR), "A through tensor memory: FP32X3 with a K-major A only");
   using MT = ModeTraits<MODE>;
-  using SL = SmemLayout<BN, MODE>;
+  using SL = SmemLayout<BN, MODE, ATM>;
   constexpr int S = SL::kStages;
   constexpr bool X3 = (MODE == kFP32X3);
   constexpr uint32_t kIdesc = make_idesc(MT::kBf16, !A_KMAJOR, !B_KMAJOR, BN);
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  constexpr uint32_t kTmemCols = SL::kTmemCols;
 
   extern __shared__ uint8_t smem_raw[];
   // stages need 1024-byte alignment (swizzle atoms)
@@ -388,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     failed = 0;
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&ready[s], kThreadsTc - 64);
+      mbar_init(&ready[s], kSplitThreads);
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
@@ -415,7 +467,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (kt >= S && !mbar_wait(&empty[s], ((kt / S) & 1) ^ 1, &failed)) break;
         uint8_t* st = stage_base + s * SL::kStageBytes;
         uint8_t* a_dst = st;
-        uint8_t* b_dst = st + SL::kABytes * MT::kBufs;
+        uint8_t* b_dst = st + (ATM ? SL::kABytes : SL::kABytes * MT::kBufs);
         mbar_expect_tx(&full[s], SL::kABytes + SL::kBBytes);
         const int k0 = (int)k_begin + kt * MT::kBK;
         if (A_KMAJOR) {
@@ -443,28 +495,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         uint8_t* st = stage_base + s * SL::kStageBytes;
         const uint32_t a_hi = smem_u32(st), a_lo = a_hi + SL::kABytes;
-        const uint32_t b_hi = a_hi + SL::kABytes * MT::kBufs, b_lo = b_hi + SL::kBBytes;
+        const uint32_t b_hi = a_hi + (ATM ? SL::kABytes : SL::kABytes * MT::kBufs), b_lo = b_hi + SL::kBBytes;
+        const uint32_t a_tm = tmem_d + SL::kAccCols + (uint32_t)s * SL::kATmemCols;  // ATM: hi at +0, lo at +32
+        // K-major: the next MMA starts 32 bytes further inside the 128-byte rows;
+        // MN-major: kUmmaK k-rows (128 bytes each) further.  MN-major 32-bit
+        // operands use the 32-byte-atom swizzle with 4-row groups.
+        constexpr uint32_t a_step = (A_KMAJOR ? 32u : (uint32_t)(MT::kUmmaK * kSlabBytes)) >> 4;
+        constexpr uint32_t b_step = (B_KMAJOR ? 32u : (uint32_t)(MT::kUmmaK * kSlabBytes)) >> 4;
+        constexpr uint32_t a_lbo = A_KMAJOR ? 16u : (uint32_t)(MT::kBK * kSlabBytes);
+        constexpr uint32_t b_lbo = B_KMAJOR ? 16u : (uint32_t)(MT::kBK * kSlabBytes);
+        constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
+        constexpr uint32_t a_h32 = desc_hi32(a_lay == 1u ? 512u : 1024u, a_lay), b_h32 = desc_hi32(b_lay == 1u ? 512u : 1024u, b_lay);
+        const uint32_t da0 = desc_lo32(a_hi, a_lbo), dal0 = desc_lo32(a_lo, a_lbo);
+        const uint32_t db0 = desc_lo32(b_hi, b_lbo), dbl0 = desc_lo32(b_lo, b_lbo);
 #pragma unroll
         for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk) {
-          // K-major: next MMA starts 32 bytes further inside the 128-byte rows.
-          // MN-major: next MMA starts kUmmaK k-rows (128 bytes each) further.
-          const uint32_t a_off = A_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
-          const uint32_t b_off = B_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
-          const uint32_t a_lbo = A_KMAJOR ? 16 : MT::kBK * kSlabBytes;
-          const uint32_t b_lbo = B_KMAJOR ? 16 : MT::kBK * kSlabBytes;
-          // MN-major 32-bit operands: 32-byte-atom swizzle, 4-row groups
-          constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
-          constexpr uint32_t a_sbo = (a_lay == 1u) ? 512u : 1024u, b_sbo = (b_lay == 1u) ? 512u : 1024u;
-          const uint64_t da = make_desc(a_hi + a_off, a_lbo, a_sbo, a_lay);
-          const uint64_t db = make_desc(b_hi + b_off, b_lbo, b_sbo, b_lay);
+          const uint64_t db = desc_pack(db0 + kk * b_step, b_h32);
           const uint32_t acc = (kt > 0 || kk > 0) ? 1u : 0u;
-          if constexpr (X3) {
-            const uint64_t dal = make_desc(a_lo + a_off, a_lbo, a_sbo, a_lay);
-            const uint64_t dbl = make_desc(b_lo + b_off, b_lbo, b_sbo, b_lay);
+          if constexpr (ATM) {
+            const uint64_t dbl = desc_pack(dbl0 + kk * b_step, b_h32);
+            const uint32_t ta_hi = a_tm + kk * MT::kUmmaK, ta_lo = ta_hi + 32;
+            umma_tmem_a(tmem_d, ta_lo, db, kIdesc, acc);   // Alo * Bhi
+            umma_tmem_a(tmem_d, ta_hi, dbl, kIdesc, 1u);   // Ahi * Blo
+            umma_tmem_a(tmem_d, ta_hi, db, kIdesc, 1u);    // Ahi * Bhi
+          } else if constexpr (X3) {
+            const uint64_t da = desc_pack(da0 + kk * a_step, a_h32);
+            const uint64_t dal = desc_pack(dal0 + kk * a_step, a_h32);
+            const uint64_t dbl = desc_pack(dbl0 + kk * b_step, b_h32);
             umma<false>(tmem_d, dal, db, kIdesc, acc);   // Alo * Bhi
             umma<false>(tmem_d, da, dbl, kIdesc, 1u);    // Ahi * Blo
             umma<false>(tmem_d, da, db, kIdesc, 1u);     // Ahi * Bhi
           } else {
+            const uint64_t da = desc_pack(da0 + kk * a_step, a_h32);
             umma<MT::kBf16>(tmem_d, da, db, kIdesc, acc);
           }
         }
@@ -475,18 +537,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (X3) {
     // ------------------------------------------- hi/lo split (warps 2..7)
     const int t = threadIdx.x - 64;
-    constexpr int NT = kThreadsTc - 64;
+    const bool a_warp = warp >= 4;  // ATM: the four warps that cover the TMEM lane quadrants (warp % 4)
+    constexpr int NT = kSplitThreads;
     for (int kt = 0; kt < KT; ++kt) {
       const int s = kt % S;
       if (!mbar_wait(&full[s], (kt / S) & 1, &failed)) break;
       uint8_t* st = stage_base + s * SL::kStageBytes;
       float4* a_hi = reinterpret_cast<float4*>(st);
       float4* a_lo = reinterpret_cast<float4*>(st + SL::kABytes);
-      float4* b_hi = reinterpret_cast<float4*>(st + SL::kABytes * 2);
-      float4* b_lo = reinterpret_cast<float4*>(st + SL::kABytes * 2 + SL::kBBytes);
+      float4* b_hi = reinterpret_cast<float4*>(st + (ATM ? SL::kABytes : SL::kABytes * 2));
+      float4* b_lo = b_hi + SL::kBBytes / 16;
+      if constexpr (ATM) {
+        // Four warps of the group (TMEM lane quadrant = warp % 4): thread = row of the A slab.  The row's
+        // eight 16-byte chunks sit at chunk position c ^ (row % 8) (128-byte swizzle);
+        // hi = the fetched word itself, lo = x - tf32(x); both go to tensor memory.
+        if (a_warp) {
+          const int row = (warp & 3) * 32 + lane;
+          const uint8_t* rp = st + row * kSlabBytes;
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(rp + ((c ^ (row & 7)) << 4));
+            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t h = __float_as_uint(x[e]) & 0xFFFFE000u;
+              hi[4 * c + e] = __float_as_uint(x[e]);
+              lo[4 * c + e] = __float_as_uint(x[e] - __uint_as_float(h));
+            }
+          }
+          const uint32_t ta = tmem_d + SL::kAccCols + (uint32_t)s * SL::kATmemCols + ((uint32_t)((warp & 3) * 32) << 16);
+          tmem_st32(ta, hi);
+          tmem_st32(ta + 32, lo);
+          tmem_st_wait();
+          tc_fence_before();
+        }
+      }
       // the split is position independent, so the swizzle does not matter here
 #pragma unroll 4
-      for (int i = t; i < SL::kABytes / 16; i += NT) {
+      for (int i = t; i < (ATM ? 0 : SL::kABytes / 16); i += NT) {
         const float4 v = a_hi[i];
         float4 h, l;
         h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
@@ -514,7 +603,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // Each epilogue thread owns one accumulator row: 32 consecutive columns per
   // tcgen05.ld, i.e. one full 128-byte line of C, read (beta / mask) and
   // written with 128-bit accesses straight from registers.
-  if (warp >= 4) {
+  if (warp >= 4 && warp < 8) {
     const int q = warp - 4;  // TMEM lane quadrant
     const bool have_acc = (KT > 0) && mbar_wait(accum, 0, &failed);
     tc_fence_after();

@@ -66,11 +66,7 @@ class MlpTrainer {
   Slice<float> db(std::size_t l) { return grads_.raw.view(segments_[2 * l + 1].first, segments_[2 * l + 1].second); }
 
   void forward(Slice<const float> X) {
-    // zero_grad (model.zig:57-62) as one fill of the flat buffer, on the side stream: the
-    // forward pass does not touch the gradients
-    d_.branch();
-    d_.mem_fill(grads_.raw, 0.f);
-    d_.end_branch();
+    d_.mem_fill(grads_.raw, 0.f);  // zero_grad (model.zig:57-62) as one fill of the flat buffer
     Slice<const float> in = X;
     for (std::size_t l = 0; l < L_; ++l) {
       opspec::linear<float> p;
@@ -83,7 +79,6 @@ class MlpTrainer {
       d_.dispatch(p);
       in = act_[l].raw;
     }
-    d_.join();
   }
   void loss_and_grad(Slice<const float> onehot) {
     opspec::softmax_ce<float> p;
