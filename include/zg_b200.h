@@ -214,6 +214,20 @@ EXTERN_C void zg_scatter_gcn_deg_scaled(dtype id, StreamWrapper stream, void* ds
 EXTERN_C void zg_scatter_gcn_deg_scaled_bwd(dtype id, StreamWrapper stream, const void* grad_out, const void* h,
                                             const void* deg, const len_t* src_idx, const len_t* tgt_idx,
                                             void* grad_h, void* grad_deg, len_t stride, len_t n_edge);
+/* The same propagation over a CSR form of the edge list, without atomics
+ * (deterministic; the graph is static, so the CSR is built once on the host by a
+ * STABLE sort of the edges, which keeps every sum in edge order and the result
+ * bit-identical to the host loops above):
+ *   transpose_form == 0, edges grouped by target (row = t, col_idx = s):
+ *       out[t,j] = sum_e (deg[s]*deg[t]) * x[s,j]   [+ bias[j]] [ReLU]   -- scatter_gcn_deg_scaled on a zero dst
+ *   transpose_form == 1, edges grouped by source (row = s, col_idx = t):
+ *       out[s,j] = sum_e (x[t,j]*deg[s]) * deg[t]                        -- grad_h of scatter_gcn_deg_scaled_bwd
+ * out is overwritten; ld_x / ld_out are row strides in elements; epilogue is
+ * ZG_EPI_NONE, ZG_EPI_BIAS or ZG_EPI_BIAS_RELU (GraphConvLayer's `+ bias` and the
+ * ReLU after it, examples/gcn/src/model.zig:36,100-112). */
+EXTERN_C void zg_csr_gcn_propagate(dtype id, StreamWrapper stream, void* out, const void* x, const void* deg,
+                                   const len_t* row_ptr, const len_t* col_idx, len_t n_rows, len_t n_feat,
+                                   len_t ld_x, len_t ld_out, int transpose_form, int epilogue, const void* bias);
 
 /* ------------------------------------------------- peer-memory all-reduce
  * Sum all-reduce of a small fp32 buffer (the data-parallel step's flat gradient

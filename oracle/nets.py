@@ -156,3 +156,58 @@ class GcnOracle:
         if update:
             self.adam.step(self.tensors(), self.grads)
         return float(np.float32(loss))
+
+
+class GcnSparseOracle:
+    """The reference's own GCN algorithm: every GraphConvLayer is h = x.W^T,
+    y = scatter_gcn_deg_scaled(h) over the edge list + bias
+    (examples/gcn/src/model.zig:100-112, :116-248; host_device.zig:1356-1403 for
+    the scatter and its backward), ReLU between the layers, row mask, softmax
+    cross-entropy over the masked rows, Adam with default clipping."""
+
+    def __init__(self, src, tgt, deg, W1, b1, W2, b2, lr=0.01):
+        self.src, self.tgt, self.deg = np.ascontiguousarray(src, np.uint64), np.ascontiguousarray(tgt, np.uint64), f32(deg)
+        self.W = [f32(W1).copy(), f32(W2).copy()]
+        self.b = [f32(b1).copy(), f32(b2).copy()]
+        self.adam = AdamState(self.tensors(), lr, clip=True)
+
+    def tensors(self):
+        return [self.W[0], self.b[0], self.W[1], self.b[1]]
+
+    def _prop(self, h):
+        N, F = h.shape
+        return O.scatter_gcn_deg_scaled(np.zeros(N * F, np.float32), f32(h).ravel(), self.deg, self.src, self.tgt, F).reshape(N, F)
+
+    def _prop_bwd(self, go, h):
+        N, F = go.shape
+        gh, _ = O.scatter_gcn_deg_scaled_bwd(f32(go).ravel(), f32(h).ravel(), self.deg, self.src, self.tgt, np.zeros(N * F, np.float32),
+                                             np.zeros(N, np.float32), F)
+        return gh.reshape(N, F)
+
+    def step(self, X, T_masked, mask_idx, update=True):
+        X = f32(X)
+        N = X.shape[0]
+        H, C = self.W[0].shape[0], self.W[1].shape[0]
+        h1 = _mm(X, self.W[0], False, True)
+        a1 = O.elwise("add", self.b[0], self._prop(h1).ravel()).reshape(N, H)
+        a1 = O.unary("relu_fwd", a1.ravel()).reshape(N, H)
+        h2 = _mm(a1, self.W[1], False, True)
+        logits = O.elwise("add", self.b[1], self._prop(h2).ravel()).reshape(N, C)
+        masked = logits[mask_idx]
+        loss, sm = O.softmax_ce_fwd(masked, T_masked, len(mask_idx))
+        dm = O.softmax_ce_bwd(sm.ravel(), f32(T_masked).ravel(), np.zeros(masked.size, np.float32), len(mask_idx)).reshape(masked.shape)
+        dlog = np.zeros((N, C), np.float32)
+        dlog[mask_idx] = dm
+        db2 = O.fold_rows(dlog.ravel(), np.zeros(C, np.float32), N, C, 1.0, 1.0)
+        dh2 = self._prop_bwd(dlog, h2)
+        dW2 = _mm(dh2, a1, True, False)
+        da1 = _mm(dh2, self.W[1], False, False)
+        da1 = O.relu_inplace_bwd(a1.ravel(), da1.ravel()).reshape(N, H)
+        db1 = O.fold_rows(da1.ravel(), np.zeros(H, np.float32), N, H, 1.0, 1.0)
+        dh1 = self._prop_bwd(da1, h1)
+        dW1 = _mm(dh1, X, True, False)
+        self.logits, self.a1, self.dlog, self.da1 = logits, a1, dlog, da1
+        self.grads = [dW1, db1, dW2, db2]
+        if update:
+            self.adam.step(self.tensors(), self.grads)
+        return float(np.float32(loss))

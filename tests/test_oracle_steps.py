@@ -107,3 +107,28 @@ def test_dqn_oracle_loss_and_gradients_match_torch(orc):
     for l in range(3):
         np.testing.assert_allclose(model.policy.dW[l], tW[l].grad.numpy(), rtol=1e-4, atol=1e-7)
         np.testing.assert_allclose(model.policy.db[l], tb[l].grad.numpy(), rtol=1e-4, atol=1e-7)
+
+
+def test_sparse_gcn_oracle_equals_dense_oracle_on_the_scatter_matrix(orc):
+    """The reference's edge-scatter GCN step and the dense-adjacency step agree
+    when the dense matrix is the one the scatter defines."""
+    from oracle.nets import GcnSparseOracle
+    N, F, H, C, M = 80, 31, 16, 7, 25
+    src, tgt = synthetic.gcn_graph(N, 300, 9)
+    Ad, d = synthetic.gcn_scatter_equivalent(src, tgt, N)
+    np.testing.assert_array_equal(d, synthetic.gcn_degree_scale(tgt, N))
+    X = synthetic.gcn_features(N, F, 0.2)
+    (W1, W2), (b1, b2) = kaiming_uniform([F, H, C], 3)
+    g = np.random.Generator(np.random.PCG64(5))
+    mask = np.sort(g.permutation(N)[:M])
+    T = np.eye(C, dtype=np.float32)[g.integers(0, C, M)]
+    sp, de = GcnSparseOracle(src, tgt, d, W1, b1, W2, b2), GcnOracle(Ad, W1, b1, W2, b2)
+    l1, l2 = sp.step(X, T, mask, update=False), de.step(X, T, mask, update=False)
+    assert abs(l1 - l2) <= 1e-5 * abs(l2)
+    for a, b in zip(sp.grads, de.grads):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+    # CSR built by a stable sort keeps the edges of a row in list order
+    rp, ci = synthetic.edges_to_csr(tgt, src, N)
+    assert rp[-1] == src.size
+    for t in (0, N // 2, N - 1):
+        np.testing.assert_array_equal(ci[int(rp[t]):int(rp[t + 1])], src[tgt == t])

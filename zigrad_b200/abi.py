@@ -200,6 +200,7 @@ SIGNATURES = {
     "zg_gather_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, vp, vp]),
     "zg_scatter_gcn_deg_scaled": (None, [dtype_t, S, vp, vp, vp, vp, vp, len_t, len_t]),
     "zg_scatter_gcn_deg_scaled_bwd": (None, [dtype_t, S, vp, vp, vp, vp, vp, vp, vp, len_t, len_t]),
+    "zg_csr_gcn_propagate": (None, [dtype_t, S, vp, vp, vp, vp, vp, len_t, len_t, len_t, len_t, C.c_int, C.c_int, vp]),
     "zg_cache_create": (CacheWrapper, [C.c_uint, len_t]),
     "zg_cache_destroy": (None, [CacheWrapper]),
     "zg_cache_alloc": (Block, [CacheWrapper, len_t, S]),

@@ -130,6 +130,18 @@ def run(configs, cpu=True, reps=200):
             row.update(cpu_us_per_step=cus, cpu_cores=cores)
         out.append(row)
         tr.free()
+        # the reference's own algorithm for the same graph: edge scatter (here: CSR walk) instead of the dense product
+        deg = synthetic.gcn_degree_scale(tgt, N)
+        trs = GcnTrainer(dev, None, X, W1, b1, W2, b2, mask, edges=(src, tgt, deg))
+        us, n = _graph_time(dev, ts, lambda: trs.step(Td), reps)
+        row = {"config": "c4s GCN sparse propagation (edge list, CSR walk), same graph", "us_per_step": us, "steps_per_s": 1e6 / us, "kernels": n}
+        if cpu:
+            from oracle.nets import GcnSparseOracle
+            m = GcnSparseOracle(src, tgt, deg, W1, b1, W2, b2)
+            cus = _cpu_time(lambda: m.step(X, T, mask), 20)
+            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        out.append(row)
+        trs.free()
 
     if "c5" in configs:
         dims = [4, 128, 128, 2]

@@ -70,6 +70,59 @@ __global__ void __launch_bounds__(kIThreads) gcn_scatter_bwd_kernel(const float*
   }
 }
 
+// GCN propagation over a CSR adjacency, no atomics.  A warp owns a row: its
+// lanes fetch up to 32 neighbours at once (index, degree scale and feature
+// row: the loads of a hub node's many neighbours are in flight together) and
+// park the products in shared memory, then lane j adds column j up IN EDGE
+// ORDER.  mode 0 = forward of scatter_gcn_deg_scaled with the edges grouped by
+// TARGET (row = target t, col = source s):
+//     out[t, j] = sum_e (deg[s] * deg[t]) * x[s, j]            (+ bias[j], ReLU)
+// mode 1 = its gradient w.r.t. h with the edges grouped by SOURCE (row = s,
+// col = t):  out[s, j] = sum_e (x[t, j] * deg[s]) * deg[t]
+// -- the products in the order of host_device.zig:1356-1403, the sums in edge
+// order when the CSR was built by a stable sort of the edge list, which makes
+// the result bit-identical to the host loops.
+constexpr int kCsrWarps = kIThreads / 32;
+
+__global__ void __launch_bounds__(kIThreads) csr_gcn_propagate_kernel(float* out, const float* __restrict__ x, const float* __restrict__ deg,
+                                                                      const len_t* __restrict__ row_ptr, const len_t* __restrict__ col,
+                                                                      size_t n_rows, size_t F, size_t ld_x, size_t ld_out, int mode,
+                                                                      int epilogue, const float* __restrict__ bias) {
+  __shared__ float prod[kCsrWarps][32][33];  // [neighbour of the chunk][feature of the tile], padded: both access patterns conflict-free
+  pdl_sync();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_rows; r += warps) {
+    const len_t k0 = row_ptr[r], k1 = row_ptr[r + 1];
+    const float dr = deg[r];
+    for (size_t j0 = 0; j0 < F; j0 += 32) {
+      const int fw = (int)((F - j0) < 32 ? (F - j0) : 32);
+      float acc = 0.f;  // lane j < fw: feature j0 + j
+      for (len_t kc = k0; kc < k1; kc += 32) {
+        const int nk = (int)((k1 - kc) < 32 ? (k1 - kc) : 32);
+        if (lane < nk) {
+          const size_t c = col[kc + lane];
+          const float dc = deg[c];
+          const float* xr = x + c * ld_x + j0;
+          for (int j = 0; j < fw; ++j) {
+            const float v = xr[j];
+            prod[warp][lane][j] = mode == 0 ? (dc * dr) * v : (v * dr) * dc;
+          }
+        }
+        __syncwarp();
+        if (lane < fw)
+          for (int l = 0; l < nk; ++l) acc += prod[warp][l][lane];
+        __syncwarp();
+      }
+      if (lane < fw) {
+        if (epilogue == ZG_EPI_BIAS || epilogue == ZG_EPI_BIAS_RELU) acc += bias[j0 + lane];
+        if (epilogue == ZG_EPI_BIAS_RELU) acc = acc > 0.f ? acc : 0.f;
+        out[r * ld_out + j0 + lane] = acc;
+      }
+    }
+  }
+}
+
 }  // namespace zg
 
 using namespace zg;
@@ -108,4 +161,16 @@ extern "C" void zg_scatter_gcn_deg_scaled_bwd(dtype id, StreamWrapper w, const v
   if (n_edge == 0 || stride == 0) return;
   gcn_scatter_bwd_kernel<<<grid_for(n_edge, kIThreads), kIThreads, 0, as_stream(w)>>>((const float*)grad_out, (const float*)h, (const float*)deg, src_idx, tgt_idx, (float*)grad_h, (float*)grad_deg, stride, n_edge);
   ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_csr_gcn_propagate(dtype id, StreamWrapper w, void* out, const void* x, const void* deg, const len_t* row_ptr,
+                                     const len_t* col_idx, len_t n_rows, len_t n_feat, len_t ld_x, len_t ld_out, int transpose_form,
+                                     int epilogue, const void* bias) {
+  if (id != SINGLE) { set_error(kUnsupported, "zg_csr_gcn_propagate: only SINGLE is implemented"); return; }
+  if (n_rows == 0 || n_feat == 0) return;
+  if (epilogue != ZG_EPI_NONE && epilogue != ZG_EPI_BIAS && epilogue != ZG_EPI_BIAS_RELU) { set_error(kBadArgument, "zg_csr_gcn_propagate: epilogue %d", epilogue); return; }
+  if (epilogue != ZG_EPI_NONE && !bias) { set_error(kBadArgument, "zg_csr_gcn_propagate: bias epilogue without bias"); return; }
+  launch_pdl(csr_gcn_propagate_kernel, dim3(grid_for(n_rows, kCsrWarps)), dim3(kIThreads), 0, as_stream(w), (float*)out, (const float*)x,
+             (const float*)deg, row_ptr, col_idx, (size_t)n_rows, (size_t)n_feat, (size_t)ld_x, (size_t)ld_out, transpose_form ? 1 : 0, epilogue,
+             (const float*)bias);
 }

@@ -436,6 +436,11 @@ class CudaDevice:
                                              p.src_indices.ptr, p.tgt_indices.ptr, p.grad_h.ptr, p.grad_deg.ptr,
                                              p.stride, p.n_edge)
 
+    def csr_gcn_propagate(self, p):
+        epi = {"none": abi.EPI_NONE, "bias": abi.EPI_BIAS, "bias_relu": abi.EPI_BIAS_RELU}[p.epilogue]
+        self.L.zg_csr_gcn_propagate(p.x.dtype, self.stream, p.out.ptr, p.x.ptr, p.deg.ptr, p.row_ptr.ptr, p.col_idx.ptr, p.n_rows, p.n_feat,
+                                    p.ld_x, p.ld_out, 1 if p.transpose else 0, epi, p.bias.ptr if p.bias is not None else None)
+
     def gather_rows(self, src: DeviceSlice, idx: DeviceSlice, rows: int, cols: int, dst: DeviceSlice,
                     offsets_out: Optional[DeviceSlice] = None):
         self.L.zg_gather_rows(src.dtype, self.stream, src.ptr, idx.ptr, rows, cols, dst.ptr,

@@ -17,6 +17,8 @@ rule; padding columns are zero and stay zero.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import numpy as np
 
 from . import opspec
@@ -29,10 +31,15 @@ def _pad4(n: int) -> int:
 
 
 class GcnTrainer:
-    def __init__(self, dev: CudaDevice, A_hat: np.ndarray, X: np.ndarray, W1, b1, W2, b2, mask_idx: np.ndarray,
+    def __init__(self, dev: CudaDevice, A_hat: Optional[np.ndarray], X: np.ndarray, W1, b1, W2, b2, mask_idx: np.ndarray,
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = True,
-                 max_norm: float = 10.0, delta: float = 1e-6, opt: str = "adam"):
+                 max_norm: float = 10.0, delta: float = 1e-6, opt: str = "adam", edges=None):
+        """`A_hat`: dense normalised adjacency (config 4), or None with
+        `edges = (src, tgt, deg)` for the reference's own sparse propagation
+        (edge list + deg^-1/2 per node): the edge scatter then runs as a CSR
+        row walk without atomics (opspec.csr_gcn_propagate)."""
         d = self.dev = dev
+        self.sparse = edges is not None
         self.N, self.F = X.shape
         self.H, self.C = W1.shape[0], W2.shape[0]
         self.Fp, self.Cp = _pad4(self.F), _pad4(self.C)
@@ -44,7 +51,16 @@ class GcnTrainer:
         Xp = np.zeros((N, Fp), np.float32)
         Xp[:, :F] = X
         self.X = d.from_numpy(Xp)
-        self.A = d.from_numpy(np.ascontiguousarray(A_hat, np.float32))
+        if self.sparse:
+            from .synthetic import edges_to_csr
+            src, tgt, deg = edges
+            rp, ci = edges_to_csr(tgt, src, N)      # forward: grouped by target, neighbours = sources
+            rpt, cit = edges_to_csr(src, tgt, N)    # gradient w.r.t. h: grouped by source, neighbours = targets
+            self.csr = tuple(d.from_numpy(a) for a in (rp, ci, rpt, cit))
+            self.deg = d.from_numpy(np.ascontiguousarray(deg, np.float32))
+            self.A = None
+        else:
+            self.A = d.from_numpy(np.ascontiguousarray(A_hat, np.float32))
         # flat parameters in attach order: W1 [H, Fp], b1 [H], W2 [C, H], b2 [C]
         W1p = np.zeros((H, Fp), np.float32)
         W1p[:, :F] = W1
@@ -79,15 +95,25 @@ class GcnTrainer:
     def _mm(self, A, B, Cbuf, m, n, k, ta, tb, lda, ldb, ldc, beta=0.0, epilogue="none", bias=None, mask=None, colsum=None):
         self.dev.dispatch(opspec.linear(A, B, Cbuf, m, n, k, ta, tb, lda, ldb, ldc, 1.0, beta, epilogue, bias, mask, colsum=colsum))
 
+    def _prop(self, x, out, F, ld, epilogue="none", bias=None, transpose=False):
+        """out = A.x (+ bias, ReLU) -- dense GEMM with the adjacency, or the CSR walk over the edges."""
+        N = self.N
+        if self.sparse:
+            rp, ci, rpt, cit = self.csr
+            self.dev.dispatch(opspec.csr_gcn_propagate(out, x, self.deg, rpt if transpose else rp, cit if transpose else ci, N, F, ld, ld,
+                                                       transpose, epilogue, bias))
+        else:
+            self._mm(self.A, x, out, N, F, N, transpose, False, N, ld, ld, 0.0, epilogue, bias)
+
     def step(self, T_masked: DeviceSlice):
         """T_masked: one-hot targets of the masked rows, fp32 [M, C] contiguous."""
         d, N, F, H, C, Fp, Cp, M = self.dev, self.N, self.F, self.H, self.C, self.Fp, self.Cp, self.M
         d.mem_fill(self.grads, 0.0)  # zero_grad (model.zig:49-54)
         # ---- forward
         self._mm(self.X, self.W1, self.h1, N, H, F, False, True, Fp, Fp, H)                       # h1 = X . W1^T
-        self._mm(self.A, self.h1, self.a1, N, H, N, False, False, N, H, H, 0.0, "bias_relu", self.b1)  # relu(A.h1 + b1)
+        self._prop(self.h1, self.a1, H, H, "bias_relu", self.b1)                                   # relu(A.h1 + b1)
         self._mm(self.a1, self.W2, self.h2, N, C, H, False, True, H, H, Cp)                       # h2 = a1 . W2^T
-        self._mm(self.A, self.h2, self.logits, N, C, N, False, False, N, Cp, Cp, 0.0, "bias", self.b2)  # A.h2 + b2
+        self._prop(self.h2, self.logits, C, Cp, "bias", self.b2)                                   # A.h2 + b2
         # ---- mask rows, loss, gradient of the masked logits (+ db2 = its column sums)
         d.mem_take(self.logits, self.offsets, self.mlog)
         d.dispatch(opspec.softmax_ce(self.mlog, T_masked, M, C, self.loss, self.dm, float(M), accumulate=False, ld=Cp,
@@ -95,11 +121,11 @@ class GcnTrainer:
         d.mem_fill(self.dlog, 0.0)
         d.dispatch(opspec.scatter_add(self.dm, self.offsets, self.dlog))                            # MaskLayer backward
         # ---- backward
-        self._mm(self.A, self.dlog, self.dh2, N, C, N, True, False, N, Cp, Cp)                    # dh2 = A^T . dlogits
+        self._prop(self.dlog, self.dh2, C, Cp, transpose=True)                                    # dh2 = A^T . dlogits
         self._mm(self.dh2, self.a1, self.dW2, C, H, N, True, False, Cp, H, H, 1.0)                # dW2 += dh2^T . a1
         self._mm(self.dh2, self.W2, self.da1, N, H, C, False, False, Cp, H, H, 0.0, "relu_mask", None, self.a1,
                  colsum=self.db1)                                                                   # da1, db1
-        self._mm(self.A, self.da1, self.dh1, N, H, N, True, False, N, H, H)                       # dh1 = A^T . da1
+        self._prop(self.da1, self.dh1, H, H, transpose=True)                                      # dh1 = A^T . da1
         self._mm(self.dh1, self.X, self.dW1, H, F, N, True, False, H, Fp, Fp, 1.0)                # dW1 += dh1^T . X
         # ---- update
         if self.opt == "adam":
@@ -122,6 +148,7 @@ class GcnTrainer:
     def free(self):
         d = self.dev
         d.sync()
-        for s in (self.X, self.A, self.params, self.grads, self.m, self.v, self.norms, self.h1, self.a1, self.h2, self.logits,
-                  self.dlog, self.dh2, self.da1, self.dh1, self.mlog, self.dm, self.offsets, self.loss, self.t_dev):
+        extra = list(self.csr) + [self.deg] if self.sparse else [self.A]
+        for s in extra + [self.X, self.params, self.grads, self.m, self.v, self.norms, self.h1, self.a1, self.h2, self.logits,
+                  self.dlog, self.dh2, self.da1, self.dh1, self.mlog, self.dm, self.offsets, self.loss, self.t_dev]:
             d.mem_cache_free(s)

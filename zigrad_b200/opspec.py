@@ -417,6 +417,25 @@ class adam:
     step_counter: Optional[Any] = None  # device u64: tensor updates so far (graph-replay safe step count)
 
 
+@_op("csr_gcn_propagate")
+class csr_gcn_propagate:
+    """scatter_gcn_deg_scaled / its grad_h (src/device/host_device.zig:1356-1403)
+    over a CSR form of the static edge list, without atomics.  transpose=False:
+    rows = targets (forward); True: rows = sources (gradient w.r.t. h)."""
+    out: Any
+    x: Any
+    deg: Any
+    row_ptr: Any
+    col_idx: Any
+    n_rows: int
+    n_feat: int
+    ld_x: int
+    ld_out: int
+    transpose: bool = False
+    epilogue: str = "none"   # none | bias | bias_relu
+    bias: Optional[Any] = None
+
+
 @_op("linear")
 class linear:
     """bmm_acc with a fused epilogue: the Linear layer's three device calls

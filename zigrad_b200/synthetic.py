@@ -81,3 +81,22 @@ def dqn_batch(B: int = 256, seed: int = 3):
     r = np.ones(B, np.float32)
     done = (g.random(B) < 0.05).astype(np.float32)
     return s, a, s2, r, done
+
+
+def gcn_degree_scale(tgt, n_nodes: int) -> np.ndarray:
+    """d = (1 + in-degree)^-1/2, as the reference's GCN layer computes it
+    (examples/gcn/src/model.zig:207-224)."""
+    deg = np.ones(n_nodes, np.float32)
+    np.add.at(deg, np.asarray(tgt).astype(np.int64), np.float32(1.0))
+    return (np.float32(1.0) / np.sqrt(np.maximum(deg, np.float32(1e-12)))).astype(np.float32)
+
+
+def edges_to_csr(rows, cols, n_nodes: int):
+    """CSR of an edge list grouped by `rows` with a STABLE sort (edges of one row
+    keep their list order): returns (row_ptr u64 [n+1], col_idx u64 [n_edge])."""
+    rows = np.asarray(rows).astype(np.int64)
+    order = np.argsort(rows, kind="stable")
+    counts = np.bincount(rows, minlength=n_nodes)
+    row_ptr = np.zeros(n_nodes + 1, np.uint64)
+    row_ptr[1:] = np.cumsum(counts)
+    return row_ptr, np.ascontiguousarray(np.asarray(cols)[order].astype(np.uint64))
