@@ -170,7 +170,6 @@ def run_gpu(args, rank, local_rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ts = torch.cuda.Stream()           # compute stream, shared with the device object
-    cs = torch.cuda.Stream()           # copy stream (end-to-end leg)
     dev = CudaDevice(local_rank, stream=ts.cuda_stream)
     B = args.batch
     global_B = B * world               # weak scaling: per-GPU batch fixed
@@ -277,54 +276,49 @@ def run_gpu(args, rank, local_rank, world):
     value = args.steps * global_B / (ms / 1e3)
     loss_after = tr.read_loss()
 
-    # ---- e2e: batches come from pinned host memory, losses go back to the host
-    pin = [(torch.from_numpy(X).pin_memory(), torch.from_numpy(T).pin_memory()) for X, T in host]
-    loss_host = torch.zeros(args.steps + args.warmup, dtype=torch.float32).pin_memory()
-    slots = [(dev.mem_cache_alloc(SINGLE, B * DIMS[0]), dev.mem_cache_alloc(SINGLE, B * DIMS[-1])) for _ in range(2)]
-    for X, T in slots:  # warm, then capture a graph per slot
+    # ---- e2e: batches come from pinned host memory through the package's input pipeline
+    # (copy stream, double-buffered), the loss of every step goes back to the host
+    from zigrad_b200.input_pipeline import BatchStager
+    st = BatchStager(dev, [(B * DIMS[0], SINGLE), (B * DIMS[-1], SINGLE)], depth=2)
+    pin = [(st.pinned_like(X), st.pinned_like(T)) for X, T in host]
+    loss_host = st.pinned((args.steps + args.warmup,), np.float32)
+    for X, T in st.slots:  # defined contents before the graphs are captured
         dev.mem_fill(X, 0.5)
         dev.mem_fill(T, 0.1)
     slot_graphs = []
-    for X, T in slots:
+    for X, T in st.slots:
         if one_graph:
             slot_graphs.append(capture(lambda: tr.step(X, T, allreduce if world > 1 else None)))
         else:
             slot_graphs.append(capture(lambda: (tr.forward(X), tr.loss_and_grad(T), tr.backward(X))))
-    copy_dev = CudaDevice.__new__(CudaDevice)  # a second view of the device on the copy stream, for memcpy only
-    copy_dev.__dict__.update(dev.__dict__)
-    from zigrad_b200 import abi
-    copy_dev.stream = abi.StreamWrapper(cs.cuda_stream)
-    ready = [torch.cuda.Event() for _ in range(2)]
-    free = [torch.cuda.Event() for _ in range(2)]
-    for ev in free:
-        ev.record(ts)
-    h2d = (B * DIMS[0] + B * DIMS[-1]) * 4
+    h2d = st.bytes_per_batch()
+    n_e2e = args.warmup + args.steps
 
     def e2e_step(i):
-        s = i % 2
-        Xp, Tp = pin[i % R]
-        cs.wait_event(free[s])
-        dev.L.memcpy_HtoD(slots[s][0].ptr, Xp.data_ptr(), Xp.numel() * 4, copy_dev.stream)
-        dev.L.memcpy_HtoD(slots[s][1].ptr, Tp.data_ptr(), Tp.numel() * 4, copy_dev.stream)
-        ready[s].record(cs)
-        ts.wait_event(ready[s])
+        if i + 1 < n_e2e:
+            st.put(pin[(i + 1) % R])          # the copy of the next batch overlaps this step
+        s = st.current_slot()
+        st.get()                              # compute stream waits for this batch's copy
         slot_graphs[s].run()
         if not one_graph:
             allreduce(tr.grads)
             update_graph.run()
-        dev.L.memcpy_DtoH(loss_host.data_ptr() + 4 * i, tr.loss.ptr, 4, dev.stream)
-        free[s].record(ts)
+        dev.L.memcpy_DtoH(loss_host.ctypes.data + 4 * i, tr.loss.ptr, 4, dev.stream)
+        st.release()
 
+    st.put(pin[0])
     for i in range(args.warmup):
         e2e_step(i)
     barrier()
     e0.record(ts)
-    for i in range(args.warmup, args.warmup + args.steps):
+    for i in range(args.warmup, n_e2e):
         e2e_step(i)
     e1.record(ts)
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     e2e_value = args.steps * global_B / (ms_e2e / 1e3)
+    e2e_last_loss = float(loss_host[n_e2e - 1])
+    st.close()
 
     # ---- roofline of the slowest kernel, timed alone over the rotating batches
     roofline, kernel_table = None, None
@@ -384,7 +378,8 @@ def run_gpu(args, rank, local_rank, world):
                            " + NCCL all-reduce of the flat gradient buffer + update graph"))},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / args.steps, "last_loss_read_on_host": e2e_last_loss,
+                    "api": "zigrad_b200.input_pipeline.BatchStager + MlpTrainer.step (captured graph per staging slot)"},
             "gpu_launches": int(kernels_per_step * args.steps),
             "kernels_per_step": int(kernels_per_step),
             "final_loss": loss_after,

@@ -35,6 +35,13 @@ EXTERN_C void zg_set_device(unsigned device_number);
  * (src/device/cuda_device.zig:24-33). */
 EXTERN_C void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller);
 
+/* Page-locked host memory for the input pipeline: host-to-device copies from
+ * it run asynchronously on a copy stream while the previous batch trains (the
+ * reference's loader copies pageable memory synchronously, tensor by tensor:
+ * examples/mnist/src/dataset.zig:11-67).  NULL on failure. */
+EXTERN_C void* zg_host_alloc_pinned(len_t nbytes);
+EXTERN_C void zg_host_free_pinned(void* hptr);
+
 /* Number of kernel nodes in a saved capture (cuda_utils.h: open_capture /
  * save_capture): what one run_capture launches. */
 EXTERN_C len_t zg_capture_kernel_count(GraphWrapper graph);

@@ -107,6 +107,8 @@ SIGNATURES = {
     "deinit_stream": (None, [S]),
     "stream_synchronize": (None, [S]),
     "zg_stream_wait": (None, [S, S]),
+    "zg_host_alloc_pinned": (vp, [len_t]),
+    "zg_host_free_pinned": (None, [vp]),
     "init_cublas_handle": (CB, [S]),
     "deinit_cublas_handle": (None, [CB]),
     "init_cudnn_handle": (CD, [S]),

@@ -303,6 +303,16 @@ extern "C" StreamWrapper init_stream(void) {
 extern "C" void deinit_stream(StreamWrapper stream) {
   if (stream.ptr) ZG_CUDA(cudaStreamDestroy(as_stream(stream)));
 }
+extern "C" void* zg_host_alloc_pinned(len_t nbytes) {
+  void* p = nullptr;
+  if (!ZG_CUDA(cudaHostAlloc(&p, nbytes ? nbytes : 1, cudaHostAllocDefault))) return nullptr;
+  return p;
+}
+
+extern "C" void zg_host_free_pinned(void* hptr) {
+  if (hptr) ZG_CUDA(cudaFreeHost(hptr));
+}
+
 extern "C" void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller) {
   // events come from a ring that lives as long as the process: a wait only
   // needs its event until the wait has been enqueued (or captured)
