@@ -136,11 +136,12 @@ if __name__ == "__main__":
     ap.add_argument("--beta", type=float, default=0.0)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same shape")
+    ap.add_argument("--operands", type=int, default=4, help="distinct A operands used in turn (1 keeps A in L2 when it fits)")
     a = ap.parse_args()
     ts = torch.cuda.Stream()
     dev = CudaDevice(0, stream=ts.cuda_stream)
     if a.m:
-        run_one(dev, ts, "custom", a.m, a.n, a.k, a.ta, a.tb, a.dtype, a.c_bf16, a.epi, a.beta, a.reps, a.cublas)
+        run_one(dev, ts, "custom", a.m, a.n, a.k, a.ta, a.tb, a.dtype, a.c_bf16, a.epi, a.beta, a.reps, a.cublas, R=a.operands)
     else:
         for cfg in C3:
             run_one(dev, ts, *cfg, reps=a.reps, cublas=a.cublas)
