@@ -44,7 +44,7 @@ LR = 0.01
 SEED = 81761  # the reference's global seed (src/zigrad.zig:66)
 METRIC = "train samples/sec (fwd+bwd+SGD)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of the
-# same full-size launches (profiles/gemm_tc_fp32x3_mlp_step_gemms_b8192.md); batch 8192 only
+# same full-size launches (the eight GEMMs of one eager step, ncu --set full); batch 8192 only
 NCU_DRAM_TRAFFIC = {"layer-1 forward GEMM+bias+ReLU [B,784]x[128,784]^T": 26165248,
                     "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]": 30363392}
 

@@ -4,7 +4,7 @@
  * Adam update, runs them as raw loops over host memory); its CUDA backend
  * has no counterpart, so the Zig CudaDevice cannot run a training step on the
  * device today.  Each declaration cites the HOST code whose semantics it
- * follows; INTEGRATION.md shows the Zig-side method that binds it.
+ * follows.
  *
  * All calls are asynchronous on the given stream and never exit the
  * process: errors are recorded in a sticky per-process status.

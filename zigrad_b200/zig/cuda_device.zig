@@ -224,7 +224,7 @@ pub fn scatter_gcn_deg_scaled_bwd(self: *const Self, T: type, p: opspec.scatter_
 }
 
 // ------------------------------------------------------ ops added to the opspec
-// (struct definitions to add to src/device/opspec.zig are in INTEGRATION.md)
+// (the struct definitions these methods take are additions to src/device/opspec.zig: softmax_ce, smooth_l1, sgd, adam, linear)
 pub fn softmax_ce(self: *const Self, T: type, p: opspec.softmax_ce(T)) void {
     cuda.zg_softmax_ce_fwd_bwd(dtype(T), self.context.stream, p.logits.ptr, p.labels.ptr, cuda.ZG_LABEL_ONEHOT, p.rows, p.classes, p.ld, p.loss_div, p.loss.ptr, if (p.grad) |g| g.ptr else null, @intFromBool(p.accumulate), null, if (p.bias_grad) |b| b.ptr else null);
 }
