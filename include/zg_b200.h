@@ -187,6 +187,11 @@ typedef struct {
 /* SGD.update over every segment (src/nn/optim.zig:100-122): per tensor
  * [if clip: nrm = ||g||; if nrm > max_norm: g *= max_norm/(nrm+delta)] then
  * p += (-lr)*g.  norms is a device scratch of n_seg floats (used when clip). */
+/* clip: 0 = off; 1 = the call computes the per-tensor norms itself; 2 = norms[j]
+ * already holds ||g_j|| of tensor j (a sharded optimizer sums the squares of its
+ * shard with zg_segment_sumsq, adds them up over the ranks and takes the root).
+ * A segment may be empty (len 0): it still counts as a tensor for Adam's step
+ * counter, which lets a rank list every tensor and own only parts of some. */
 EXTERN_C void zg_sgd_step(dtype id, StreamWrapper stream, void* params, void* grads,
                           const zg_segment* seg, len_t n_seg, double lr,
                           int clip, double max_norm, double delta, void* norms);
@@ -202,6 +207,9 @@ EXTERN_C void zg_adam_step(dtype id, StreamWrapper stream, void* params, void* g
                            const zg_segment* seg, len_t n_seg, len_t t_first,
                            double lr, double beta1, double beta2, double eps,
                            int clip, double max_norm, double delta, void* norms, void* bf16_copy, void* step_counter);
+/* out[j] = sum of squares of segment j (fp64 accumulation, deterministic two-stage): the
+ * shard-local part of the per-tensor gradient norm of host_device.zig:339-346 */
+EXTERN_C void zg_segment_sumsq(dtype id, StreamWrapper stream, const void* x, const zg_segment* seg, len_t n_seg, void* out);
 /* target[i] = tau*src[i] + (1-tau)*target[i] (examples/dqn/src/dqn_agent.zig:111-123) */
 EXTERN_C void zg_soft_update(dtype id, StreamWrapper stream, const void* src, void* target, len_t n, double tau);
 /* fp32 -> bf16 (round to nearest even) and back */

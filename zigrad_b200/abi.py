@@ -187,6 +187,7 @@ SIGNATURES = {
     "zg_smooth_l1_fwd_bwd": (None, [dtype_t, S, vp, vp, len_t, dbl, vp, vp]),
     "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp]),
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp]),
+    "zg_segment_sumsq": (None, [dtype_t, S, vp, C.POINTER(Segment), len_t, vp]),
     "zg_soft_update": (None, [dtype_t, S, vp, vp, len_t, dbl]),
     "zg_cast": (None, [dtype_t, dtype_t, S, vp, vp, len_t]),
     # ---- peer-memory all-reduce

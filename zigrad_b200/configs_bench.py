@@ -160,7 +160,7 @@ def run(configs, cpu=True, reps=200):
     return out
 
 
-def run_c3_dp(steps=20, warmup=5):
+def run_c3_dp(steps=20, warmup=5, zero=False):
     """Config c3 data-parallel: one process per GPU (torchrun), 8192 rows per
     GPU (the global batch of 65536 at 8 GPUs; weak scaling below that), the
     gradient of each layer all-reduced over NCCL as soon as its weight-gradient
@@ -171,7 +171,7 @@ def run_c3_dp(steps=20, warmup=5):
     import torch.distributed as dist
     from .abi import BF16
     from .device import CudaDevice
-    from .dp import OverlappedGradAllReduce
+    from .dp import OverlappedGradAllReduce, ZeroShardedAdam
     from .mlp import MlpTrainer, kaiming_uniform
 
     rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
@@ -193,11 +193,16 @@ def run_c3_dp(steps=20, warmup=5):
     Xd = dev.mem_cache_alloc(BF16, X.size)
     dev.cast(xf, Xd)
     Td = dev.from_numpy(lab)
-    red = OverlappedGradAllReduce() if world > 1 else None
+    red = OverlappedGradAllReduce() if (world > 1 and not zero) else None
+    zopt = ZeroShardedAdam(tr, ts, side) if (world > 1 and zero) else None
 
     def step():
         tr.forward(Xd)
         tr.loss_and_grad(Td)
+        if zopt:  # reduce-scatter per layer, Adam on the owned slices, all-gather of the bf16 weights
+            tr.backward(Xd, on_layer_grads=zopt.start)
+            zopt.finish()
+            return
         tr.backward(Xd, on_layer_grads=(lambda l: red.start(tr.layer_grads(l), side)) if red else None)
         if red:
             red.finish(ts)
@@ -226,7 +231,9 @@ def run_c3_dp(steps=20, warmup=5):
     loss = tr.read_loss()
     if rank == 0:
         us = ms * 1e3 / steps
-        print(json.dumps({"config": "c3 data-parallel, bf16 + fp32 master, Adam, per-layer NCCL all-reduce overlapped with backward",
+        how = ("per-layer NCCL reduce-scatter overlapped with backward, Adam sharded over the ranks, all-gather of the bf16 weights" if zopt
+               else "per-layer NCCL all-reduce overlapped with backward")
+        print(json.dumps({"config": "c3 data-parallel, bf16 + fp32 master, Adam, " + how,
                           "n_gpus": world, "global_batch": B * world, "us_per_step": us, "samples_per_s": B * world / us * 1e6,
                           "TFLOPs_per_gpu": 293011456.0 * B / us * 1e-6, "allreduce_bytes_per_step": 4 * tr.n_params,
                           "loss": loss, "scaling": "weak"}), flush=True)
@@ -241,9 +248,10 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--reps", type=int, default=200, help="graph replays per timing")
     ap.add_argument("--dp", action="store_true", help="config c3 data-parallel under torchrun (one process per GPU)")
+    ap.add_argument("--zero", action="store_true", help="with --dp: shard the optimizer over the ranks (reduce-scatter / all-gather)")
     a = ap.parse_args()
     if a.dp:
-        run_c3_dp()
+        run_c3_dp(zero=a.zero)
         raise SystemExit(0)
     for r in run(a.configs.split(","), cpu=not a.no_cpu, reps=a.reps):
         print(json.dumps(r), flush=True)

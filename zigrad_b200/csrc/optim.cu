@@ -28,7 +28,7 @@ __device__ __forceinline__ bool same_phase(const void* a, const void* b) {
 // norms[first + j] = ||g_j||_2 for every segment of the table.  grid = (chunks, n);
 // chunk partials are folded by the last CTA of each segment in index order.
 __global__ void __launch_bounds__(kOThreads) seg_nrm2_kernel(const float* __restrict__ g, const __grid_constant__ SegTable tab,
-                                                             float* norms, double* partial, unsigned* counters) {
+                                                             float* norms, double* partial, unsigned* counters, int squares) {
   __shared__ double sm[32];
   pdl_sync();
   const int seg = blockIdx.y;
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kOThreads) seg_nrm2_kernel(const float* __rest
   double s = 0.0;
   for (unsigned k = threadIdx.x; k < gridDim.x; k += blockDim.x) s += __ldcg(mine + k);
   s = block_sum<double>(s, sm);
-  if (threadIdx.x == 0) norms[tab.first + seg] = (float)sqrt(s);
+  if (threadIdx.x == 0) norms[tab.first + seg] = squares ? (float)s : (float)sqrt(s);  // squares: the caller sums them over shards first
 }
 
 __device__ __forceinline__ float clip_factor(const float* norms, int idx, float max_norm, float delta, bool* on) {
@@ -217,7 +217,7 @@ static unsigned chunks_for(const zg_segment* seg, size_t n_seg) {
   return (unsigned)(c < 1 ? 1 : c);
 }
 
-static bool compute_norms(cudaStream_t s, const float* grads, const zg_segment* seg, size_t n_seg, float* norms) {
+static bool compute_norms(cudaStream_t s, const float* grads, const zg_segment* seg, size_t n_seg, float* norms, int squares = 0) {
   if (!norms) { set_error(kBadArgument, "optimizer: clip requested but norms scratch is NULL"); return false; }
   for (size_t first = 0; first < n_seg; first += kMaxSeg) {
     SegTable tab;
@@ -230,7 +230,7 @@ static bool compute_norms(cudaStream_t s, const float* grads, const zg_segment* 
     unsigned* counters = nullptr;
     double* partial = static_cast<double*>(workspace(s, sizeof(double) * chunks * tab.n, &counters));
     if (!partial) return false;
-    if (!launch_pdl(seg_nrm2_kernel, dim3(chunks, tab.n), dim3(kOThreads), 0, s, grads, tab, norms, partial, counters)) return false;
+    if (!launch_pdl(seg_nrm2_kernel, dim3(chunks, tab.n), dim3(kOThreads), 0, s, grads, tab, norms, partial, counters, squares)) return false;
   }
   return true;
 }
@@ -245,7 +245,8 @@ extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads
   if (n_seg == 0) return;
   cudaStream_t s = as_stream(w);
   const float nlr = -(float)lr;  // lr cast f64 -> f32, then negated (optim.zig:103)
-  if (clip && !compute_norms(s, (const float*)grads, seg, n_seg, (float*)norms)) return;
+  if (clip == 1 && !compute_norms(s, (const float*)grads, seg, n_seg, (float*)norms)) return;
+  if (clip == 2 && !norms) { set_error(kBadArgument, "optimizer: clip with given norms but norms is NULL"); return; }
   for (size_t first = 0; first < n_seg; first += kMaxSeg) {
     SegTable tab;
     memset(&tab, 0, sizeof(tab));
@@ -266,7 +267,8 @@ extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grad
   if (n_seg == 0) return;
   cudaStream_t s = as_stream(w);
   const float lr = (float)lr_, beta1 = (float)beta1_, beta2 = (float)beta2_, eps = (float)eps_;
-  if (clip && !compute_norms(s, (const float*)grads, seg, n_seg, (float*)norms)) return;
+  if (clip == 1 && !compute_norms(s, (const float*)grads, seg, n_seg, (float*)norms)) return;
+  if (clip == 2 && !norms) { set_error(kBadArgument, "optimizer: clip with given norms but norms is NULL"); return; }
   for (size_t first = 0; first < n_seg; first += kMaxSeg) {
     SegTable tab;
     memset(&tab, 0, sizeof(tab));
@@ -292,4 +294,10 @@ extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grad
   if (step_counter) {  // advance the device counter once per tensor, after every update kernel has read it
     launch_pdl(counter_add_kernel, dim3(1), dim3(1), 0, s, static_cast<unsigned long long*>(step_counter), (unsigned long long)n_seg);
   }
+}
+
+extern "C" void zg_segment_sumsq(dtype id, StreamWrapper w, const void* x, const zg_segment* seg, len_t n_seg, void* out) {
+  if (id != SINGLE) { set_error(kUnsupported, "zg_segment_sumsq: only SINGLE is implemented"); return; }
+  if (n_seg == 0) return;
+  compute_norms(as_stream(w), (const float*)x, seg, n_seg, (float*)out, 1);
 }

@@ -473,9 +473,13 @@ class CudaDevice:
     def adam(self, p):
         self.L.zg_adam_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr,
                             self._segments(p.segments), len(p.segments), p.t_first, p.lr, p.beta1, p.beta2, p.eps,
-                            int(p.clip), p.max_norm, p.delta, p.norms.ptr if p.norms is not None else None,
+                            2 if p.clip == "given" else int(bool(p.clip)), p.max_norm, p.delta,
+                            p.norms.ptr if p.norms is not None else None,
                             p.bf16_copy.ptr if p.bf16_copy is not None else None,
                             p.step_counter.ptr if p.step_counter is not None else None)
+
+    def segment_sumsq(self, x: DeviceSlice, segments, out: DeviceSlice):
+        self.L.zg_segment_sumsq(x.dtype, self.stream, x.ptr, self._segments(segments), len(segments), out.ptr)
 
     def soft_update(self, src: DeviceSlice, target: DeviceSlice, tau: float):
         self.L.zg_soft_update(src.dtype, self.stream, src.ptr, target.ptr, src.len, tau)

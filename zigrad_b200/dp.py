@@ -160,3 +160,87 @@ class PeerAllReduce:
         if self.region:
             self.dev.L.zg_comm_free(self.region)
             self.region = None
+
+
+class ZeroShardedAdam:
+    """Data-parallel Adam with the optimizer sharded over the ranks (reduce-scatter
+    of the gradients, Adam on the owned slices, all-gather of the bf16 weights).
+
+    For the wide mixed-precision MLP the all-reduce + replicated Adam of the plain
+    data-parallel step moves 2 x 218 MB over the links and spends 0.29 ms per step
+    in an optimizer kernel that every rank repeats.  Here, per layer l:
+      * `start(l)` (called on the side stream right after dW_l was issued) starts an
+        asynchronous REDUCE-SCATTER of the layer's slice [dW_l ; db_l] of the flat
+        gradient buffer: rank r receives the r-th 1/world part, in place;
+      * `finish()` waits for the reductions, forms the per-tensor gradient norms
+        (sum of squares of the owned parts, summed over the ranks, root) as the
+        reference clips per tensor (src/device/host_device.zig:339-346), runs Adam
+        (src/nn/optim.zig:177-234) over the owned parts only -- every tensor stays
+        in the segment list, possibly empty, so the per-tensor step counter runs
+        as on one device -- and ALL-GATHERS the updated bf16 weights in place.
+    fp32 master weights and moments exist only for the owned parts (the rest of
+    those buffers is unused); forward and backward read the bf16 copy.
+    Layer slices must divide by the world size (true for 4096-wide layers at 8)."""
+
+    def __init__(self, trainer, main_stream, side_stream, group=None):
+        import torch
+        import torch.distributed as dist
+        if not trainer.bf16 or trainer.opt != "adam":
+            raise ValueError("ZeroShardedAdam drives an MlpTrainer in bf16 mode with Adam")
+        self.tr, self.dist, self.group, self.torch = trainer, dist, group, torch
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.main, self.side = main_stream, side_stream
+        tr, W = trainer, self.world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.g32 = torch.as_tensor(_CudaView(tr.grads.ptr, tr.grads.len, "<f4"), device=dev)
+        self.w16 = torch.as_tensor(_CudaView(tr.params_bf16.ptr, tr.params_bf16.len, "<i2"), device=dev).view(torch.bfloat16)
+        self.layers, self.owned = [], []
+        for l in range(tr.L):
+            (woff, wn), (boff, bn) = tr.segments[2 * l], tr.segments[2 * l + 1]
+            n = wn + bn
+            if n % W:
+                raise ValueError("layer %d has %d parameters: not divisible by %d ranks" % (l, n, W))
+            c = n // W
+            lo, hi = woff + self.rank * c, woff + (self.rank + 1) * c
+            self.layers.append((woff, n, c))
+            # owned part of the weight tensor, owned part of the bias tensor (either may be empty)
+            self.owned.append((lo, max(0, min(hi, woff + wn) - lo)))
+            b0 = max(lo, boff)
+            self.owned.append((b0, max(0, hi - b0)))
+        self.sumsq = tr.dev.mem_cache_alloc(0, len(self.owned))
+        self.sumsq_t = torch.as_tensor(_CudaView(self.sumsq.ptr, self.sumsq.len, "<f4"), device=dev)
+        self._pending = []
+
+    def start(self, l: int) -> None:
+        off, n, c = self.layers[l]
+        full = self.g32[off:off + n]
+        mine = self.g32[off + self.rank * c: off + (self.rank + 1) * c]
+        with self.torch.cuda.stream(self.side):
+            self._pending.append(self.dist.reduce_scatter_tensor(mine, full, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self) -> None:
+        from . import opspec
+        tr, d = self.tr, self.tr.dev
+        with self.torch.cuda.stream(self.main):
+            for w in self._pending:
+                w.wait()
+        self._pending = []
+        clip = tr.clip
+        if clip:
+            d.segment_sumsq(tr.grads, self.owned, self.sumsq)
+            with self.torch.cuda.stream(self.main):
+                self.dist.all_reduce(self.sumsq_t, op=self.dist.ReduceOp.SUM, group=self.group)
+            d.dispatch(opspec.sqrt_fwd(self.sumsq, self.sumsq))
+        d.dispatch(opspec.adam(tr.params, tr.grads, tr.m, tr.v, self.owned, tr.t + 1, tr.lr, tr.beta1, tr.beta2, tr.eps,
+                               "given" if clip else False, tr.max_norm, tr.delta, self.sumsq, tr.params_bf16, tr.t_dev))
+        tr.t += len(self.owned)
+        works = []
+        with self.torch.cuda.stream(self.main):
+            for off, n, c in self.layers:
+                works.append(self.dist.all_gather_into_tensor(self.w16[off:off + n], self.w16[off + self.rank * c: off + (self.rank + 1) * c],
+                                                              group=self.group, async_op=True))
+            for w in works:
+                w.wait()
+
+    def free(self) -> None:
+        self.tr.dev.mem_cache_free(self.sumsq)
