@@ -355,7 +355,8 @@ def test_plan_api_of_the_reference_shim(gpu):
     np.testing.assert_array_equal(be.down(t_).reshape(7, 5), M.T)
 
 
-@pytest.mark.parametrize("rows,C", [(3000, 1000), (20011, 64), (4100, 256), (2500, 512), (9000, 128)])
+@pytest.mark.parametrize("rows,C", [(3000, 1000), (20011, 64), (4100, 256), (2500, 512), (9000, 128),
+                                     (120003, 10), (300000, 4), (70001, 16), (50000, 28), (150001, 7)])
 def test_softmax_ce_fast_paths_large_index_labels(gpu, rows, C):
     """The FAST form (index labels, power-of-two divisor, gradient written,
     bias gradient fused) at sizes that take the staged kernel; the last row group

@@ -268,8 +268,11 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
   const int C = a.C;
   const size_t ld = a.ld;
   const size_t stage_floats = (size_t)group_rows * ld;
-  float* stage0 = reinterpret_cast<float*>(st_raw);
+  // a stage = the logits of a group of rows followed by their labels (u64 each)
+  const size_t stage_bytes = stage_floats * sizeof(float) + (size_t)group_rows * sizeof(len_t);
   const size_t n_groups = (a.rows + group_rows - 1) / group_rows;
+  auto stage_logits = [&](int s) -> float* { return reinterpret_cast<float*>(st_raw + (size_t)s * stage_bytes); };
+  auto stage_labels = [&](int s) -> len_t* { return reinterpret_cast<len_t*>(st_raw + (size_t)s * stage_bytes + stage_floats * sizeof(float)); };
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStStages; ++s) ac::mbar_init(&full[s], 1);
     ac::mbar_fence_init();
@@ -279,13 +282,14 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
   pdl_sync();
   // rows of group g; a group whose byte count is not a multiple of 16 (the ragged last one) is copied by the threads
   auto rows_of = [&](size_t g) -> int { const size_t r0 = g * group_rows; return (int)((a.rows - r0) < (size_t)group_rows ? (a.rows - r0) : (size_t)group_rows); };
-  auto bulk_ok = [&](int nrows) -> bool { return ((size_t)nrows * ld) % 4 == 0; };
+  auto bulk_ok = [&](int nrows) -> bool { return ((size_t)nrows * ld) % 4 == 0 && nrows % 2 == 0; };
   auto issue_load = [&](size_t g, int s) {  // thread 0 only
     const int nrows = rows_of(g);
     if (!bulk_ok(nrows)) return;
-    const uint32_t bytes = (uint32_t)((size_t)nrows * ld * sizeof(float));
-    ac::mbar_expect_tx(&full[s], bytes);
-    ac::bulk_load(stage0 + (size_t)s * stage_floats, a.logits + g * (size_t)group_rows * ld, bytes, &full[s]);
+    const uint32_t bytes = (uint32_t)((size_t)nrows * ld * sizeof(float)), lbytes = (uint32_t)(nrows * sizeof(len_t));
+    ac::mbar_expect_tx(&full[s], bytes + lbytes);
+    ac::bulk_load(stage_logits(s), a.logits + g * (size_t)group_rows * ld, bytes, &full[s]);
+    ac::bulk_load(stage_labels(s), static_cast<const len_t*>(a.labels) + g * (size_t)group_rows, lbytes, &full[s]);
   };
   float loss_acc = 0.f;
   float bias_acc[ITEMS];
@@ -302,7 +306,8 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
   for (size_t g = blockIdx.x; g < n_groups; g += gridDim.x, ++it) {
     const int s = (int)(it % kStStages);
     const int nrows = rows_of(g);
-    float* st = stage0 + (size_t)s * stage_floats;
+    float* st = stage_logits(s);
+    len_t* lst = stage_labels(s);
     if (threadIdx.x == 0) {
       // refill the stage that group it-1 used: its bulk store must have finished reading it
       const size_t gn = g + (size_t)(kStStages - 1) * gridDim.x;
@@ -316,6 +321,7 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
     } else {
       const float* src = a.logits + g * (size_t)group_rows * ld;
       for (size_t e = threadIdx.x; e < (size_t)nrows * ld; e += kStThreads) st[e] = src[e];
+      for (int e = threadIdx.x; e < nrows; e += kStThreads) lst[e] = static_cast<const len_t*>(a.labels)[g * (size_t)group_rows + e];
     }
     __syncthreads();
     if (failed) break;
@@ -335,7 +341,7 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
         }
         lab[k] = -1;
         if (ok) {
-          const len_t l = static_cast<const len_t*>(a.labels)[g * (size_t)group_rows + r0 + k];
+          const len_t l = lst[r0 + k];
           lab[k] = l < (len_t)C ? (int)l : -1;
         }
       }
@@ -606,6 +612,155 @@ __global__ void __launch_bounds__(kRowThreads) softmax_ce_row_kernel(const SmceA
   smce_finish(a, loss_acc, sm32);
 }
 
+// Narrow rows at scale (index labels, FAST form, unpadded 16-byte aligned
+// rows): the same thread-per-row arithmetic, but the blocks of rows travel
+// through a ring of shared-memory stages with bulk asynchronous copies (as in
+// softmax_ce_staged_kernel) instead of being copied by the threads -- the
+// staging arithmetic was about half of the narrow kernel's instructions.  A stage
+// holds kNrRows rows exactly as they lie in memory (row stride C); a thread
+// takes rows t, t + 128, ...  With stride C the thread-per-row reads conflict
+// gcd(C, 32) ways, so the launcher uses this kernel when that is at most 4.
+constexpr int kNrRows = 512;     // rows per stage
+constexpr int kNrStages = 3;
+
+template <int CP>
+__global__ void __launch_bounds__(kRowThreads) softmax_ce_rows_staged_kernel(const SmceArgs a) {
+  constexpr int P2 = pow2_at_least(CP);
+  extern __shared__ __align__(128) unsigned char nr_raw[];
+  __shared__ uint64_t full[kNrStages];
+  __shared__ float sm32[32];
+  __shared__ float wsum[kRowThreads / 32][32];
+  __shared__ int failed;
+  const int C = a.C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t stage_floats = (size_t)kNrRows * C;
+  const size_t stage_bytes = stage_floats * sizeof(float) + (size_t)kNrRows * sizeof(len_t);  // logits, then the rows' labels
+  const size_t n_groups = (a.rows + kNrRows - 1) / kNrRows;
+  auto stage_logits = [&](int s) -> float* { return reinterpret_cast<float*>(nr_raw + (size_t)s * stage_bytes); };
+  auto stage_labels = [&](int s) -> len_t* { return reinterpret_cast<len_t*>(nr_raw + (size_t)s * stage_bytes + stage_floats * sizeof(float)); };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kNrStages; ++s) ac::mbar_init(&full[s], 1);
+    ac::mbar_fence_init();
+    failed = 0;
+  }
+  __syncthreads();
+  pdl_sync();
+  auto rows_of = [&](size_t g) -> int { const size_t r0 = g * kNrRows; return (int)((a.rows - r0) < (size_t)kNrRows ? (a.rows - r0) : (size_t)kNrRows); };
+  auto bulk_ok = [&](int nrows) -> bool { return ((size_t)nrows * C) % 4 == 0 && nrows % 2 == 0; };  // whole groups always; the ragged last one maybe not
+  auto issue_load = [&](size_t g, int s) {
+    const int nrows = rows_of(g);
+    if (!bulk_ok(nrows)) return;
+    const uint32_t bytes = (uint32_t)((size_t)nrows * C * sizeof(float)), lbytes = (uint32_t)(nrows * sizeof(len_t));
+    ac::mbar_expect_tx(&full[s], bytes + lbytes);
+    ac::bulk_load(stage_logits(s), a.logits + g * stage_floats, bytes, &full[s]);
+    ac::bulk_load(stage_labels(s), static_cast<const len_t*>(a.labels) + g * (size_t)kNrRows, lbytes, &full[s]);
+  };
+  float gacc[P2];
+#pragma unroll
+  for (int j = 0; j < P2; ++j) gacc[j] = 0.f;
+  float loss_acc = 0.f;
+  if (threadIdx.x == 0) {
+    for (int k = 0; k < kNrStages - 1; ++k) {
+      const size_t g = blockIdx.x + (size_t)k * gridDim.x;
+      if (g < n_groups) issue_load(g, k);
+    }
+  }
+  size_t it = 0;
+  for (size_t g = blockIdx.x; g < n_groups; g += gridDim.x, ++it) {
+    const int s = (int)(it % kNrStages);
+    const int nrows = rows_of(g);
+    float* st = stage_logits(s);
+    len_t* lst = stage_labels(s);
+    if (threadIdx.x == 0) {
+      const size_t gn = g + (size_t)(kNrStages - 1) * gridDim.x;
+      if (gn < n_groups) {
+        ac::bulk_wait_read<0>();  // the store of the group that used that stage has finished reading it
+        issue_load(gn, (int)((it + kNrStages - 1) % kNrStages));
+      }
+    }
+    if (bulk_ok(nrows)) {
+      // (only the very last group can be ragged and skip the barrier, so the parity is a function of `it`)
+      if (!ac::mbar_wait(&full[s], (uint32_t)((it / kNrStages) & 1))) failed = 1;
+    } else {
+      const float* src = a.logits + g * stage_floats;
+      for (size_t e = threadIdx.x; e < (size_t)nrows * C; e += kRowThreads) st[e] = src[e];
+      for (int e = threadIdx.x; e < nrows; e += kRowThreads) lst[e] = static_cast<const len_t*>(a.labels)[g * (size_t)kNrRows + e];
+    }
+    __syncthreads();
+    if (failed) break;
+    for (int rr = threadIdx.x; rr < nrows; rr += kRowThreads) {
+      float* xs = st + (size_t)rr * C;
+      float d[CP], e[CP];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        d[j] = (j < C) ? xs[j] : -INFINITY;
+        mx = fmaxf(mx, d[j]);
+      }
+      const len_t l = lst[rr];
+      const int lab = l < (len_t)C ? (int)l : -1;
+      const float dlab = lab >= 0 ? xs[lab] - mx : 0.f;
+      float se = 0.f;
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        e[j] = fast_exp(d[j] - mx);
+        se += e[j];
+      }
+      const float lse = logf(se);
+      if (lab >= 0) loss_acc -= clamp_logp(dlab - lse);
+      const float sc = (1.f / se) * a.inv_divisor;
+#pragma unroll
+      for (int j = 0; j < CP; ++j) {
+        if (j < C) {
+          float gv = e[j] * sc;
+          if (j == lab) gv -= a.inv_divisor;
+          gacc[j] += gv;
+          xs[j] = gv;
+        }
+      }
+    }
+    if (bulk_ok(nrows) && (reinterpret_cast<uintptr_t>(a.dlogits) & 15u) == 0) {
+      ac::fence_async_smem();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        ac::bulk_store(a.dlogits + g * stage_floats, st, (uint32_t)((size_t)nrows * C * sizeof(float)));
+        ac::bulk_commit();
+      }
+    } else {
+      __syncthreads();
+      float* dst = a.dlogits + g * stage_floats;
+      for (size_t e2 = threadIdx.x; e2 < (size_t)nrows * C; e2 += kRowThreads) dst[e2] = st[e2];
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) {
+    ac::bulk_wait_all<0>();
+    if (failed) *a.counter_error = 1;
+  }
+  if (a.dbias) {
+#pragma unroll
+    for (int off = P2 / 2; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int j = 0; j < off; ++j) {
+        const float send = upper ? gacc[j] : gacc[j + off];
+        const float keep = upper ? gacc[j + off] : gacc[j];
+        gacc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= P2; off >>= 1) gacc[0] += __shfl_xor_sync(0xffffffffu, gacc[0], off);
+    wsum[warp][lane] = gacc[0];
+    __syncthreads();
+    if ((int)threadIdx.x < C) {
+      float sres = 0.f;
+      for (int w = 0; w < kRowThreads / 32; ++w) sres += wsum[w][threadIdx.x];
+      a.partial[gridDim.x + (size_t)blockIdx.x * C + threadIdx.x] = sres;
+    }
+  }
+  smce_finish(a, loss_acc, sm32);
+}
+
 // Rows wider than 1024: three passes over the row (values come back from L1/L2).
 template <bool INDEX_LABELS>
 __global__ void __launch_bounds__(kLThreads) softmax_ce_wide_kernel(const SmceArgs a) {
@@ -768,11 +923,11 @@ static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   int group_rows = (int)((size_t)65536 / ((size_t)a.ld * sizeof(float)));
   group_rows = group_rows / (kWarps * ROWS) * (kWarps * ROWS);
   if (group_rows < kWarps * ROWS) group_rows = kWarps * ROWS;
-  const size_t smem = (size_t)kStStages * group_rows * a.ld * sizeof(float);
+  const size_t smem = (size_t)kStStages * ((size_t)group_rows * a.ld * sizeof(float) + (size_t)group_rows * sizeof(len_t));
   auto kern = softmax_ce_staged_kernel<ITEMS, ROWS>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))) return;
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024))) return;
     attr_set = true;
   }
   const size_t n_groups = (a.rows + group_rows - 1) / group_rows;
@@ -790,6 +945,33 @@ static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
 
+template <int CP>
+static void launch_smce_rows_staged(cudaStream_t s, SmceArgs a) {
+  const int C = a.C;
+  const size_t smem = (size_t)kNrStages * ((size_t)kNrRows * C * sizeof(float) + (size_t)kNrRows * sizeof(len_t));
+  auto kern = softmax_ce_rows_staged_kernel<CP>;
+  static bool attr_set = false;
+  static unsigned per_sm = 1;
+  if (!attr_set) {
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024))) return;
+    attr_set = true;
+  }
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kRowThreads, smem) != cudaSuccess || occ < 1) { (void)cudaGetLastError(); occ = 1; }
+  per_sm = (unsigned)occ;
+  const size_t n_groups = (a.rows + kNrRows - 1) / kNrRows;
+  const unsigned g = (unsigned)std::min<size_t>(n_groups, (size_t)sm_count() * per_sm);
+  unsigned* counters = nullptr;
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * ((size_t)g + (a.dbias ? (size_t)g * C : 0)), &counters));
+  if (!partial) return;
+  a.partial = partial;
+  a.counter = counters;
+  a.fold_bias_inline = 1;
+  a.counter_error = reinterpret_cast<unsigned*>(kernel_timeout_flag());
+  if (!a.counter_error) return;
+  launch_pdl(kern, dim3(g), dim3(kRowThreads), smem, s, a);
+}
+
 template <bool IDX>
 static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
   const int C = a.C;
@@ -800,13 +982,27 @@ static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
 #define ZG_ROWS(CPV) return fast ? launch_smce_rows<CPV, IDX, true>(s, a) : launch_smce_rows<CPV, IDX, false>(s, a)
 #define ZG_WARPS(I, R) return fast ? launch_smce_warps<I, R, IDX, true>(s, a) : launch_smce_warps<I, R, IDX, false>(s, a)
   // large index-label problems with unpadded, 16-byte aligned rows: the staged kernel
-  if (IDX && fast && C > 32 && C <= 1024 && C % 4 == 0 && a.ld == (size_t)C && host_aligned16(a.logits) && host_aligned16(a.dlogits) &&
+  if (IDX && fast && C > 32 && C <= 1024 && C % 4 == 0 && a.ld == (size_t)C && host_aligned16(a.logits) && host_aligned16(a.dlogits) && host_aligned16(a.labels) &&
       a.rows * (size_t)C >= ((size_t)1 << 20) && (size_t)kStStages * 16 * C * sizeof(float) <= 196 * 1024) {
     if (C <= 64) return launch_smce_staged<2, 8>(s, a);
     if (C <= 128) return launch_smce_staged<4, 4>(s, a);
     if (C <= 256) return launch_smce_staged<8, 2>(s, a);
     if (C <= 512) return launch_smce_staged<16, 1>(s, a);
     return launch_smce_staged<32, 1>(s, a);
+  }
+  // narrow rows at scale: the bulk-copy ring (see softmax_ce_rows_staged_kernel for the conditions)
+  {
+    int gcd = C, b32 = 32;
+    while (b32) { const int t = gcd % b32; gcd = b32; b32 = t; }
+    if (IDX && fast && C <= 32 && a.ld == (size_t)C && gcd <= 4 && host_aligned16(a.logits) && host_aligned16(a.dlogits) && host_aligned16(a.labels) &&
+        a.rows * (size_t)C >= ((size_t)1 << 20)) {
+      if (C <= 4) return launch_smce_rows_staged<4>(s, a);
+      if (C <= 8) return launch_smce_rows_staged<8>(s, a);
+      if (C <= 12) return launch_smce_rows_staged<12>(s, a);
+      if (C <= 16) return launch_smce_rows_staged<16>(s, a);
+      if (C <= 24) return launch_smce_rows_staged<24>(s, a);
+      return launch_smce_rows_staged<32>(s, a);
+    }
   }
   if (C <= 4) ZG_ROWS(4);
   if (C <= 8) ZG_ROWS(8);
