@@ -373,7 +373,9 @@ def test_softmax_ce_fast_paths_large_index_labels(gpu, rows, C):
     G, Ls, Bg = d.from_numpy(np.full((rows, C), 7.0, np.float32)), d.from_numpy(np.zeros(1, np.float32)), d.from_numpy(np.ones(C, np.float32))
     d.dispatch(opspec.softmax_ce(X, T, rows, C, Ls, G, div, False, None, 0, Bg))
     got_g, got_l, got_b = d.to_numpy(G, (rows, C)), float(d.to_numpy(Ls)[0]), d.to_numpy(Bg)
-    assert abs(got_l - wl) <= 2e-5 * abs(wl), (got_l, wl)
+    # the host loop adds up to 300 000 row losses one after the other in fp32 (rounding ~ sqrt(rows) * 6e-8
+    # relative); the device folds per-thread and per-CTA partial sums: 1e-4, the bound of the hot path
+    assert abs(got_l - wl) <= 1e-4 * abs(wl), (got_l, wl)
     assert rel_err(got_g, wg) <= 1e-5, rel_err(got_g, wg)
     assert rel_err(got_b, wg.astype(np.float64).sum(0)) <= 1e-4
     for s in (X, T, G, Ls, Bg):
