@@ -356,7 +356,8 @@ def test_plan_api_of_the_reference_shim(gpu):
 
 
 @pytest.mark.parametrize("rows,C", [(3000, 1000), (20011, 64), (4100, 256), (2500, 512), (9000, 128),
-                                     (120003, 10), (300000, 4), (70001, 16), (50000, 28), (150001, 7)])
+                                     (120003, 10), (300000, 4), (70001, 16), (50000, 28), (150001, 7),
+                                     (30001, 36), (12001, 100), (22003, 48)])
 def test_softmax_ce_fast_paths_large_index_labels(gpu, rows, C):
     """The FAST form (index labels, power-of-two divisor, gradient written,
     bias gradient fused) at sizes that take the staged kernel; the last row group

@@ -125,6 +125,13 @@ __device__ __forceinline__ float clamp_logp(float lp) { return fminf(fmaxf(lp, k
 // exponential (relative error about 2^-22 plus 2^-24 |d| from the rounded
 // product; the softmax that comes out agrees with an exact one to ~1e-6)
 __device__ __forceinline__ float fast_exp(float d) { return __expf(d); }
+// exp(x - m) as 2^(x log2(e) - m log2(e)): one fused multiply-add and one ex2.approx (nm2 = -m log2(e))
+constexpr float kLog2e = 1.4426950408889634f;
+__device__ __forceinline__ float fast_exp_shifted(float x, float nm2) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(x, kLog2e, nm2)));
+  return r;
+}
 
 // FAST: dlogits written (not accumulated), no probabilities wanted, divisor a power of two
 template <bool FAST>
@@ -256,7 +263,14 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
 constexpr int kStThreads = 512;
 constexpr int kStStages = 3;
 
-template <int ITEMS, int ROWS>
+//
+// SUBL > 0 selects the sub-warp form for rows of up to 128 columns: SUBL lanes
+// (8 or 16) share a row, each holding 8 consecutive columns (two 128-bit
+// shared-memory accesses), a warp works on 32 / SUBL rows at once and the row
+// reductions take log2(SUBL) shuffle rounds for all of them together; the
+// lane-per-column form spends 10 shuffles on every 64-column row and is bound
+// by the shuffle/shared-memory pipe there.  ROWS must then be 32 / SUBL.
+template <int ITEMS, int ROWS, int SUBL = 0>
 __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const SmceArgs a, const int group_rows) {
   extern __shared__ __align__(128) unsigned char st_raw[];
   __shared__ uint64_t full[kStStages];
@@ -292,9 +306,10 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
     ac::bulk_load(stage_labels(s), static_cast<const len_t*>(a.labels) + g * (size_t)group_rows, lbytes, &full[s]);
   };
   float loss_acc = 0.f;
-  float bias_acc[ITEMS];
+  constexpr int kAcc = SUBL > 0 ? 8 : ITEMS;
+  float bias_acc[kAcc];
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) bias_acc[i] = 0.f;
+  for (int i = 0; i < kAcc; ++i) bias_acc[i] = 0.f;
   // prologue: the first kStStages - 1 groups of this CTA
   if (threadIdx.x == 0) {
     for (int k = 0; k < kStStages - 1; ++k) {
@@ -326,6 +341,61 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
     __syncthreads();
     if (failed) break;
     // ---- the rows of this stage, ROWS per warp and trip, in place
+    if constexpr (SUBL > 0) {
+      static_assert(ROWS * SUBL == 32, "sub-warp form: ROWS == 32 / SUBL");
+      const int sub = lane / SUBL, c0 = (lane % SUBL) * 8;
+      for (int r0 = warp * ROWS; r0 < nrows; r0 += kWarps * ROWS) {
+        const int r = r0 + sub;
+        const bool ok = r < nrows;
+        float* xr = st + (size_t)(ok ? r : 0) * ld + c0;
+        const bool v0 = ok && c0 < C, v1 = ok && c0 + 4 < C;  // C % 4 == 0: a quad lies wholly inside or outside the row
+        const float4 q0 = v0 ? *reinterpret_cast<const float4*>(xr) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        const float4 q1 = v1 ? *reinterpret_cast<const float4*>(xr + 4) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        float x[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        int lab = -1;
+        if (ok) {
+          const len_t l = lst[r];
+          lab = l < (len_t)C ? (int)l : -1;
+        }
+        float m = x[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, x[i]);
+#pragma unroll
+        for (int o = SUBL / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (!ok) m = 0.f;  // an idle row slot: keep the arithmetic finite
+        const bool owner = lab >= c0 && lab < c0 + 8;
+        const float dlab = owner ? st[(size_t)r * ld + lab] - m : 0.f;
+        float se = 0.f;
+        const float nm2 = -m * kLog2e;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[i] = fast_exp_shifted(x[i], nm2);
+          se += x[i];
+        }
+#pragma unroll
+        for (int o = SUBL / 2; o > 0; o >>= 1) se += __shfl_xor_sync(0xffffffffu, se, o);
+        if (ok) {
+          if (owner) loss_acc -= clamp_logp(dlab - __logf(se));
+          const float sc = __fdividef(a.inv_divisor, se);
+          const int li = lab - c0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x[i] *= sc;
+            if (i == li) x[i] -= a.inv_divisor;
+          }
+          if (v0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) bias_acc[i] += x[i];
+            *reinterpret_cast<float4*>(xr) = make_float4(x[0], x[1], x[2], x[3]);
+          }
+          if (v1) {
+#pragma unroll
+            for (int i = 4; i < 8; ++i) bias_acc[i] += x[i];
+            *reinterpret_cast<float4*>(xr + 4) = make_float4(x[4], x[5], x[6], x[7]);
+          }
+        }
+      }
+    } else
     for (int r0 = warp * ROWS; r0 < nrows; r0 += kWarps * ROWS) {
       float x[ROWS][ITEMS];
       float mx[ROWS], se[ROWS];
@@ -362,9 +432,10 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
         float sacc = 0.f;
         dlab[k] = 0.f;
         if (lab[k] >= 0 && (lab[k] & 31) == lane) dlab[k] = st[(size_t)(r0 + k) * ld + lab[k]] - mx[k];
+        const float nm2 = -mx[k] * kLog2e;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-          x[k][i] = fast_exp(x[k][i] - mx[k]);
+          x[k][i] = fast_exp_shifted(x[k][i], nm2);
           sacc += x[k][i];
         }
         se[k] = sacc;
@@ -376,9 +447,9 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
 #pragma unroll
       for (int k = 0; k < ROWS; ++k) {
         if (r0 + k >= nrows) continue;
-        const float lse = logf(se[k]);
+        const float lse = __logf(se[k]);
         if (lab[k] >= 0 && (lab[k] & 31) == lane) loss_acc -= clamp_logp(dlab[k] - lse);
-        const float sc = (1.f / se[k]) * a.inv_divisor;
+        const float sc = __fdividef(a.inv_divisor, se[k]);
         float* out = st + (size_t)(r0 + k) * ld;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
@@ -414,13 +485,30 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
   }
   float* bias_partial = a.partial + gridDim.x;
   if (a.dbias) {
+    if constexpr (SUBL > 0) {
+      // the row slots of a warp hold the same columns: fold them onto slot 0 first
+#pragma unroll
+      for (int o = SUBL; o < 32; o <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bias_acc[i] += __shfl_xor_sync(0xffffffffu, bias_acc[i], o);
+    }
     // per-CTA column partials, warps in a fixed order
     for (int w = 0; w < kWarps; ++w) {
       if (warp == w) {
+        if constexpr (SUBL > 0) {
+          if (lane < SUBL) {
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-          const int j = lane + 32 * i;
-          if (j < C) colsum[j] = (w == 0 ? 0.f : colsum[j]) + bias_acc[i];
+            for (int i = 0; i < 8; ++i) {
+              const int j = lane * 8 + i;
+              if (j < C) colsum[j] = (w == 0 ? 0.f : colsum[j]) + bias_acc[i];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < ITEMS; ++i) {
+            const int j = lane + 32 * i;
+            if (j < C) colsum[j] = (w == 0 ? 0.f : colsum[j]) + bias_acc[i];
+          }
         }
       }
       __syncthreads();
@@ -915,7 +1003,7 @@ static void launch_smce_warps(cudaStream_t s, SmceArgs a) {
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
 
-template <int ITEMS, int ROWS>
+template <int ITEMS, int ROWS, int SUBL = 0>
 static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   const int C = a.C;
   constexpr int kWarps = kStThreads / 32;
@@ -924,7 +1012,7 @@ static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   group_rows = group_rows / (kWarps * ROWS) * (kWarps * ROWS);
   if (group_rows < kWarps * ROWS) group_rows = kWarps * ROWS;
   const size_t smem = (size_t)kStStages * ((size_t)group_rows * a.ld * sizeof(float) + (size_t)group_rows * sizeof(len_t));
-  auto kern = softmax_ce_staged_kernel<ITEMS, ROWS>;
+  auto kern = softmax_ce_staged_kernel<ITEMS, ROWS, SUBL>;
   static bool attr_set = false;
   if (!attr_set) {
     if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024))) return;
@@ -984,8 +1072,8 @@ static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
   // large index-label problems with unpadded, 16-byte aligned rows: the staged kernel
   if (IDX && fast && C > 32 && C <= 1024 && C % 4 == 0 && a.ld == (size_t)C && host_aligned16(a.logits) && host_aligned16(a.dlogits) && host_aligned16(a.labels) &&
       a.rows * (size_t)C >= ((size_t)1 << 20) && (size_t)kStStages * 16 * C * sizeof(float) <= 196 * 1024) {
-    if (C <= 64) return launch_smce_staged<2, 8>(s, a);
-    if (C <= 128) return launch_smce_staged<4, 4>(s, a);
+    if (C <= 64) return launch_smce_staged<4, 4, 8>(s, a);
+    if (C <= 128) return launch_smce_staged<4, 2, 16>(s, a);
     if (C <= 256) return launch_smce_staged<8, 2>(s, a);
     if (C <= 512) return launch_smce_staged<16, 1>(s, a);
     return launch_smce_staged<32, 1>(s, a);

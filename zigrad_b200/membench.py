@@ -93,7 +93,7 @@ def run(mib=1024, reps=10, only=None):
     dev.mem_cache_free(xb)
 
     # fused softmax + cross-entropy forward/backward over index labels
-    for C in (1000, 10, 64):
+    for C in (1000, 10, 64, 128):
         rows = n // C
         lab = dev.from_numpy(np.random.Generator(np.random.PCG64(C)).integers(0, C, rows).astype(np.uint64))
         lg = x.view(0, rows * C)
