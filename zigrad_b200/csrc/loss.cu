@@ -254,14 +254,23 @@ __global__ void __launch_bounds__(kLThreads) softmax_ce_kernel(const SmceArgs a)
 
 // Wide rows with index labels, staged: the logits travel through a ring of
 // shared-memory stages filled by bulk asynchronous copies (a group of whole rows
-// per stage, several groups in flight per SM regardless of how many registers
-// the math needs), each warp works on rows of the current stage in place, and
-// the gradient leaves through a bulk store of the same stage.  Memory latency
-// is hidden by the ring instead of by occupancy.  FAST form only (dlogits
-// written, power-of-two divisor, no probabilities); rows must be 16-byte
-// aligned (ld % 4 == 0, base aligned).
-constexpr int kStThreads = 512;
-constexpr int kStStages = 3;
+// and their labels per stage), each consumer warp works on rows of the current
+// stage in place, and the gradient leaves through a bulk store of the same
+// stage.  Memory latency is hidden by the ring instead of by occupancy.
+//
+// Roles: warps 0..15 compute; one lane of warp 16 drives the copies.  The
+// consumers of a stage wait on its `full` barrier (bytes landed), compute, make
+// their writes visible to the copy engine and arrive on its `done` barrier; the
+// copy lane waits on `done`, issues the bulk store, waits until the store has
+// read the stage and refills it with the group n_stages further on.  No
+// CTA-wide barrier sits on this path: warps run ahead into the next stage while
+// the previous one drains.  Whole groups only go through the ring; the ragged
+// last group of the problem is copied by the threads of one CTA after its ring.
+// FAST form only (dlogits written, power-of-two divisor, no probabilities);
+// unpadded rows (ld == C, C % 4 == 0) and 16-byte aligned bases.
+constexpr int kStThreads = 512;  // consumer threads
+constexpr int kStLaunchThreads = kStThreads + 32;
+constexpr int kStMaxStages = 8;
 
 //
 // SUBL > 0 selects the sub-warp form for rows of up to 128 columns: SUBL lanes
@@ -271,9 +280,9 @@ constexpr int kStStages = 3;
 // lane-per-column form spends 10 shuffles on every 64-column row and is bound
 // by the shuffle/shared-memory pipe there.  ROWS must then be 32 / SUBL.
 template <int ITEMS, int ROWS, int SUBL = 0>
-__global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const SmceArgs a, const int group_rows) {
+__global__ void __launch_bounds__(kStLaunchThreads, 1) softmax_ce_staged_kernel(const SmceArgs a, const int group_rows, const int n_stages) {
   extern __shared__ __align__(128) unsigned char st_raw[];
-  __shared__ uint64_t full[kStStages];
+  __shared__ uint64_t full[kStMaxStages], done[kStMaxStages];
   __shared__ float sm32[32];
   __shared__ float colsum[32 * ITEMS];
   __shared__ int failed;
@@ -284,63 +293,31 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
   const size_t stage_floats = (size_t)group_rows * ld;
   // a stage = the logits of a group of rows followed by their labels (u64 each)
   const size_t stage_bytes = stage_floats * sizeof(float) + (size_t)group_rows * sizeof(len_t);
-  const size_t n_groups = (a.rows + group_rows - 1) / group_rows;
+  const size_t n_full = a.rows / (size_t)group_rows;
+  const int tail_rows = (int)(a.rows - n_full * (size_t)group_rows);
+  const size_t my_groups = n_full > blockIdx.x ? (n_full - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   auto stage_logits = [&](int s) -> float* { return reinterpret_cast<float*>(st_raw + (size_t)s * stage_bytes); };
   auto stage_labels = [&](int s) -> len_t* { return reinterpret_cast<len_t*>(st_raw + (size_t)s * stage_bytes + stage_floats * sizeof(float)); };
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStStages; ++s) ac::mbar_init(&full[s], 1);
+    for (int s = 0; s < n_stages; ++s) {
+      ac::mbar_init(&full[s], 1);
+      ac::mbar_init(&done[s], kWarps);
+    }
     ac::mbar_fence_init();
     failed = 0;
   }
   __syncthreads();
   pdl_sync();
-  // rows of group g; a group whose byte count is not a multiple of 16 (the ragged last one) is copied by the threads
-  auto rows_of = [&](size_t g) -> int { const size_t r0 = g * group_rows; return (int)((a.rows - r0) < (size_t)group_rows ? (a.rows - r0) : (size_t)group_rows); };
-  auto bulk_ok = [&](int nrows) -> bool { return ((size_t)nrows * ld) % 4 == 0 && nrows % 2 == 0; };
-  auto issue_load = [&](size_t g, int s) {  // thread 0 only
-    const int nrows = rows_of(g);
-    if (!bulk_ok(nrows)) return;
-    const uint32_t bytes = (uint32_t)((size_t)nrows * ld * sizeof(float)), lbytes = (uint32_t)(nrows * sizeof(len_t));
-    ac::mbar_expect_tx(&full[s], bytes + lbytes);
-    ac::bulk_load(stage_logits(s), a.logits + g * (size_t)group_rows * ld, bytes, &full[s]);
-    ac::bulk_load(stage_labels(s), static_cast<const len_t*>(a.labels) + g * (size_t)group_rows, lbytes, &full[s]);
-  };
   float loss_acc = 0.f;
   constexpr int kAcc = SUBL > 0 ? 8 : ITEMS;
   float bias_acc[kAcc];
 #pragma unroll
   for (int i = 0; i < kAcc; ++i) bias_acc[i] = 0.f;
-  // prologue: the first kStStages - 1 groups of this CTA
-  if (threadIdx.x == 0) {
-    for (int k = 0; k < kStStages - 1; ++k) {
-      const size_t g = blockIdx.x + (size_t)k * gridDim.x;
-      if (g < n_groups) issue_load(g, k);
-    }
-  }
-  size_t it = 0;
-  for (size_t g = blockIdx.x; g < n_groups; g += gridDim.x, ++it) {
-    const int s = (int)(it % kStStages);
-    const int nrows = rows_of(g);
-    float* st = stage_logits(s);
-    len_t* lst = stage_labels(s);
-    if (threadIdx.x == 0) {
-      // refill the stage that group it-1 used: its bulk store must have finished reading it
-      const size_t gn = g + (size_t)(kStStages - 1) * gridDim.x;
-      if (gn < n_groups) {
-        ac::bulk_wait_read<0>();
-        issue_load(gn, (int)((it + kStStages - 1) % kStStages));
-      }
-    }
-    if (bulk_ok(nrows)) {
-      if (!ac::mbar_wait(&full[s], (uint32_t)((it / kStStages) & 1))) failed = 1;
-    } else {
-      const float* src = a.logits + g * (size_t)group_rows * ld;
-      for (size_t e = threadIdx.x; e < (size_t)nrows * ld; e += kStThreads) st[e] = src[e];
-      for (int e = threadIdx.x; e < nrows; e += kStThreads) lst[e] = static_cast<const len_t*>(a.labels)[g * (size_t)group_rows + e];
-    }
-    __syncthreads();
-    if (failed) break;
-    // ---- the rows of this stage, ROWS per warp and trip, in place
+  volatile int* failed_v = &failed;
+  const int warps_per_group = (group_rows + ROWS - 1) / ROWS < kWarps ? (group_rows + ROWS - 1) / ROWS : 0;
+
+  // ---- the rows [0, nrows) of one stage, ROWS per warp and trip, in place
+  auto compute_rows = [&](float* st, const len_t* lst, const int nrows, const int warp) {
     if constexpr (SUBL > 0) {
       static_assert(ROWS * SUBL == 32, "sub-warp form: ROWS == 32 / SUBL");
       const int sub = lane / SUBL, c0 = (lane % SUBL) * 8;
@@ -395,7 +372,7 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
           }
         }
       }
-    } else
+    } else {
     for (int r0 = warp * ROWS; r0 < nrows; r0 += kWarps * ROWS) {
       float x[ROWS][ITEMS];
       float mx[ROWS], se[ROWS];
@@ -463,26 +440,63 @@ __global__ void __launch_bounds__(kStThreads, 1) softmax_ce_staged_kernel(const 
         }
       }
     }
-    // ---- the stage leaves through one bulk store (the launcher takes unpadded rows only: ld == C)
-    if (bulk_ok(nrows) && (reinterpret_cast<uintptr_t>(a.dlogits) & 15u) == 0) {
-      ac::fence_async_smem();
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        ac::bulk_store(a.dlogits + g * (size_t)group_rows * ld, st, (uint32_t)((size_t)nrows * ld * sizeof(float)));
+    }
+  };
+
+  if (warp == kWarps) {
+    // ---- the copy lane
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)(stage_floats * sizeof(float)), lbytes = (uint32_t)((size_t)group_rows * sizeof(len_t));
+      auto issue_load = [&](size_t it) {
+        const size_t g = blockIdx.x + it * gridDim.x;
+        const int s = (int)(it % (size_t)n_stages);
+        ac::mbar_expect_tx(&full[s], bytes + lbytes);
+        ac::bulk_load(stage_logits(s), a.logits + g * stage_floats, bytes, &full[s]);
+        ac::bulk_load(stage_labels(s), static_cast<const len_t*>(a.labels) + g * (size_t)group_rows, lbytes, &full[s]);
+      };
+      for (size_t it = 0; it < (size_t)n_stages && it < my_groups; ++it) issue_load(it);
+      for (size_t it = 0; it < my_groups; ++it) {
+        const int s = (int)(it % (size_t)n_stages);
+        if (!ac::mbar_wait(&done[s], (uint32_t)((it / (size_t)n_stages) & 1))) { *failed_v = 1; break; }
+        if (*failed_v) break;
+        ac::bulk_store(a.dlogits + (blockIdx.x + it * gridDim.x) * stage_floats, stage_logits(s), bytes);
         ac::bulk_commit();
+        if (it + n_stages < my_groups) {
+          ac::bulk_wait_read<0>();  // the store has read the stage: it can take the next group
+          issue_load(it + n_stages);
+        }
       }
-    } else {
-      __syncthreads();
-      float* dst = a.dlogits + g * (size_t)group_rows * ld;
-      for (size_t e = threadIdx.x; e < (size_t)nrows * ld; e += kStThreads)
-        if ((int)(e % ld) < C) dst[e] = st[e];
-      __syncthreads();
+      ac::bulk_wait_all<0>();  // every store has landed before the CTA retires its shared memory
+    }
+  } else {
+    // ---- the consumers
+    for (size_t it = 0; it < my_groups; ++it) {
+      const int s = (int)(it % (size_t)n_stages);
+      if (!ac::mbar_wait(&full[s], (uint32_t)((it / (size_t)n_stages) & 1))) { *failed_v = 1; break; }
+      if (*failed_v) break;
+      // a group smaller than one trip of all warps: successive groups go to successive sets of warps
+      compute_rows(stage_logits(s), stage_labels(s), group_rows, (int)((warp + it * (size_t)warps_per_group) % kWarps));
+      ac::fence_async_smem();
+      __syncwarp();
+      if (lane == 0) ac::mbar_arrive(&done[s]);
     }
   }
-  if (threadIdx.x == 0) {
-    ac::bulk_wait_all<0>();  // every store has landed before the CTA retires its shared memory
-    if (failed) *a.counter_error = 1;
+  __syncthreads();
+  // ---- the ragged last group: one CTA, plain loads and stores through stage 0
+  if (tail_rows > 0 && blockIdx.x == (unsigned)(n_full % gridDim.x) && !failed) {
+    float* st = stage_logits(0);
+    len_t* lst = stage_labels(0);
+    const size_t first = n_full * (size_t)group_rows;
+    const float* src = a.logits + first * ld;
+    for (size_t e = threadIdx.x; e < (size_t)tail_rows * ld; e += blockDim.x) st[e] = src[e];
+    for (int e = threadIdx.x; e < tail_rows; e += blockDim.x) lst[e] = static_cast<const len_t*>(a.labels)[first + e];
+    __syncthreads();
+    if (warp < kWarps) compute_rows(st, lst, tail_rows, warp);
+    __syncthreads();
+    float* dst = a.dlogits + first * ld;
+    for (size_t e = threadIdx.x; e < (size_t)tail_rows * ld; e += blockDim.x) dst[e] = st[e];
   }
+  if (threadIdx.x == 0 && failed) *a.counter_error = 1;
   float* bias_partial = a.partial + gridDim.x;
   if (a.dbias) {
     if constexpr (SUBL > 0) {
@@ -1007,11 +1021,24 @@ template <int ITEMS, int ROWS, int SUBL = 0>
 static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   const int C = a.C;
   constexpr int kWarps = kStThreads / 32;
-  // rows per stage: about 64 KB, a multiple of what the warps take per trip
-  int group_rows = (int)((size_t)65536 / ((size_t)a.ld * sizeof(float)));
-  group_rows = group_rows / (kWarps * ROWS) * (kWarps * ROWS);
-  if (group_rows < kWarps * ROWS) group_rows = kWarps * ROWS;
-  const size_t smem = (size_t)kStStages * ((size_t)group_rows * a.ld * sizeof(float) + (size_t)group_rows * sizeof(len_t));
+  // rows per stage: about 32 KB (small stages keep the copies flowing smoothly), whole trips of
+  // all warps, or for wide rows a power-of-two fraction of one trip; four stages (measured best: 32 KB x 4)
+  static const size_t stage_target = [] { const char* e = getenv("ZG_SMCE_STAGE_KB"); return (size_t)(e ? atoi(e) : 32) * 1024; }();
+  static const int max_stages = [] { const char* e = getenv("ZG_SMCE_STAGES"); const int v = e ? atoi(e) : 4; return v < 2 ? 2 : (v > kStMaxStages ? kStMaxStages : v); }();
+  const size_t row_bytes = (size_t)a.ld * sizeof(float);
+  constexpr int kTrip = kWarps * ROWS;
+  int group_rows = (int)(stage_target / row_bytes);
+  if (group_rows >= kTrip) {
+    group_rows = group_rows / kTrip * kTrip;
+  } else {
+    int gr = kTrip;
+    while (gr > 2 && gr > ROWS && (size_t)gr * row_bytes > stage_target) gr /= 2;
+    group_rows = gr;
+  }
+  const size_t stage_bytes = (size_t)group_rows * row_bytes + (size_t)group_rows * sizeof(len_t);
+  int n_stages = (int)std::min<size_t>((size_t)max_stages, ((size_t)200 * 1024) / stage_bytes);
+  if (n_stages < 2) { set_error(kUnsupported, "zg_softmax_ce_fwd_bwd: rows too wide for the staged kernel"); return; }
+  const size_t smem = (size_t)n_stages * stage_bytes;
   auto kern = softmax_ce_staged_kernel<ITEMS, ROWS, SUBL>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -1029,7 +1056,7 @@ static void launch_smce_staged(cudaStream_t s, SmceArgs a) {
   a.fold_bias_inline = separate_fold ? 0 : 1;
   a.counter_error = reinterpret_cast<unsigned*>(kernel_timeout_flag());
   if (!a.counter_error) return;
-  if (!launch_pdl(kern, dim3(g), dim3(kStThreads), smem, s, a, group_rows)) return;
+  if (!launch_pdl(kern, dim3(g), dim3(kStLaunchThreads), smem, s, a, group_rows, n_stages)) return;
   if (separate_fold) fold_rows_f32(s, partial + g, a.dbias, g, (size_t)C);
 }
 
@@ -1071,7 +1098,7 @@ static void launch_softmax_ce(cudaStream_t s, SmceArgs a) {
 #define ZG_WARPS(I, R) return fast ? launch_smce_warps<I, R, IDX, true>(s, a) : launch_smce_warps<I, R, IDX, false>(s, a)
   // large index-label problems with unpadded, 16-byte aligned rows: the staged kernel
   if (IDX && fast && C > 32 && C <= 1024 && C % 4 == 0 && a.ld == (size_t)C && host_aligned16(a.logits) && host_aligned16(a.dlogits) && host_aligned16(a.labels) &&
-      a.rows * (size_t)C >= ((size_t)1 << 20) && (size_t)kStStages * 16 * C * sizeof(float) <= 196 * 1024) {
+      a.rows * (size_t)C >= ((size_t)1 << 20) && (size_t)2 * 2 * C * (sizeof(float) + 2) <= 196 * 1024) {
     if (C <= 64) return launch_smce_staged<4, 4, 8>(s, a);
     if (C <= 128) return launch_smce_staged<4, 2, 16>(s, a);
     if (C <= 256) return launch_smce_staged<8, 2>(s, a);
