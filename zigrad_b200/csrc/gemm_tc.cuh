@@ -6,14 +6,21 @@
 // Roles inside the CTA (8 warps):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and B
 //               k-slabs into a ring of shared-memory stages (128-byte swizzle)
-//   warp 1      MMA issuer: one elected thread issues tcgen05.mma with the
-//               accumulator in tensor memory; also owns the TMEM allocation
+//   warp 1      MMA issuer: the whole warp walks the k loop (so waits and
+//               descriptor arithmetic stay warp-uniform; a loop run by a single
+//               lane measured 55 cycles per tcgen05.mma issued against 20 this
+//               way), one elected lane issues tcgen05.mma with the accumulator
+//               in tensor memory; also owns the TMEM allocation
 //   warps 2-7   FP32X3 mode only: for every fp32 operand slab write the
 //               remainder lo = x - tf32(x) to a second buffer.  The MMA reads
 //               only the top 19 bits of an fp32 word (measured: results do not
 //               change when the low 13 bits are cleared first), so the fetched
 //               slab itself serves as "hi" and Ahi*Bhi + Alo*Bhi + Ahi*Blo
-//               recovers fp32-level accuracy
+//               recovers fp32-level accuracy.  With a K-major A (hi and lo of A
+//               go to tensor memory) and tiles of up to 64 columns, warps 4-7
+//               split A, warps 2-3 most of B, each fetching its part of the
+//               next slab before it hands the current one over; one mbarrier
+//               arrival per warp
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator (warp q reads TMEM
 //               lanes 32q..32q+31, one row per thread), alpha/beta/bias/ReLU/
 //               mask in registers, 128-bit row-contiguous global accesses
@@ -104,6 +111,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase (try_wait may suspend the thread for a while when the phase is
+// still open; a look-ahead must not)
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and raises *failed) when the limit is hit or
 // another role already failed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
@@ -157,6 +177,12 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+// One lane of a converged warp (the same lane every time for the full mask)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 // mbarrier arrives once all previously issued MMAs of this thread are done
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -403,6 +429,10 @@ struct SmemLayout {
   static constexpr int kTmemNeed = ATM ? kAccCols + kATmemCols * kStages : kAccCols;
   static constexpr int kTmemCols = kTmemNeed <= 32 ? 32 : (kTmemNeed <= 64 ? 64 : (kTmemNeed <= 128 ? 128 : (kTmemNeed <= 256 ? 256 : 512)));
   static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // ATM: 16-byte words of a B slab per thread of the two B warps / of the four A warps
+  // (BN 128: 8 + 4, BN 64: 6 + 1, BN 32: 4 + 0; 64 * kBWordsB + 128 * kBWordsA = BN * 8)
+  static constexpr int kBWordsA = BN >= 128 ? 4 : (BN >= 64 ? 1 : 0);
+  static constexpr int kBWordsB = (BN * 8 - 128 * kBWordsA) / 64;
 };
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE, bool ATM = false>
@@ -440,7 +470,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     failed = 0;
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&ready[s], kSplitThreads);
+      mbar_init(&ready[s], kSplitThreads / 32);  // one arrival per split warp
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
@@ -488,10 +518,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (waits and descriptor arithmetic stay
+    // warp-uniform); one elected lane issues the MMAs and their commit.
+    // The barrier of the next slab is polled once before this slab's MMAs go
+    // out, so that in steady state no wait sits between two slabs.
+    {
+      bool have = false;
       for (int kt = 0; kt < KT; ++kt) {
         const int s = kt % S;
-        if (!mbar_wait(X3 ? &ready[s] : &full[s], (kt / S) & 1, &failed)) break;
+        if (!have) {
+          const bool got = mbar_wait(X3 ? &ready[s] : &full[s], (kt / S) & 1, &failed);
+          if (!__all_sync(0xffffffffu, got)) break;
+        }
+        bool next_seen = false;  // consumed after the MMAs of this slab are out
+        if (kt + 1 < KT) {
+          const int s1 = (kt + 1) % S;
+          next_seen = mbar_test(X3 ? &ready[s1] : &full[s1], ((kt + 1) / S) & 1);
+        }
         tc_fence_after();
         uint8_t* st = stage_base + s * SL::kStageBytes;
         const uint32_t a_hi = smem_u32(st), a_lo = a_hi + SL::kABytes;
@@ -508,6 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         constexpr uint32_t a_h32 = desc_hi32(a_lay == 1u ? 512u : 1024u, a_lay), b_h32 = desc_hi32(b_lay == 1u ? 512u : 1024u, b_lay);
         const uint32_t da0 = desc_lo32(a_hi, a_lbo), dal0 = desc_lo32(a_lo, a_lbo);
         const uint32_t db0 = desc_lo32(b_hi, b_lbo), dbl0 = desc_lo32(b_lo, b_lbo);
+        if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk) {
           const uint64_t db = desc_pack(db0 + kk * b_step, b_h32);
@@ -531,14 +575,123 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+        }
+        have = __all_sync(0xffffffffu, next_seen);
       }
-      umma_commit(accum);
+      if (elect_one()) umma_commit(accum);
     }
   } else if (X3) {
     // ------------------------------------------- hi/lo split (warps 2..7)
     const int t = threadIdx.x - 64;
     const bool a_warp = warp >= 4;  // ATM: the four warps that cover the TMEM lane quadrants (warp % 4)
     constexpr int NT = kSplitThreads;
+    // Narrow tiles run the pipelined role loops below; with BN = 128 the MMAs' operand reads load the
+    // shared-memory pipe so heavily that the plain lock-step split measured faster.
+    constexpr bool PIPE = ATM && BN <= 64;
+    if (PIPE && a_warp) {
+      // Four warps (TMEM lane quadrant = warp % 4), thread = row of the A slab.  The row's eight
+      // 16-byte chunks sit at chunk position c ^ (row % 8) (128-byte swizzle); hi = the fetched
+      // word itself, lo = x - tf32(x); both go to tensor memory.  The row of the NEXT slab is
+      // fetched while the stores of this one drain, so a warp's chain per slab is
+      // split -> store -> (load next) -> wait -> arrive.
+      const int row = (warp & 3) * 32 + lane;
+      const uint32_t ta0 = tmem_d + SL::kAccCols + ((uint32_t)((warp & 3) * 32) << 16);
+      float4 v[8];
+      bool have = false;
+      auto load_row = [&](int stage) {
+        const uint8_t* rp = stage_base + stage * SL::kStageBytes + row * kSlabBytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(rp + ((c ^ (row & 7)) << 4));
+      };
+      for (int kt = 0; kt < KT; ++kt) {
+        const int s = kt % S;
+        if (!have) {
+          const bool got = mbar_wait(&full[s], (kt / S) & 1, &failed);
+          if (!__all_sync(0xffffffffu, got)) break;
+          load_row(s);
+        }
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float x[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t h = __float_as_uint(x[e]) & 0xFFFFE000u;
+            hi[4 * c + e] = __float_as_uint(x[e]);
+            lo[4 * c + e] = __float_as_uint(x[e] - __uint_as_float(h));
+          }
+        }
+        const uint32_t ta = ta0 + (uint32_t)s * SL::kATmemCols;
+        tmem_st32(ta, hi);
+        tmem_st32(ta + 32, lo);
+        if constexpr (SL::kBWordsA > 0) {
+          // this warp's share of the B split (the words after those of the two B warps)
+          float4* bh = reinterpret_cast<float4*>(stage_base + s * SL::kStageBytes + SL::kABytes);
+          float4* bl = bh + SL::kBBytes / 16;
+#pragma unroll
+          for (int j = 0; j < SL::kBWordsA; ++j) {
+            const int i = 64 * SL::kBWordsB + (threadIdx.x - 128) + 128 * j;
+            const float4 b = bh[i];
+            float4 l;
+            l.x = b.x - __uint_as_float(__float_as_uint(b.x) & 0xFFFFE000u);
+            l.y = b.y - __uint_as_float(__float_as_uint(b.y) & 0xFFFFE000u);
+            l.z = b.z - __uint_as_float(__float_as_uint(b.z) & 0xFFFFE000u);
+            l.w = b.w - __uint_as_float(__float_as_uint(b.w) & 0xFFFFE000u);
+            bl[i] = l;
+          }
+        }
+        have = false;
+        if (kt + 1 < KT) {
+          const int s1 = (kt + 1) % S;
+          have = __all_sync(0xffffffffu, mbar_test(&full[s1], ((kt + 1) / S) & 1));
+          if (have) load_row(s1);
+        }
+        if constexpr (SL::kBWordsA > 0) fence_async_smem();
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[s]);
+      }
+    } else if (PIPE) {
+      // The two other warps split B: lo = x - tf32(x) into the second B buffer of the stage.
+      // Like the A warps they fetch the next slab's part before they hand this one over.
+      constexpr int NB = SL::kBWordsB;  // 16-byte words per thread and slab
+      float4 v[NB];
+      bool have = false;
+      auto b_hi_of = [&](int stage) { return reinterpret_cast<float4*>(stage_base + stage * SL::kStageBytes + SL::kABytes); };
+      auto load_b = [&](int stage) {
+        const float4* src = b_hi_of(stage);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) v[j] = src[t + 64 * j];
+      };
+      for (int kt = 0; kt < KT; ++kt) {
+        const int s = kt % S;
+        if (!have) {
+          const bool got = mbar_wait(&full[s], (kt / S) & 1, &failed);
+          if (!__all_sync(0xffffffffu, got)) break;
+          load_b(s);
+        }
+        float4* dst = b_hi_of(s) + SL::kBBytes / 16;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          float4 l;
+          l.x = v[j].x - __uint_as_float(__float_as_uint(v[j].x) & 0xFFFFE000u);
+          l.y = v[j].y - __uint_as_float(__float_as_uint(v[j].y) & 0xFFFFE000u);
+          l.z = v[j].z - __uint_as_float(__float_as_uint(v[j].z) & 0xFFFFE000u);
+          l.w = v[j].w - __uint_as_float(__float_as_uint(v[j].w) & 0xFFFFE000u);
+          dst[t + 64 * j] = l;
+        }
+        have = false;
+        if (kt + 1 < KT) {
+          const int s1 = (kt + 1) % S;
+          have = __all_sync(0xffffffffu, mbar_test(&full[s1], ((kt + 1) / S) & 1));
+          if (have) load_b(s1);
+        }
+        fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[s]);
+      }
+    } else
     for (int kt = 0; kt < KT; ++kt) {
       const int s = kt % S;
       if (!mbar_wait(&full[s], (kt / S) & 1, &failed)) break;
@@ -548,10 +701,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float4* b_hi = reinterpret_cast<float4*>(st + (ATM ? SL::kABytes : SL::kABytes * 2));
       float4* b_lo = b_hi + SL::kBBytes / 16;
       if constexpr (ATM) {
-        // Four warps of the group (TMEM lane quadrant = warp % 4): thread = row of the A slab.  The row's
-        // eight 16-byte chunks sit at chunk position c ^ (row % 8) (128-byte swizzle);
-        // hi = the fetched word itself, lo = x - tf32(x); both go to tensor memory.
-        if (a_warp) {
+        if (a_warp) {  // thread = row of the A slab, as in the pipelined loop above
           const int row = (warp & 3) * 32 + lane;
           const uint8_t* rp = st + row * kSlabBytes;
           uint32_t hi[32], lo[32];
@@ -595,7 +745,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         b_lo[i] = l;
       }
       fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-      mbar_arrive(&ready[s]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ready[s]);
     }
   }
 
