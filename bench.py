@@ -45,8 +45,8 @@ SEED = 81761  # the reference's global seed (src/zigrad.zig:66)
 METRIC = "train samples/sec (fwd+bwd+SGD)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of the
 # same full-size launches (the eight GEMMs of one eager step, ncu --set full); batch 8192 only
-NCU_DRAM_TRAFFIC = {"layer-1 forward GEMM+bias+ReLU [B,784]x[128,784]^T": 26165248,
-                    "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]": 30363392}
+NCU_DRAM_TRAFFIC = {"layer-1 forward GEMM+bias+ReLU [B,784]x[128,784]^T": 26165504,
+                    "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]": 30362624}
 
 
 def make_batch(B, seed):

@@ -179,40 +179,55 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loops (waits and descriptor arithmetic stay
+    // warp-uniform), one elected lane issues the MMAs and the commits; the
+    // barrier of the next ring position is tested before this slab's MMAs go out.
+    {
       uint32_t it = 0, tcount = 0;
-      bool ok = true;
+      bool ok = true, have = false;
       for (; ok; ++tcount) {
         const int j = (int)(tcount % kSchedDepth);
-        if (!mbar_wait(&sched_full[j], (tcount / kSchedDepth) & 1, &failed)) break;
+        bool got = mbar_wait(&sched_full[j], (tcount / kSchedDepth) & 1, &failed);
+        if (!__all_sync(0xffffffffu, got)) break;
         const uint32_t t = sched_tile[j];
-        mbar_arrive(&sched_empty[j]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sched_empty[j]);
         if (t == kNoTile) break;
         const uint32_t buf = tcount & 1;
-        if (tcount >= 2 && !mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1) ^ 1, &failed)) break;
+        if (tcount >= 2) {
+          got = mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1) ^ 1, &failed);
+          if (!__all_sync(0xffffffffu, got)) break;
+        }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         const int KT = slabs_of(tile_coord(t, tiles_m, tiles_n, p.splits).split);
         for (int kt = 0; kt < KT; ++kt, ++it) {
           const int s = (int)(it % S);
-          if (!mbar_wait(&full[s], (it / S) & 1, &failed)) { ok = false; break; }
+          if (!have) {
+            got = mbar_wait(&full[s], (it / S) & 1, &failed);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+          }
+          const uint32_t it1 = it + 1;
+          const bool next_seen = mbar_test(&full[it1 % S], (it1 / S) & 1);
           tc_fence_after();
           const uint32_t a_s = smem_u32(smem + s * SL::kStageBytes), b_s = a_s + SL::kABytes;
+          constexpr uint32_t a_step = (A_KMAJOR ? 32u : (uint32_t)(MT::kUmmaK * kSlabBytes)) >> 4;
+          constexpr uint32_t b_step = (B_KMAJOR ? 32u : (uint32_t)(MT::kUmmaK * kSlabBytes)) >> 4;
+          constexpr uint32_t a_lbo = A_KMAJOR ? 16u : (uint32_t)(MT::kBK * kSlabBytes);
+          constexpr uint32_t b_lbo = B_KMAJOR ? 16u : (uint32_t)(MT::kBK * kSlabBytes);
+          constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
+          constexpr uint32_t a_h32 = desc_hi32(a_lay == 1u ? 512u : 1024u, a_lay), b_h32 = desc_hi32(b_lay == 1u ? 512u : 1024u, b_lay);
+          const uint32_t da0 = desc_lo32(a_s, a_lbo), db0 = desc_lo32(b_s, b_lbo);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk) {
-            const uint32_t a_off = A_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
-            const uint32_t b_off = B_KMAJOR ? kk * 32 : kk * MT::kUmmaK * kSlabBytes;
-            const uint32_t a_lbo = A_KMAJOR ? 16 : MT::kBK * kSlabBytes;
-            const uint32_t b_lbo = B_KMAJOR ? 16 : MT::kBK * kSlabBytes;
-            constexpr uint32_t a_lay = (!A_KMAJOR && !MT::kBf16) ? 1u : 2u, b_lay = (!B_KMAJOR && !MT::kBf16) ? 1u : 2u;
-            constexpr uint32_t a_sbo = (a_lay == 1u) ? 512u : 1024u, b_sbo = (b_lay == 1u) ? 512u : 1024u;
-            const uint64_t da = make_desc(a_s + a_off, a_lbo, a_sbo, a_lay);
-            const uint64_t db = make_desc(b_s + b_off, b_lbo, b_sbo, b_lay);
-            umma<MT::kBf16>(tmem_d, da, db, kIdesc, (kt > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < MT::kBK / MT::kUmmaK; ++kk)
+              umma<MT::kBf16>(tmem_d, desc_pack(da0 + kk * a_step, a_h32), desc_pack(db0 + kk * b_step, b_h32), kIdesc,
+                              (kt > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&empty[s]);
           }
-          umma_commit(&empty[s]);
+          have = __all_sync(0xffffffffu, next_seen);
         }
-        if (ok) umma_commit(&acc_full[buf]);
+        if (ok && elect_one()) umma_commit(&acc_full[buf]);
       }
     }
   } else if (warp >= 4) {
