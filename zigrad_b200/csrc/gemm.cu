@@ -229,7 +229,7 @@ static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensor
   return launch_pdl(kern, grid, dim3(tc::tc_threads(MODE)), (size_t)SL::kTotal, s, ta, tb, p);
 }
 
-// FP32X3 with a K-major A: the hi/lo parts of A live in tensor memory (ZG_X3_TMEM_A=0 keeps them in shared memory)
+// FP32X3: the hi/lo parts of A live in tensor memory (ZG_X3_TMEM_A=0 keeps them in shared memory)
 static bool x3_tmem_a() {
   static const bool on = [] { const char* e = getenv("ZG_X3_TMEM_A"); return !(e && e[0] == '0'); }();
   return on;
@@ -241,9 +241,11 @@ static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor,
 #define ZG_TC_CASE(BNV)                                                                       \
   if (bn == BNV) {                                                                            \
     if constexpr (MODE == tc::kFP32X3) {                                                      \
-      if (a_kmajor && x3_tmem_a()) {                                                          \
-        if (b_kmajor) return launch_tc_inst<BNV, true, true, MODE, true>(s, ta, tb, p, grid); \
-        return launch_tc_inst<BNV, true, false, MODE, true>(s, ta, tb, p, grid);              \
+      if (x3_tmem_a()) {                                                                      \
+        if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE, true>(s, ta, tb, p, grid);   \
+        if (a_kmajor) return launch_tc_inst<BNV, true, false, MODE, true>(s, ta, tb, p, grid);              \
+        if (b_kmajor) return launch_tc_inst<BNV, false, true, MODE, true>(s, ta, tb, p, grid);              \
+        return launch_tc_inst<BNV, false, false, MODE, true>(s, ta, tb, p, grid);                           \
       }                                                                                       \
     }                                                                                         \
     if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE>(s, ta, tb, p, grid);   \

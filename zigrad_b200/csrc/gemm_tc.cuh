@@ -407,7 +407,30 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (
   }
 }
 
-// ATM: FP32X3 with a K-major A operand keeps the hi and lo parts of A in TENSOR
+// One row of an fp32 A slab (32 k values of row `row` of the 128-row tile) from its shared-memory stage.
+// K-major: the row is 128 contiguous bytes whose 16-byte chunks sit at position c ^ (row % 8).
+// MN-major: the stage holds four column blocks of 32 rows; a block is 32 k-rows of 128 bytes (32
+// consecutive rows of A) whose 32-byte atoms sit at position atom ^ (k % 4); the read transposes.
+template <bool A_KMAJOR>
+__device__ __forceinline__ void load_a_row(const uint8_t* a_stage, int row, float4 (&v)[8]) {
+  if constexpr (A_KMAJOR) {
+    const uint8_t* rp = a_stage + row * kSlabBytes;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(rp + ((c ^ (row & 7)) << 4));
+  } else {
+    const uint8_t* bp = a_stage + (row >> 5) * (32 * kSlabBytes) + ((row & 7) << 2);
+    const int atom = (row >> 3) & 3;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      v[c].x = *reinterpret_cast<const float*>(bp + (4 * c + 0) * kSlabBytes + ((atom ^ 0) << 5));
+      v[c].y = *reinterpret_cast<const float*>(bp + (4 * c + 1) * kSlabBytes + ((atom ^ 1) << 5));
+      v[c].z = *reinterpret_cast<const float*>(bp + (4 * c + 2) * kSlabBytes + ((atom ^ 2) << 5));
+      v[c].w = *reinterpret_cast<const float*>(bp + (4 * c + 3) * kSlabBytes + ((atom ^ 3) << 5));
+    }
+  }
+}
+
+// ATM: FP32X3 keeps the hi and lo parts of the A operand in TENSOR
 // MEMORY (written by the split warps with tcgen05.st, read by the MMA from
 // there): shared memory then holds A once per stage (the fetched slab) and no
 // MMA reads it, which takes 64 of the 144 KB per 128x64x32 slab off the
@@ -438,12 +461,13 @@ struct SmemLayout {
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE, bool ATM = false>
 __global__ void __launch_bounds__(tc_threads(MODE), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
-  static_assert(!ATM || (MODE == kFP32X3 && A_KMAJOR), "A through tensor memory: FP32X3 with a K-major A only");
+  static_assert(!ATM || MODE == kFP32X3, "A through tensor memory: FP32X3 only");
   using MT = ModeTraits<MODE>;
   using SL = SmemLayout<BN, MODE, ATM>;
   constexpr int S = SL::kStages;
   constexpr bool X3 = (MODE == kFP32X3);
-  constexpr uint32_t kIdesc = make_idesc(MT::kBf16, !A_KMAJOR, !B_KMAJOR, BN);
+  // an A operand in tensor memory is K-major by construction (row m in lane m, one k element per column)
+  constexpr uint32_t kIdesc = make_idesc(MT::kBf16, ATM ? false : !A_KMAJOR, !B_KMAJOR, BN);
   constexpr uint32_t kTmemCols = SL::kTmemCols;
 
   extern __shared__ uint8_t smem_raw[];
@@ -598,11 +622,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t ta0 = tmem_d + SL::kAccCols + ((uint32_t)((warp & 3) * 32) << 16);
       float4 v[8];
       bool have = false;
-      auto load_row = [&](int stage) {
-        const uint8_t* rp = stage_base + stage * SL::kStageBytes + row * kSlabBytes;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const float4*>(rp + ((c ^ (row & 7)) << 4));
-      };
+      auto load_row = [&](int stage) { load_a_row<A_KMAJOR>(stage_base + stage * SL::kStageBytes, row, v); };
       for (int kt = 0; kt < KT; ++kt) {
         const int s = kt % S;
         if (!have) {
@@ -703,12 +723,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if constexpr (ATM) {
         if (a_warp) {  // thread = row of the A slab, as in the pipelined loop above
           const int row = (warp & 3) * 32 + lane;
-          const uint8_t* rp = st + row * kSlabBytes;
+          float4 va[8];
+          load_a_row<A_KMAJOR>(st, row, va);
           uint32_t hi[32], lo[32];
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const float4 v = *reinterpret_cast<const float4*>(rp + ((c ^ (row & 7)) << 4));
-            const float x[4] = {v.x, v.y, v.z, v.w};
+            const float x[4] = {va[c].x, va[c].y, va[c].z, va[c].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const uint32_t h = __float_as_uint(x[e]) & 0xFFFFE000u;
