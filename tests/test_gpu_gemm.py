@@ -152,6 +152,43 @@ def test_gemm_epilogue_column_sums_are_the_bias_gradient(gpu, mode, m, n, k):
     assert rel_err(sums, want_db) <= 3e-5, rel_err(sums, want_db)
 
 
+@pytest.mark.parametrize("m,n,k,tb", [(8192, 10, 64, True), (5003, 7, 16, False), (1000, 16, 512, True), (3001, 13, 100, True),
+                                      (8192, 64, 10, False), (4097, 256, 16, False), (999, 20, 3, True), (2050, 128, 7, False)])
+def test_short_dimension_gemms(gpu, m, n, k, tb):
+    """The FFMA kernels for n <= 16 or k <= 16 (the classifier layer forward and
+    backward): plain product with alpha/beta where the kernel takes it, and the
+    bias + ReLU epilogue, against the oracle's sgemm."""
+    g = rng(m + 31 * n + 7 * k)
+    A = g.standard_normal((m, k)).astype(np.float32)
+    B = g.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    C0 = g.standard_normal((m, n)).astype(np.float32)
+    b = g.standard_normal(n).astype(np.float32)
+    ldb = k if tb else n
+    be = GpuBackend(gpu)
+    for alpha, beta in ((1.0, 0.0), (-0.5, 2.0)):
+        got = be.bmm_acc(A, B, C0, (1, m, k), (1, k, n), (1, m, n), False, tb, k, ldb, n, alpha, beta)
+        want = ORC.bmm_acc(A, B, C0, (1, m, k), (1, k, n), (1, m, n), False, tb, k, ldb, n, alpha, beta)
+        assert rel_err(got, want) <= 1e-5, (alpha, beta, rel_err(got, want))
+    z = ORC.bmm_acc(A, B, np.zeros((m, n), np.float32), (1, m, k), (1, k, n), (1, m, n), False, tb, k, ldb, n, 1.0, 0.0)
+    act = ORC.relu_fwd(ORC.elwise("add", b, z.ravel())).reshape(m, n)
+    got = be.linear(A, B, np.zeros((m, n), np.float32), m, n, k, False, tb, k, ldb, n, 1.0, 0.0, "bias_relu", bias=b)
+    assert rel_err(got, act) <= 1e-5
+
+
+@pytest.mark.parametrize("m,n,k", [(10, 64, 8192), (16, 128, 4096), (3, 256, 2000), (7, 32, 1024)])
+@pytest.mark.parametrize("beta", [1.0, 0.0, 0.5])
+def test_narrow_weight_gradient(gpu, m, n, k, beta):
+    """dW = dY^T X for a layer with at most 16 outputs (A stored [k, m], B stored
+    [k, n], deep k): the FFMA kernel that folds k blocks with atomics."""
+    g = rng(m * 5 + n + k)
+    A = g.standard_normal((k, m)).astype(np.float32)
+    B = g.standard_normal((k, n)).astype(np.float32)
+    C0 = g.standard_normal((m, n)).astype(np.float32)
+    got = GpuBackend(gpu).bmm_acc(A, B, C0, (1, m, k), (1, k, n), (1, m, n), True, False, m, n, n, 1.0, beta)
+    want = ORC.bmm_acc(A, B, C0, (1, m, k), (1, k, n), (1, m, n), True, False, m, n, n, 1.0, beta)
+    assert rel_err(got, want) <= 1e-5, rel_err(got, want)
+
+
 def to_bf16_bits(x):
     return (oracle.round_bf16(np.ascontiguousarray(x, np.float32).ravel()).view(np.uint32) >> 16).astype(np.uint16)
 

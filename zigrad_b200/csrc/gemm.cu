@@ -10,6 +10,7 @@
 #include "driver_api.h"
 #include "gemm_tc.cuh"
 #include "gemm_tc_persistent.cuh"
+#include "gemm_skinny.cuh"
 #include "../../include/blas_conflux.h"
 
 namespace zg {
@@ -288,6 +289,57 @@ static bool launch_persistent(cudaStream_t s, bool a_kmajor, bool b_kmajor, cons
   return launch_persistent_inst<false, false, MODE>(s, ta, tb, p, tiles_m, tiles_n, n_tiles);
 }
 
+// fp32 problems with n <= 16 or k <= 16 (see gemm_skinny.cuh).  Returns true when taken.
+static bool try_skinny(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m,
+                       len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue,
+                       const void* bias, const void* mask, void* colsum) {
+  static const bool off = [] { const char* e = getenv("ZG_GEMM_NO_SKINNY"); return e && e[0] == '1'; }();
+  if (off || id != SINGLE || c_id != SINGLE || nA != 1 || nB != 1 || nC != 1) return false;
+  if (m > 0x7fffffffu || k == 0 || k > 0x7fffffffu || lda > 0xffffffffu || ldb > 0xffffffffu || ldc > 0xffffffffu) return false;
+  skinny::Params p;
+  p.A = static_cast<const float*>(A); p.B = static_cast<const float*>(B); p.C = static_cast<float*>(C);
+  p.bias = static_cast<const float*>(bias); p.mask = static_cast<const float*>(mask); p.colsum = static_cast<float*>(colsum);
+  p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k;
+  p.lda = (uint32_t)lda; p.ldb = (uint32_t)ldb; p.ldc = (uint32_t)ldc;
+  p.alpha = (float)alpha; p.beta = (float)beta; p.epilogue = epilogue; p.tb = tb ? 1 : 0;
+  if (ta) {
+    // weight gradient of a narrow layer: A [k, m], B [k, n]
+    if (tb || m > 16 || n < 16 || n > 256 || 256 % n != 0 || k < 1024 || epilogue != ZG_EPI_NONE || colsum) return false;
+    prescale_c<float>(s, static_cast<float*>(C), 1, m, n, ldc, m * ldc, beta);
+    const size_t ctas = std::min<size_t>((k + 31) / 32, (size_t)sm_count() * 2);
+    const uint32_t rows_per_cta = (uint32_t)((k + ctas - 1) / ctas);
+    const unsigned grid = (unsigned)((k + rows_per_cta - 1) / rows_per_cta);
+    const int mmax = m <= 4 ? 4 : (m <= 8 ? 8 : (m <= 12 ? 12 : 16));
+    const size_t smem = (size_t)(skinny::kThreads / n) * mmax * n * sizeof(float);
+    if (mmax == 4) return launch_pdl(skinny::skinny_m_kernel<4>, dim3(grid), dim3(skinny::kThreads), smem, s, p, rows_per_cta);
+    if (mmax == 8) return launch_pdl(skinny::skinny_m_kernel<8>, dim3(grid), dim3(skinny::kThreads), smem, s, p, rows_per_cta);
+    if (mmax == 12) return launch_pdl(skinny::skinny_m_kernel<12>, dim3(grid), dim3(skinny::kThreads), smem, s, p, rows_per_cta);
+    return launch_pdl(skinny::skinny_m_kernel<16>, dim3(grid), dim3(skinny::kThreads), smem, s, p, rows_per_cta);
+  }
+  if (m < 256) return false;
+  if (n <= 16 && k >= 16 && k <= 512 && k % 4 == 0 && lda % 4 == 0 && host_aligned16(A) && epilogue != ZG_EPI_RELU_MASK && !colsum) {
+    const unsigned grid = (unsigned)((m + skinny::kThreads / 4 - 1) / (skinny::kThreads / 4));
+    const size_t smem = (size_t)n * k * sizeof(float);
+    if (n <= 4) return launch_pdl(skinny::skinny_n_kernel<4>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    if (n <= 8) return launch_pdl(skinny::skinny_n_kernel<8>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    if (n <= 12) return launch_pdl(skinny::skinny_n_kernel<12>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    return launch_pdl(skinny::skinny_n_kernel<16>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+  }
+  if (k <= 16 && n >= 16 && n <= 256 && n % 4 == 0 && ldc % 4 == 0 && host_aligned16(C) && beta == 0.0 &&
+      (epilogue != ZG_EPI_RELU_MASK || host_aligned16(mask)) && (!bias || host_aligned16(bias))) {
+    const size_t cg = n / 4;
+    if (colsum && (cg & (cg - 1)) != 0) return false;  // a thread keeps one column group only when cg divides the stride
+    const size_t want = (m * cg + skinny::kThreads - 1) / skinny::kThreads;
+    const unsigned grid = (unsigned)std::min<size_t>(want, (size_t)sm_count() * 8);
+    const size_t smem = ((size_t)n * k + n) * sizeof(float);
+    if (k <= 4) return launch_pdl(skinny::skinny_k_kernel<4>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    if (k <= 8) return launch_pdl(skinny::skinny_k_kernel<8>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    if (k <= 12) return launch_pdl(skinny::skinny_k_kernel<12>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+    return launch_pdl(skinny::skinny_k_kernel<16>, dim3(grid), dim3(skinny::kThreads), smem, s, p);
+  }
+  return false;
+}
+
 // Returns true when the tensor-core path took the problem.
 static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                             len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
@@ -416,6 +468,7 @@ void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const voi
   if ((epilogue == ZG_EPI_BIAS || epilogue == ZG_EPI_BIAS_RELU) && !bias) { set_error(kBadArgument, "bmm: bias epilogue without bias"); return; }
   if (epilogue == ZG_EPI_RELU_MASK && !mask) { set_error(kBadArgument, "bmm: mask epilogue without mask source"); return; }
   if (colsum && id == DOUBLE) { set_error(kUnsupported, "bmm: column sums are fp32 only"); return; }
+  if (try_skinny(id, c_id, s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum)) return;
   if (try_tensor_core(id, c_id, s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum)) return;
   if (id == SINGLE && c_id == SINGLE) launch_simt<float, float>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);
   else if (id == DOUBLE && c_id == DOUBLE) launch_simt<double, double>(s, A, B, C, nA, nB, nC, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias, mask, colsum);

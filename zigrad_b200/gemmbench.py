@@ -1,7 +1,7 @@
 """Timing of single GEMMs through the `linear` op (zg_bmm).
 
     python -m zigrad_b200.gemmbench                       # the shapes of the wide bf16 MLP (config c3) + the headline MLP's
-    python -m zigrad_b200.gemmbench --m 8192 --n 4096 --k 4096 --dtype bf16 --epi bias_relu [--ta] [--tb] [--c-bf16]
+    python -m zigrad_b200.gemmbench --m 8192 --n 4096 --k 4096 --dtype bf16 --epi bias_relu [--ta] [--tb] [--c-bf16]   # --dtype: bf16 | f32 (3xTF32) | tf32 | ffma (fp32 FFMA kernel)
 
 Each GEMM runs on 4 distinct A operands in turn (so the inputs of consecutive
 launches differ), is captured into a CUDA graph and timed with CUDA events on
@@ -37,7 +37,7 @@ C3 = [
 def run_one(dev, ts, name, m, n, k, ta, tb, dtype, c_bf16, epi, beta, reps=10, cublas=False, R=4):
     import torch
     bf16 = dtype == "bf16"
-    dev.L.zg_set_math_mode(abi.MATH_TF32 if dtype == "tf32" else abi.MATH_FP32X3)
+    dev.L.zg_set_math_mode(abi.MATH_TF32 if dtype == "tf32" else (abi.MATH_FFMA if dtype == "ffma" else abi.MATH_FP32X3))
     a_shape = (k, m) if ta else (m, k)
     b_shape = (n, k) if tb else (k, n)
     g = np.random.default_rng(0)
@@ -130,7 +130,7 @@ if __name__ == "__main__":
     ap.add_argument("--k", type=int)
     ap.add_argument("--ta", action="store_true")
     ap.add_argument("--tb", action="store_true")
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "tf32"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "tf32", "ffma"])
     ap.add_argument("--c-bf16", action="store_true")
     ap.add_argument("--epi", default="none", choices=["none", "bias", "bias_relu", "relu_mask"])
     ap.add_argument("--beta", type=float, default=0.0)
