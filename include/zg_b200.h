@@ -192,9 +192,12 @@ typedef struct {
  * shard with zg_segment_sumsq, adds them up over the ranks and takes the root).
  * A segment may be empty (len 0): it still counts as a tensor for Adam's step
  * counter, which lets a rank list every tensor and own only parts of some. */
+/* zero_grads != 0: the kernel also clears every gradient it has applied, which
+ * is the next step's zero_grad (src/nn/model.zig:57-62) without a launch of its
+ * own; the gradients are then NOT readable after the call. */
 EXTERN_C void zg_sgd_step(dtype id, StreamWrapper stream, void* params, void* grads,
                           const zg_segment* seg, len_t n_seg, double lr,
-                          int clip, double max_norm, double delta, void* norms);
+                          int clip, double max_norm, double delta, void* norms, int zero_grads);
 /* Adam.update over every segment (src/nn/optim.zig:177-234), all in fp32:
  * the step counter advances once per TENSOR (optim.zig:189): segment j uses
  * t = t_first + j.  m, v are laid out like params.  When bf16_copy != NULL
@@ -274,9 +277,10 @@ EXTERN_C void zg_allreduce_oneshot(StreamWrapper stream, void* buf, len_t n, uns
                                    void* const* comm, len_t cap_elems);
 /* The same reduction with the SGD update of src/nn/optim.zig:100-122 (no
  * clipping) applied to the reduced gradient in the same kernel:
- * params[i] += (-lr) * sum_r grads_r[i]; grads receives the sum as well. */
+ * params[i] += (-lr) * sum_r grads_r[i]; grads receives the sum as well, or
+ * zeros when zero_grads != 0 (the next step's zero_grad, as in zg_sgd_step). */
 EXTERN_C void zg_allreduce_sgd_oneshot(StreamWrapper stream, void* grads, void* params, len_t n, double lr,
-                                       unsigned rank, unsigned world, void* const* comm, len_t cap_elems);
+                                       unsigned rank, unsigned world, void* const* comm, len_t cap_elems, int zero_grads);
 
 /* --------------------------------------------- stream-ordered caching allocator
  * Device-side replacement for the Zig CachingAllocator + BlockPool

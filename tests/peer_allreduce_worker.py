@@ -49,6 +49,14 @@ def main():
             print("rank %d: fused SGD mismatch n=%d" % (rank, n), flush=True)
         dev.mem_cache_free(pbuf)
         dev.mem_cache_free(gbuf)
+        # the same with zero_grads: identical parameters, the gradient buffer reads back as zeros
+        pbuf, gbuf = dev.from_numpy(P0), dev.from_numpy(host[rank])
+        ar.reduce_and_sgd(gbuf, pbuf, 0.01, True)
+        if dev.to_numpy(gbuf).any() or not np.array_equal(dev.to_numpy(pbuf), wantp):
+            ok = False
+            print("rank %d: fused SGD + zero mismatch n=%d" % (rank, n), flush=True)
+        dev.mem_cache_free(pbuf)
+        dev.mem_cache_free(gbuf)
         # replay from a captured graph: the epoch counter lives on the device
         x = np.full(n, float(rank + 1), np.float32)
         buf = dev.from_numpy(x)

@@ -60,6 +60,51 @@ def test_one_sgd_step_every_tensor(gpu, fused, B):
     gpu.mem_cache_free(Td)
 
 
+def test_update_that_clears_gradients_trains_like_zero_grad(gpu):
+    """zero_grads_in_update: no zero_grad launch from the second step on; losses and
+    parameters follow the plain trainer (same kernels otherwise; the weight
+    gradients are summed with atomics, hence a tolerance), eagerly and from a
+    captured graph."""
+    B = 1024
+    Ws, bs = kaiming_uniform(DIMS, 4242)
+    plain = MlpTrainer(gpu, DIMS, B, Ws, bs, "sgd", lr=0.05)
+    fast = MlpTrainer(gpu, DIMS, B, Ws, bs, "sgd", lr=0.05, zero_grads_in_update=True)
+    bufs = []
+    for i in range(3):
+        X, T, _ = batch(B, 50 + i)
+        Xd, Td = gpu.from_numpy(X), gpu.from_numpy(T)
+        bufs += [Xd, Td]
+        plain.step(Xd, Td)
+        fast.step(Xd, Td)
+        assert abs(plain.read_loss() - fast.read_loss()) <= 1e-5 * abs(plain.read_loss())
+    assert not gpu.to_numpy(fast.grads).any()
+    gpu.sync()
+    gpu.capture.open()
+    fast.step(bufs[0], bufs[1])
+    gpu.capture.save()
+    graph = gpu.capture.detach()
+    gpu.capture.open()
+    plain.step(bufs[0], bufs[1])
+    gpu.capture.save()
+    graph_plain = gpu.capture.detach()
+    assert graph.kernel_count() == graph_plain.kernel_count() - 1  # no fill of the gradient buffer
+    for _ in range(2):
+        graph.run()
+        graph_plain.run()
+    gpu.sync()
+    pW, pb = plain.get_params()
+    fW, fb = fast.get_params()
+    for l in range(3):
+        assert_close("W%d" % l, fW[l], pW[l], 1e-5)
+        assert_close("b%d" % l, fb[l], pb[l], 1e-5)
+    graph.free()
+    graph_plain.free()
+    plain.free()
+    fast.free()
+    for b_ in bufs:
+        gpu.mem_cache_free(b_)
+
+
 def test_loss_over_100_sgd_steps_config2(gpu):
     """784-128-64-10 at batch 8192, 100 SGD steps over a fixed set of seeded
     batches: per-step loss within 1e-3 relative of the CPU path."""

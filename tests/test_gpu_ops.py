@@ -282,6 +282,21 @@ def test_sgd_step_flat_buffer(gpu, clip):
 
 
 @pytest.mark.parametrize("clip", [False, True])
+def test_sgd_step_that_clears_the_gradients(gpu, clip):
+    """zero_grads: the same update, and the applied gradients read back as zeros."""
+    g = rng(14)
+    n = 109386
+    p, gr = g.standard_normal(n).astype(np.float32), (g.standard_normal(n) * (0.2 if clip else 1.0)).astype(np.float32)
+    be = GpuBackend(gpu)
+    P, G, N = be.up(p), be.up(gr), be.up(np.zeros(len(SEGS), np.float32))
+    gpu.dispatch(opspec.sgd(P, G, SEGS, 0.01, clip, 10.0, 1e-6, N, True))
+    wp, _ = ORC.sgd(p, gr, SEGS, 0.01, clip, 10.0, 1e-6)
+    assert rel_err(gpu.to_numpy(P), wp) <= 2e-7
+    assert not gpu.to_numpy(G).any()
+    be.down(P), be.down(N)
+
+
+@pytest.mark.parametrize("clip", [False, True])
 def test_adam_step_flat_buffer_per_tensor_counter(gpu, clip):
     g = rng(13)
     n = 109386

@@ -185,7 +185,7 @@ SIGNATURES = {
     "zg_broadcast": (None, [dtype_t, S, vp, len_t, vp, len_t, dbl, dbl]),
     "zg_softmax_ce_fwd_bwd": (None, [dtype_t, S, vp, vp, i32, len_t, len_t, len_t, dbl, vp, vp, i32, vp, vp]),
     "zg_smooth_l1_fwd_bwd": (None, [dtype_t, S, vp, vp, len_t, dbl, vp, vp]),
-    "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp]),
+    "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp, i32]),
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp]),
     "zg_segment_sumsq": (None, [dtype_t, S, vp, C.POINTER(Segment), len_t, vp]),
     "zg_soft_update": (None, [dtype_t, S, vp, vp, len_t, dbl]),
@@ -198,7 +198,7 @@ SIGNATURES = {
     "zg_ipc_close": (None, [vp]),
     "zg_comm_error": (C.c_int, [vp, S]),
     "zg_allreduce_oneshot": (None, [S, vp, len_t, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
-    "zg_allreduce_sgd_oneshot": (None, [S, vp, vp, len_t, dbl, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
+    "zg_allreduce_sgd_oneshot": (None, [S, vp, vp, len_t, dbl, C.c_uint, C.c_uint, C.POINTER(vp), len_t, i32]),
     "zg_scatter_add": (None, [dtype_t, S, vp, vp, len_t, vp]),
     "zg_gather_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, vp, vp]),
     "zg_scatter_gcn_deg_scaled": (None, [dtype_t, S, vp, vp, vp, vp, vp, len_t, len_t]),

@@ -39,6 +39,7 @@ struct ArArgs {
   float* params;  // optional fused SGD: params += nlr * (reduced gradient)
   float nlr;
   float* grads;
+  int zero_grads;  // with params: leave zeros instead of the sum in grads
   size_t n, cap_pairs;
   unsigned rank, world;
   char* comm[kArMaxWorld];
@@ -96,8 +97,8 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
       s1 += __uint_as_float(w.z);
     }
     if (gave_up) break;
-    a.grads[2 * i] = s0;
-    if (2 * i + 1 < a.n) a.grads[2 * i + 1] = s1;
+    a.grads[2 * i] = a.zero_grads ? 0.f : s0;
+    if (2 * i + 1 < a.n) a.grads[2 * i + 1] = a.zero_grads ? 0.f : s1;
     if (a.params) {  // the SGD update of src/nn/optim.zig:100-122 (no clipping) on the reduced gradient
       a.params[2 * i] = fmaf(a.nlr, s0, a.params[2 * i]);
       if (2 * i + 1 < a.n) a.params[2 * i + 1] = fmaf(a.nlr, s1, a.params[2 * i + 1]);
@@ -153,8 +154,8 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArA
     v1 = (2 * i + 1 < a.n) ? a.grads[2 * i + 1] : 0.f;
   };
   auto store_result = [&](size_t i, float s0, float s1) {
-    a.grads[2 * i] = s0;
-    if (2 * i + 1 < a.n) a.grads[2 * i + 1] = s1;
+    a.grads[2 * i] = a.zero_grads ? 0.f : s0;
+    if (2 * i + 1 < a.n) a.grads[2 * i + 1] = a.zero_grads ? 0.f : s1;
     if (a.params) {
       a.params[2 * i] = fmaf(a.nlr, s0, a.params[2 * i]);
       if (2 * i + 1 < a.n) a.params[2 * i + 1] = fmaf(a.nlr, s1, a.params[2 * i + 1]);
@@ -262,21 +263,21 @@ extern "C" int zg_comm_error(void* region, StreamWrapper stream) {
 }
 
 static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigned rank, unsigned world, void* const* comm, len_t cap_elems,
-                             void* params, double lr);
+                             void* params, double lr, int zero_grads);
 
 extern "C" void zg_allreduce_oneshot(StreamWrapper stream, void* grads, len_t n, unsigned rank, unsigned world, void* const* comm,
                                      len_t cap_elems) {
-  allreduce_launch(stream, grads, n, rank, world, comm, cap_elems, nullptr, 0.0);
+  allreduce_launch(stream, grads, n, rank, world, comm, cap_elems, nullptr, 0.0, 0);
 }
 
 extern "C" void zg_allreduce_sgd_oneshot(StreamWrapper stream, void* grads, void* params, len_t n, double lr, unsigned rank, unsigned world,
-                                         void* const* comm, len_t cap_elems) {
+                                         void* const* comm, len_t cap_elems, int zero_grads) {
   if (!params) { set_error(kBadArgument, "zg_allreduce_sgd_oneshot: params is NULL"); return; }
-  allreduce_launch(stream, grads, n, rank, world, comm, cap_elems, params, lr);
+  allreduce_launch(stream, grads, n, rank, world, comm, cap_elems, params, lr, zero_grads);
 }
 
 static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigned rank, unsigned world, void* const* comm, len_t cap_elems,
-                             void* params, double lr) {
+                             void* params, double lr, int zero_grads) {
   if (n == 0) return;
   if (world < 1 || world > (unsigned)kArMaxWorld || rank >= world) { set_error(kBadArgument, "zg_allreduce_oneshot: rank %u / world %u", rank, world); return; }
   if (n > cap_elems) { set_error(kBadArgument, "zg_allreduce_oneshot: %lu elements exceed the comm region's %lu", n, cap_elems); return; }
@@ -286,6 +287,7 @@ static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigne
   a.grads = static_cast<float*>(grads);
   a.params = static_cast<float*>(params);
   a.nlr = -(float)lr;
+  a.zero_grads = (params && zero_grads) ? 1 : 0;
   a.n = n; a.cap_pairs = cap_elems / 2; a.rank = rank; a.world = world;
   for (unsigned p = 0; p < world; ++p) {
     if (!comm[p]) { set_error(kBadArgument, "zg_allreduce_oneshot: comm region of rank %u is NULL", p); return; }

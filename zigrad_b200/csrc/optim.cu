@@ -85,7 +85,7 @@ __device__ __forceinline__ float clip_factor(const float* norms, int idx, float 
 // norm exceeds max_norm.
 template <bool CLIP>
 __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* grads, const __grid_constant__ SegTable tab, float nlr,
-                                                        const float* __restrict__ norms, float max_norm, float delta) {
+                                                        const float* __restrict__ norms, float max_norm, float delta, const int zero) {
   pdl_sync();
   const int seg = blockIdx.y;
   float* p = params + tab.offset[seg];
@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* gr
     for (size_t i = tid; i < head; i += nth) {
       float gi = g[i];
       if (CLIP && on) { gi *= f; g[i] = gi; }
+      if (zero) g[i] = 0.f;
       p[i] = fmaf(nlr, gi, p[i]);
     }
     float4* gq = reinterpret_cast<float4*>(g + head);
@@ -114,18 +115,21 @@ __global__ void __launch_bounds__(kOThreads) sgd_kernel(float* params, float* gr
         gv.x *= f; gv.y *= f; gv.z *= f; gv.w *= f;
         gq[v] = gv;
       }
+      if (zero) gq[v] = make_float4(0.f, 0.f, 0.f, 0.f);
       pv.x = fmaf(nlr, gv.x, pv.x); pv.y = fmaf(nlr, gv.y, pv.y); pv.z = fmaf(nlr, gv.z, pv.z); pv.w = fmaf(nlr, gv.w, pv.w);
       pq[v] = pv;
     }
     for (size_t i = head + nv * 4 + tid; i < n; i += nth) {
       float gi = g[i];
       if (CLIP && on) { gi *= f; g[i] = gi; }
+      if (zero) g[i] = 0.f;
       p[i] = fmaf(nlr, gi, p[i]);
     }
   } else {
     for (size_t i = tid; i < n; i += nth) {
       float gi = g[i];
       if (CLIP && on) { gi *= f; g[i] = gi; }
+      if (zero) g[i] = 0.f;
       p[i] = fmaf(nlr, gi, p[i]);
     }
   }
@@ -240,7 +244,7 @@ static bool compute_norms(cudaStream_t s, const float* grads, const zg_segment* 
 using namespace zg;
 
 extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads, const zg_segment* seg, len_t n_seg, double lr,
-                            int clip, double max_norm, double delta, void* norms) {
+                            int clip, double max_norm, double delta, void* norms, int zero_grads) {
   if (id != SINGLE) { set_error(kUnsupported, "zg_sgd_step: only SINGLE is implemented"); return; }
   if (n_seg == 0) return;
   cudaStream_t s = as_stream(w);
@@ -254,8 +258,8 @@ extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads
     tab.first = (int)first;
     for (int j = 0; j < tab.n; ++j) { tab.offset[j] = seg[first + j].offset; tab.len[j] = seg[first + j].len; }
     const dim3 grid(chunks_for(seg + first, tab.n), tab.n);
-    if (clip) launch_pdl(sgd_kernel<true>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)norms, (float)max_norm, (float)delta);
-    else launch_pdl(sgd_kernel<false>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)nullptr, 0.f, 0.f);
+    if (clip) launch_pdl(sgd_kernel<true>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)norms, (float)max_norm, (float)delta, zero_grads);
+    else launch_pdl(sgd_kernel<false>, grid, dim3(kOThreads), 0, s, (float*)params, (float*)grads, tab, nlr, (const float*)nullptr, 0.f, 0.f, zero_grads);
   }
 }
 

@@ -468,7 +468,8 @@ class CudaDevice:
 
     def sgd(self, p):
         self.L.zg_sgd_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, self._segments(p.segments), len(p.segments),
-                           p.lr, int(p.clip), p.max_norm, p.delta, p.norms.ptr if p.norms is not None else None)
+                           p.lr, int(p.clip), p.max_norm, p.delta, p.norms.ptr if p.norms is not None else None,
+                           int(bool(getattr(p, 'zero_grads', False))))
 
     def adam(self, p):
         self.L.zg_adam_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr,

@@ -143,10 +143,12 @@ class PeerAllReduce:
     def __call__(self, grads) -> None:
         self.dev.L.zg_allreduce_oneshot(self.dev.stream, grads.ptr, grads.len, self.rank, self.world, self.ptrs, self.cap)
 
-    def reduce_and_sgd(self, grads, params, lr: float) -> None:
-        """All-reduce fused with the plain SGD update (no clipping): one kernel."""
+    def reduce_and_sgd(self, grads, params, lr: float, zero_grads: bool = False) -> None:
+        """All-reduce fused with the plain SGD update (no clipping): one kernel.
+        zero_grads leaves zeros instead of the summed gradient behind (the
+        next step's zero_grad without a launch of its own)."""
         self.dev.L.zg_allreduce_sgd_oneshot(self.dev.stream, grads.ptr, params.ptr, grads.len, float(lr), self.rank, self.world,
-                                            self.ptrs, self.cap)
+                                            self.ptrs, self.cap, int(zero_grads))
 
     def error(self) -> int:
         return int(self.dev.L.zg_comm_error(self.region, self.dev.stream))

@@ -198,7 +198,8 @@ class CudaDevice {
   }
   template <typename T> void op(const opspec::sgd<T>& p) {
     const std::vector<zg_segment> seg = segments(p.segments);
-    zg_sgd_step(dtype_of<T>(), cur(), p.params.ptr, p.grads.ptr, seg.data(), seg.size(), p.lr, p.clip ? 1 : 0, p.max_norm, p.delta, p.norms.ptr);
+    zg_sgd_step(dtype_of<T>(), cur(), p.params.ptr, p.grads.ptr, seg.data(), seg.size(), p.lr, p.clip ? 1 : 0, p.max_norm, p.delta, p.norms.ptr,
+                p.zero_grads ? 1 : 0);
   }
   template <typename T> void op(const opspec::adam<T>& p) {
     const std::vector<zg_segment> seg = segments(p.segments);

@@ -250,6 +250,7 @@ struct sgd {
   bool clip = false;
   double max_norm = 10.0, delta = 1e-6;
   Slice<float> norms;  // scratch, one per tensor (clip only)
+  bool zero_grads = false;  // also clear the applied gradients (the next step's zero_grad)
 };
 
 // Adam.update over a flat parameter set (src/nn/optim.zig:177-234)

@@ -52,7 +52,7 @@ class MlpTrainer:
     def __init__(self, dev: CudaDevice, dims: Sequence[int], batch: int, weights, biases, opt: str = "sgd",
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
                  max_norm: float = 10.0, delta: float = 1e-6, fused: bool = True, loss_div: Optional[int] = None,
-                 index_labels: bool = False, bf16: bool = False, pad_logits: bool = True):
+                 index_labels: bool = False, bf16: bool = False, pad_logits: bool = True, zero_grads_in_update: bool = False):
         self.dev, self.dims, self.B, self.L = dev, [int(d) for d in dims], int(batch), len(dims) - 1
         self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
         self.clip, self.max_norm, self.delta = clip, max_norm, delta
@@ -61,6 +61,11 @@ class MlpTrainer:
         self.t = 0  # Adam's optimizer-wide counter (advances once per tensor per step)
         if bf16 and not fused:
             raise ValueError("the bf16 path exists only as fused ops")
+        # SGD only: the update kernel clears the gradients it applied, so the next step needs no
+        # zero_grad launch (the gradients are then not readable after step())
+        if zero_grads_in_update and not (fused and opt == "sgd"):
+            raise ValueError("zero_grads_in_update needs the fused ops and SGD")
+        self.zero_grads_in_update, self._grads_clear = bool(zero_grads_in_update), False
         # flat parameter layout, attach order
         self.segments, off = [], 0
         for l in range(self.L):
@@ -117,8 +122,11 @@ class MlpTrainer:
             # zero_grad (model.zig:57-62) as ONE fill of the flat gradient buffer; the
             # weight-gradient GEMMs then accumulate with beta = 1 as the reference does
             # (kept on the main stream: as a side branch joined after the forward pass it
-            # cost more in extra graph dependencies than the 2.5 us it hides)
-            d.mem_fill(self.grads, 0.0)
+            # cost more in extra graph dependencies than the 2.5 us it hides).  With
+            # zero_grads_in_update the previous step's SGD kernel has cleared them already.
+            if not self._grads_clear:
+                d.mem_fill(self.grads, 0.0)
+            self._grads_clear = False
         for l in range(self.L):
             K, N = self.dims[l], self.dims[l + 1]
             last = l + 1 == self.L
@@ -197,7 +205,9 @@ class MlpTrainer:
     def update(self):
         d = self.dev
         if self.opt == "sgd":
-            d.dispatch(opspec.sgd(self.params, self.grads, self.segments, self.lr, self.clip, self.max_norm, self.delta, self.norms))
+            d.dispatch(opspec.sgd(self.params, self.grads, self.segments, self.lr, self.clip, self.max_norm, self.delta, self.norms,
+                                  self.zero_grads_in_update))
+            self._grads_clear = self.zero_grads_in_update
         elif self.opt == "adam":
             d.dispatch(opspec.adam(self.params, self.grads, self.m, self.v, self.segments, self.t + 1, self.lr, self.beta1,
                                    self.beta2, self.eps, self.clip, self.max_norm, self.delta, self.norms,
@@ -221,7 +231,11 @@ class MlpTrainer:
         if allreduce is not None:
             fused = getattr(allreduce, "reduce_and_sgd", None)
             if fused is not None and self.opt == "sgd" and not self.clip:
-                fused(self.grads, self.params, self.lr)  # reduction and update in one kernel
+                if self.zero_grads_in_update:
+                    fused(self.grads, self.params, self.lr, True)  # reduction, update and zero_grad in one kernel
+                    self._grads_clear = True
+                else:
+                    fused(self.grads, self.params, self.lr)  # reduction and update in one kernel
                 return
             allreduce(self.grads)
         self.update()

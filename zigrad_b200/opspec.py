@@ -394,6 +394,7 @@ class sgd:
     max_norm: float = 10.0
     delta: float = 1e-6
     norms: Optional[Any] = None
+    zero_grads: bool = False  # also clear the applied gradients (the next step's zero_grad)
 
 
 @_op("adam")
