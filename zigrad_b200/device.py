@@ -10,6 +10,7 @@ other implementation behind it: without the library or without a GPU it raises.
 from __future__ import annotations
 
 import contextlib
+import os
 
 import ctypes as C
 from dataclasses import dataclass
@@ -169,6 +170,9 @@ class CudaDevice:
         after everything issued so far on the main stream; they may overlap what
         the main stream runs next.  `join()` makes the main stream wait for them
         (required before the results are used and before a capture is saved)."""
+        if os.environ.get("ZG_NO_BRANCH") == "1":  # everything in issue order on the main stream
+            yield
+            return
         if self._side is None:
             self._side = self.L.init_stream()
         main = self.stream
