@@ -232,7 +232,7 @@ pub fn smooth_l1(self: *const Self, T: type, p: opspec.smooth_l1(T)) void {
     cuda.zg_smooth_l1_fwd_bwd(dtype(T), self.context.stream, p.pred.ptr, p.target.ptr, p.pred.len, p.beta, p.loss.ptr, if (p.grad) |g| g.ptr else null);
 }
 pub fn sgd(self: *const Self, T: type, p: opspec.sgd(T)) void {
-    cuda.zg_sgd_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.segments.ptr, p.segments.len, p.lr, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr);
+    cuda.zg_sgd_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.segments.ptr, p.segments.len, p.lr, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr, @intFromBool(p.zero_grads));
 }
 pub fn adam(self: *const Self, T: type, p: opspec.adam(T)) void {
     cuda.zg_adam_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, p.segments.ptr, p.segments.len, p.t_first, p.lr, p.beta1, p.beta2, p.eps, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr, null, null);
