@@ -35,6 +35,18 @@ EXTERN_C void zg_set_device(unsigned device_number);
  * (src/device/cuda_device.zig:24-33). */
 EXTERN_C void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller);
 
+/* Events for ordering that outlives the call: zg_event_record marks the work
+ * enqueued on `stream` so far, zg_stream_wait_event makes everything enqueued
+ * on `stream` afterwards wait for that mark (a never-recorded event does not
+ * block).  The input pipeline keeps one "copied" and one "consumed" event per
+ * staging slot, so a step waits for ITS batch only and a copy for the step that
+ * last read ITS slot.  No counterpart in the reference (one stream, synchronous
+ * copies: src/device/cuda_device.zig:24-33, 520-531). */
+EXTERN_C void* zg_event_create(void);
+EXTERN_C void zg_event_destroy(void* event);
+EXTERN_C void zg_event_record(void* event, StreamWrapper stream);
+EXTERN_C void zg_stream_wait_event(StreamWrapper stream, void* event);
+
 /* Page-locked host memory for the input pipeline: host-to-device copies from
  * it run asynchronously on a copy stream while the previous batch trains (the
  * reference's loader copies pageable memory synchronously, tensor by tensor:
@@ -93,7 +105,10 @@ EXTERN_C void zg_clamp_bwd(dtype id, StreamWrapper stream, const void* x, const 
                            len_t n, double lo, double hi);
 /* Unary maps y = f(x) (host_device.zig:383-387 sqrt, :480-482 rsqrt with
  * p = eps, :497-510 exp, :549-551 tanh, :561-563 sigmoid) */
-enum { ZG_UN_EXP = 0, ZG_UN_SQRT = 1, ZG_UN_RSQRT = 2, ZG_UN_TANH = 3, ZG_UN_SIGM = 4 };
+/* ZG_UN_POW: y = x^p (host_device.zig:353-361, pow_fwd / pow_fwd_).  x == y is
+ * allowed for every op: the in-place forms pow_fwd_ and sqrt_fwd_
+ * (host_device.zig:358-361, 390-392) are the same call with one pointer. */
+enum { ZG_UN_EXP = 0, ZG_UN_SQRT = 1, ZG_UN_RSQRT = 2, ZG_UN_TANH = 3, ZG_UN_SIGM = 4, ZG_UN_POW = 5 };
 EXTERN_C void zg_unary_fwd(dtype id, StreamWrapper stream, int op, const void* x, void* y, len_t n, double p);
 /* Their accumulating backward passes: x_g += f'(.) * y_g.  `v` is y for
  * exp/tanh/sigm (host_device.zig:512-515,553-555,565-567) and x for
@@ -101,6 +116,31 @@ EXTERN_C void zg_unary_fwd(dtype id, StreamWrapper stream, int op, const void* x
  * (host_device.zig:396-408, 485-503). */
 EXTERN_C void zg_unary_bwd(dtype id, StreamWrapper stream, int op, const void* v, const void* y_g, void* x_g,
                            len_t n, double p);
+/* opspec.pow_bwd (host_device.zig:365-379): x_g += exponent * x^(exponent-1) * y_g,
+ * entries with x < eps receive no gradient (eps is an f32 in the op struct). */
+EXTERN_C void zg_pow_bwd(dtype id, StreamWrapper stream, const void* x, const void* y_g, void* x_g, len_t n,
+                         double exponent, double eps);
+/* opspec.tanh_inplace_bwd / sigm_inplace_bwd (host_device.zig:557-559, 569-571):
+ * x holds the activation's OUTPUT; x_g *= (1 - x*x) for ZG_UN_TANH,
+ * x_g *= x*(1 - x) for ZG_UN_SIGM.  Other ops are refused. */
+EXTERN_C void zg_unary_inplace_bwd(dtype id, StreamWrapper stream, int op, const void* x, void* x_g, len_t n);
+/* Byte-mask activations (host_device.zig:600-701): one bit per element, bit
+ * (i % 8) of mask[i / 8]; mask holds ceil(n/8) bytes (mem_alloc_byte_mask,
+ * device_reference.zig:41-43).
+ *   relu_mask_fwd   x <= 0: x = 0 and the bit is set        (in place)
+ *   relu_mask_bwd   bit set: x_g = 0
+ *   clamp_mask_fwd  y = x UNCHANGED (what the reference stores, :611) and the
+ *                   bit is set where min(hi, max(lo, x)) != x
+ *   clamp_mask_bwd  bit set: x_g += y_g                     (:636-640)
+ * The reference's code for the last n % 8 elements of the two clamp forms names
+ * fields its op structs do not have (p.x_g in :621, p.x in :633), so it cannot
+ * be instantiated; here the tail follows the same per-element rule as the full
+ * bytes. */
+EXTERN_C void zg_relu_mask_fwd(dtype id, StreamWrapper stream, void* x, unsigned char* mask, len_t n);
+EXTERN_C void zg_relu_mask_bwd(dtype id, StreamWrapper stream, void* x_g, const unsigned char* mask, len_t n);
+EXTERN_C void zg_clamp_mask_fwd(dtype id, StreamWrapper stream, const void* x, void* y, unsigned char* mask, len_t n,
+                                double lo, double hi);
+EXTERN_C void zg_clamp_mask_bwd(dtype id, StreamWrapper stream, void* x_g, const void* y_g, const unsigned char* mask, len_t n);
 /* opspec.transpose (host_device.zig:261-267): B[j,i] = A[i,j] + alpha*B[j,i] */
 EXTERN_C void zg_transpose(dtype id, StreamWrapper stream, const void* A, void* B, len_t m, len_t n, double alpha);
 
@@ -221,6 +261,19 @@ EXTERN_C void zg_cast(dtype src_id, dtype dst_id, StreamWrapper stream, const vo
 /* ------------------------------------------------------------------- index
  * opspec.scatter_add (host_device.zig:1039-1086): dst[offsets[i]] += src[i] */
 EXTERN_C void zg_scatter_add(dtype id, StreamWrapper stream, const void* src, const len_t* offsets, len_t n, void* dst);
+/* opspec.scatter_add_2d (host_device.zig:1137-1160): dst[indices[i], :] += src[i, :]
+ * for n_blocks blocks of `stride` contiguous elements (fp atomics: the values
+ * added are the reference's, the order in which duplicates land is not). */
+EXTERN_C void zg_scatter_add_2d(dtype id, StreamWrapper stream, const void* src, const len_t* indices, len_t n_blocks,
+                                len_t stride, void* dst);
+/* opspec.scatter_add_csr (host_device.zig:1325-1335): dst[j] += src[i] for
+ * j in [row_ptr[i], row_ptr[i+1]); row_ptr has n_segments + 1 entries. Exact. */
+EXTERN_C void zg_scatter_add_csr(dtype id, StreamWrapper stream, const void* src, const len_t* row_ptr, len_t n_segments, void* dst);
+/* opspec.segment_sum_csr (host_device.zig:1337-1351): dst[i] = sum of
+ * src[row_offsets[i] .. row_offsets[i+1]) (overwritten).  Segments of up to 32
+ * elements are added left to right like the host loop; longer ones by 32
+ * strided partial sums and a fixed shuffle tree. */
+EXTERN_C void zg_segment_sum_csr(dtype id, StreamWrapper stream, const void* src, const len_t* row_offsets, len_t n_segments, void* dst);
 /* NDArray.gather along dim 1 of a [rows, cols] array with one index per row
  * (src/ndarray.zig:593-633; offsets are computed on the host there):
  * dst[r] = src[r*cols + idx[r]]; offsets_out (optional) receives r*cols+idx[r] */
@@ -266,13 +319,21 @@ EXTERN_C void zg_csr_gcn_propagate(dtype id, StreamWrapper stream, void* out, co
  * (bit-identical replicas).  Every rank must launch it the same number of times
  * (an epoch counter in device memory pairs the launches, so captured graphs can
  * replay it); world <= 8; n <= cap_elems.  Waits on peers are bounded: when one
- * runs out the kernel stops reducing and zg_comm_error() reports 1. */
+ * runs out the kernel stops reducing, leaves buf partly reduced and reports it. */
 EXTERN_C void* zg_comm_alloc(len_t cap_elems, unsigned world);
 EXTERN_C void zg_comm_free(void* region);
 EXTERN_C void zg_ipc_export(void* dptr, unsigned char* handle_out64);
 EXTERN_C void* zg_ipc_open(const unsigned char* handle64);
 EXTERN_C void zg_ipc_close(void* dptr);
+/* zg_comm_error synchronises the stream, returns the region's error word (1 = a
+ * launch since the last call gave up waiting) and clears it; the same event also
+ * raises the library-wide time-out status (zg_last_error() == 4 after the next
+ * stream_synchronize).  zg_comm_set_spin_limit sets how many polls a wait may
+ * take (0 restores the default, about seconds; ZG_SPIN_LIMIT in the environment
+ * sets the initial value) -- a short limit is how a host notices a missing peer
+ * quickly, and how the give-up path is tested without hanging a GPU. */
 EXTERN_C int zg_comm_error(void* region, StreamWrapper stream);
+EXTERN_C void zg_comm_set_spin_limit(unsigned polls);
 EXTERN_C void zg_allreduce_oneshot(StreamWrapper stream, void* buf, len_t n, unsigned rank, unsigned world,
                                    void* const* comm, len_t cap_elems);
 /* The same reduction with the SGD update of src/nn/optim.zig:100-122 (no

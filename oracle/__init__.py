@@ -222,6 +222,69 @@ def bwd3(name: str, x_g, y, y_g):
     return x_g
 
 
+def inplace_bwd(name: str, x, x_g):
+    """tanh_inplace_bwd / sigm_inplace_bwd: x_g *= f'(x), x the activation's output."""
+    getattr(lib(), "orc_" + name)(_f(x), _f(x_g), len_t(x.size))
+    return x_g
+
+
+def pow_fwd(x, e, y=None):
+    if y is None:
+        y = np.empty_like(x)
+    lib().orc_pow_fwd(_f(x), _f(y), len_t(x.size), C.c_float(e))
+    return y
+
+
+def pow_bwd(x, x_g, y_g, e, eps):
+    lib().orc_pow_bwd(_f(x), _f(x_g), _f(y_g), len_t(x.size), C.c_float(e), C.c_float(eps))
+    return x_g
+
+
+def _m(a: np.ndarray):
+    assert a.dtype == np.uint8 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(C.POINTER(C.c_ubyte))
+
+
+def relu_mask_fwd(x):
+    """In place on x; returns the byte mask (ceil(n/8) bytes)."""
+    mask = np.zeros((x.size + 7) // 8, np.uint8)
+    lib().orc_relu_mask_fwd(_f(x), _m(mask), len_t(x.size))
+    return mask
+
+
+def relu_mask_bwd(x_g, mask):
+    lib().orc_relu_mask_bwd(_f(x_g), _m(mask), len_t(x_g.size))
+    return x_g
+
+
+def clamp_mask_fwd(x, lo, hi):
+    y = np.empty_like(x)
+    mask = np.zeros((x.size + 7) // 8, np.uint8)
+    lib().orc_clamp_mask_fwd(_f(x), _f(y), _m(mask), len_t(x.size), C.c_float(lo), C.c_float(hi))
+    return y, mask
+
+
+def clamp_mask_bwd(x_g, y_g, mask):
+    lib().orc_clamp_mask_bwd(_f(x_g), _f(y_g), _m(mask), len_t(x_g.size))
+    return x_g
+
+
+def scatter_add_2d(src, indices, dst, stride):
+    lib().orc_scatter_add_2d(_f(src), _u(indices), len_t(indices.size), len_t(stride), _f(dst))
+    return dst
+
+
+def scatter_add_csr(src, row_ptr, dst):
+    lib().orc_scatter_add_csr(_f(src), _u(row_ptr), len_t(src.size), _f(dst))
+    return dst
+
+
+def segment_sum_csr(src, row_offsets):
+    dst = np.zeros(row_offsets.size - 1, np.float32)
+    lib().orc_segment_sum_csr(_f(src), _u(row_offsets), len_t(dst.size), _f(dst))
+    return dst
+
+
 def rsqrt_fwd(x, eps, y=None):
     if y is None:
         y = np.empty_like(x)

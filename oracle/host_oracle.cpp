@@ -352,6 +352,59 @@ void orc_sigm_bwd(float* x_g, const float* y, const float* y_g, len_t n) {
   for (len_t i = 0; i < n; ++i) x_g[i] += y[i] * (1.f - y[i]) * y_g[i];
 }
 
+// tanh_inplace_bwd: x_g *= 1 - x*x (:557-559); sigm_inplace_bwd: x_g *= x*(1-x) (:569-571)
+void orc_tanh_inplace_bwd(const float* x, float* x_g, len_t n) {
+  for (len_t i = 0; i < n; ++i) x_g[i] *= (1.f - (x[i] * x[i]));
+}
+void orc_sigm_inplace_bwd(const float* x, float* x_g, len_t n) {
+  for (len_t i = 0; i < n; ++i) x_g[i] *= (x[i] * (1.f - x[i]));
+}
+
+// pow_fwd / pow_fwd_ : y = pow(x, exp) (:353-361; y may alias x);
+// pow_bwd: x < eps -> +0, else x_g += exp * pow(x, exp-1) * y_g (:365-379)
+void orc_pow_fwd(const float* x, float* y, len_t n, float e) {
+  for (len_t i = 0; i < n; ++i) y[i] = std::pow(x[i], e);
+}
+void orc_pow_bwd(const float* x, float* x_g, const float* y_g, len_t n, float e, float eps) {
+  const float em1 = e - 1.f;
+  for (len_t i = 0; i < n; ++i)
+    if (!(x[i] < eps)) x_g[i] += e * std::pow(x[i], em1) * y_g[i];
+}
+
+// Byte-mask activations (:600-701): bit (i % 8) of mask[i / 8] per element
+// (std.bit_set.IntegerBitSet(8), :16).  The loops below state the per-element
+// rule of the reference's full-byte loops and apply it to the last n % 8
+// elements as well (the reference's tail code of the two clamp forms names
+// fields that its op structs do not have, :621 and :633).
+// relu_mask_fwd (:652-678): x <= 0 -> x = 0, bit set.
+void orc_relu_mask_fwd(float* x, unsigned char* mask, len_t n) {
+  for (len_t b = 0; b < (n + 7) / 8; ++b) mask[b] = 0;
+  for (len_t i = 0; i < n; ++i)
+    if (x[i] <= 0.f) {
+      x[i] = 0.f;
+      mask[i / 8] |= (unsigned char)(1u << (i % 8));
+    }
+}
+// relu_mask_bwd (:680-701): bit set -> x_g = 0
+void orc_relu_mask_bwd(float* x_g, const unsigned char* mask, len_t n) {
+  for (len_t i = 0; i < n; ++i)
+    if (mask[i / 8] & (1u << (i % 8))) x_g[i] = 0.f;
+}
+// clamp_mask_fwd (:600-628): bit = (x != min(hi, max(lo, x))); y receives x itself (:611)
+void orc_clamp_mask_fwd(const float* x, float* y, unsigned char* mask, len_t n, float lo, float hi) {
+  for (len_t b = 0; b < (n + 7) / 8; ++b) mask[b] = 0;
+  for (len_t i = 0; i < n; ++i) {
+    const float clamped = std::fmin(hi, std::fmax(lo, x[i]));
+    if (x[i] != clamped) mask[i / 8] |= (unsigned char)(1u << (i % 8));
+    y[i] = x[i];
+  }
+}
+// clamp_mask_bwd (:630-650): bit set -> x_g += y_g
+void orc_clamp_mask_bwd(float* x_g, const float* y_g, const unsigned char* mask, len_t n) {
+  for (len_t i = 0; i < n; ++i)
+    if (mask[i / 8] & (1u << (i % 8))) x_g[i] += y_g[i];
+}
+
 // max_fwd: y = x[isamax(x)] -- the element of largest MAGNITUDE (:573-580);
 // max_bwd: every position equal to y receives the gradient (:582-588)
 void orc_max_fwd(const float* x, float* y, len_t n) {
@@ -522,6 +575,25 @@ void orc_take(const float* src, const len_t* idx, len_t n, float* dst) {
 // values to the same places)
 void orc_scatter_add(const float* src, const len_t* offs, len_t n, float* dst) {
   for (len_t i = 0; i < n; ++i) dst[offs[i]] += src[i];
+}
+
+// scatter_add_2d (:1137-1160): dst[indices[i], :] += src[i, :], blocks of `stride`
+void orc_scatter_add_2d(const float* src, const len_t* indices, len_t n_blocks, len_t stride, float* dst) {
+  for (len_t b = 0; b < n_blocks; ++b)
+    for (len_t j = 0; j < stride; ++j) dst[indices[b] * stride + j] += src[b * stride + j];
+}
+// scatter_add_csr (:1325-1335): dst[j] += src[i] for j in [row_ptr[i], row_ptr[i+1])
+void orc_scatter_add_csr(const float* src, const len_t* row_ptr, len_t n_seg, float* dst) {
+  for (len_t i = 0; i < n_seg; ++i)
+    for (len_t j = row_ptr[i]; j < row_ptr[i + 1]; ++j) dst[j] += src[i];
+}
+// segment_sum_csr (:1337-1351) with the native left-to-right vsum_contig (:1318-1322)
+void orc_segment_sum_csr(const float* src, const len_t* row_ptr, len_t n_seg, float* dst) {
+  for (len_t i = 0; i < n_seg; ++i) {
+    float s = 0.f;
+    for (len_t j = row_ptr[i]; j < row_ptr[i + 1]; ++j) s += src[j];
+    dst[i] = s;
+  }
 }
 
 void orc_scatter_gcn_deg_scaled(float* dst, const float* h, const float* deg,

@@ -14,7 +14,13 @@ import numpy as np
 import oracle
 from zigrad_b200 import opspec
 from zigrad_b200.abi import SINGLE
-from zigrad_b200.device import USIZE
+from zigrad_b200.device import USIZE, DeviceSlice
+
+# Every buffer a GPU test uploads sits between two guard regions filled with this byte; they are
+# checked when the test's buffers are released, so a store that strays outside its operand -- which
+# the caching allocator would otherwise let land silently in a neighbouring block -- fails the test.
+GUARD_BYTES = 256
+GUARD_FILL = 0xA5
 
 
 def f32(a):
@@ -83,6 +89,38 @@ class OracleBackend:
         if name == "sqrt":
             return oracle.sqrt_bwd(v, x_g, y_g, p)
         return oracle.bwd3(name + "_bwd", x_g, v, y_g)
+
+    def pow_fwd(self, x, e):
+        return oracle.pow_fwd(f32(x).ravel(), e)
+
+    def pow_bwd(self, x, x_g, y_g, e, eps):
+        return oracle.pow_bwd(f32(x), f32(x_g).copy(), f32(y_g), e, eps)
+
+    def inplace_bwd(self, name, x, x_g):
+        return oracle.inplace_bwd(name + "_inplace_bwd", f32(x), f32(x_g).copy())
+
+    def relu_mask_fwd(self, x):
+        x = f32(x).copy()
+        mask = oracle.relu_mask_fwd(x)
+        return x, mask
+
+    def relu_mask_bwd(self, x_g, mask):
+        return oracle.relu_mask_bwd(f32(x_g).copy(), np.ascontiguousarray(mask, np.uint8))
+
+    def clamp_mask_fwd(self, x, lo, hi):
+        return oracle.clamp_mask_fwd(f32(x), lo, hi)
+
+    def clamp_mask_bwd(self, x_g, y_g, mask):
+        return oracle.clamp_mask_bwd(f32(x_g).copy(), f32(y_g), np.ascontiguousarray(mask, np.uint8))
+
+    def scatter_add_2d(self, src, indices, dst, stride):
+        return oracle.scatter_add_2d(f32(src).ravel(), np.ascontiguousarray(indices, np.uint64), f32(dst).ravel().copy(), stride)
+
+    def scatter_add_csr(self, src, row_ptr, dst):
+        return oracle.scatter_add_csr(f32(src), np.ascontiguousarray(row_ptr, np.uint64), f32(dst).copy())
+
+    def segment_sum_csr(self, src, row_offsets):
+        return oracle.segment_sum_csr(f32(src), np.ascontiguousarray(row_offsets, np.uint64))
 
     def nrm2(self, x):
         return oracle.nrm2(f32(x))
@@ -161,14 +199,27 @@ class GpuBackend:
         self._live = []
 
     def up(self, a, dtype=np.float32):
-        s = self.d.from_numpy(np.ascontiguousarray(np.asarray(a, dtype=dtype)).ravel())
-        self._live.append(s)
-        return s
+        a = np.ascontiguousarray(np.asarray(a, dtype=dtype)).ravel()
+        g = GUARD_BYTES // a.itemsize
+        padded = np.empty(a.size + 2 * g, a.dtype)
+        padded.view(np.uint8)[:] = GUARD_FILL
+        padded[g:g + a.size] = a
+        base = self.d.from_numpy(padded)
+        self._live.append((base, g, a.size))
+        return DeviceSlice(base.ptr + GUARD_BYTES, a.size, base.dtype, 0)
+
+    def check_guards(self):
+        for base, g, n in self._live:
+            lo = self.d.to_numpy(base.view(0, g)).view(np.uint8)
+            hi = self.d.to_numpy(base.view(g + n, g)).view(np.uint8)
+            assert (lo == GUARD_FILL).all(), "a kernel wrote BEFORE a %d-element operand" % n
+            assert (hi == GUARD_FILL).all(), "a kernel wrote PAST a %d-element operand" % n
 
     def down(self, s, shape=None):
         out = self.d.to_numpy(s, shape)
-        for b in self._live:
-            self.d.mem_cache_free(b)
+        self.check_guards()
+        for base, _, _ in self._live:
+            self.d.mem_cache_free(base)
         self._live = []
         return out
 
@@ -280,6 +331,71 @@ class GpuBackend:
         else:
             self.d.dispatch(cls(XG, V, YG))
         return self.down(XG)
+
+    def pow_fwd(self, x, e, inplace=False):
+        X = self.up(x)
+        if inplace:
+            self.d.dispatch(opspec.pow_fwd_(X, e))
+            return self.down(X)
+        Y = self.up(np.zeros(np.asarray(x).size, np.float32))
+        self.d.dispatch(opspec.pow_fwd(X, e, Y))
+        return self.down(Y)
+
+    def sqrt_inplace(self, x):
+        X = self.up(x)
+        self.d.dispatch(opspec.sqrt_fwd_(X))
+        return self.down(X)
+
+    def pow_bwd(self, x, x_g, y_g, e, eps):
+        X, XG, YG = self.up(x), self.up(x_g), self.up(y_g)
+        self.d.dispatch(opspec.pow_bwd(X, XG, e, YG, eps))
+        return self.down(XG)
+
+    def inplace_bwd(self, name, x, x_g):
+        X, XG = self.up(x), self.up(x_g)
+        self.d.dispatch(getattr(opspec, name + "_inplace_bwd")(X, XG))
+        return self.down(XG)
+
+    def relu_mask_fwd(self, x):
+        X = self.up(x)
+        M = self.up(np.full((np.asarray(x).size + 7) // 8, 0xFF, np.uint8), np.uint8)  # stale contents must not survive
+        self.d.dispatch(opspec.relu_mask_fwd(X, M))
+        m = self.d.to_numpy(M)
+        return self.down(X), m
+
+    def relu_mask_bwd(self, x_g, mask):
+        XG, M = self.up(x_g), self.up(mask, np.uint8)
+        self.d.dispatch(opspec.relu_mask_bwd(XG, M))
+        return self.down(XG)
+
+    def clamp_mask_fwd(self, x, lo, hi):
+        n = np.asarray(x).size
+        X, Y = self.up(x), self.up(np.zeros(n, np.float32))
+        M = self.up(np.full((n + 7) // 8, 0xFF, np.uint8), np.uint8)
+        self.d.dispatch(opspec.clamp_mask_fwd(X, Y, lo, hi, M))
+        m = self.d.to_numpy(M)
+        return self.down(Y), m
+
+    def clamp_mask_bwd(self, x_g, y_g, mask):
+        XG, YG, M = self.up(x_g), self.up(y_g), self.up(mask, np.uint8)
+        self.d.dispatch(opspec.clamp_mask_bwd(XG, YG, M))
+        return self.down(XG)
+
+    def scatter_add_2d(self, src, indices, dst, stride):
+        S, I, D = self.up(src), self.up(indices, np.uint64), self.up(dst)
+        self.d.dispatch(opspec.scatter_add_2d(S, I, D, stride))
+        return self.down(D)
+
+    def scatter_add_csr(self, src, row_ptr, dst):
+        S, R, D = self.up(src), self.up(row_ptr, np.uint64), self.up(dst)
+        self.d.dispatch(opspec.scatter_add_csr(S, R, D))
+        return self.down(D)
+
+    def segment_sum_csr(self, src, row_offsets):
+        S, R = self.up(src), self.up(row_offsets, np.uint64)
+        D = self.up(np.full(np.asarray(row_offsets).size - 1, 7.0, np.float32))  # dst is overwritten
+        self.d.dispatch(opspec.segment_sum_csr(S, R, D))
+        return self.down(D)
 
     def nrm2(self, x):
         X, Y = self.up(x), self.scalar()

@@ -100,6 +100,10 @@ def literal():
         mul_add_bwd=dict(src="src/ndtensor.zig:1789-1833", w=[3, 2], b=[1, 1], x=[4, 4], grad_w=[4, 4],
                          grad_b=[1, 1]),
         inplace_add=dict(src="src/ndtensor.zig:2153-2208", x=[4, 4, 4, 4], seed_grad=2.0, grads=[2, 2, 2, 2]),
+        # eps of the backward = the library default (src/zigrad.zig:70)
+        pow=dict(src="src/ndtensor.zig:2286-2312", x=[2, 3, 0, 1], exp=2.0, eps=1e-12, y=[4, 9, 0, 1], grad=[4, 6, 0, 2]),
+        sqrt=dict(src="src/ndtensor.zig:2314-2340", x=[4, 9, 16, 1], eps=1e-12, y=[2, 3, 4, 1],
+                  grad=[0.25, 1.0 / 6.0, 0.125, 0.5]),
     )
 
 

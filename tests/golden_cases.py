@@ -114,5 +114,16 @@ def check_losses(be):
     np.testing.assert_array_equal(grad, arr(c["input_grad"]))
 
 
+def check_pow_sqrt(be):
+    c = LIT["pow"]
+    x = arr(c["x"])
+    np.testing.assert_array_equal(be.pow_fwd(x, c["exp"]), arr(c["y"]))
+    np.testing.assert_array_equal(be.pow_bwd(x, np.zeros_like(x), np.ones_like(x), c["exp"], c["eps"]), arr(c["grad"]))
+    c = LIT["sqrt"]
+    x = arr(c["x"])
+    np.testing.assert_array_equal(be.unary("sqrt", x), arr(c["y"]))
+    np.testing.assert_array_equal(be.unary_bwd("sqrt", x, np.ones_like(x), np.zeros_like(x), c["eps"]), arr(c["grad"]))
+
+
 ALL = [check_bmm, check_bmm_bwd, check_matvec_dot, check_reductions, check_gather, check_clip_clamp,
-       check_add_broadcast, check_mul_div_bwd, check_losses]
+       check_add_broadcast, check_mul_div_bwd, check_losses, check_pow_sqrt]

@@ -3,6 +3,7 @@ the step intact and in order, also when the copies overlap running steps."""
 import numpy as np
 import pytest
 
+import oracle
 from zigrad_b200.abi import SINGLE
 from zigrad_b200.input_pipeline import BatchStager
 from zigrad_b200.mlp import MlpTrainer, kaiming_uniform
@@ -19,6 +20,8 @@ def test_staged_batches_give_the_same_losses_as_resident_batches(gpu):
         X = g.uniform(0, 1, (B, dims[0])).astype(np.float32)
         T = np.eye(dims[-1], dtype=np.float32)[g.integers(0, dims[-1], B)]
         data.append((X, T))
+    cpu = oracle.MlpOracle(dims, Ws, bs, "sgd", lr=0.05)  # the reference's host path on the same batches
+    want_cpu = [cpu.step(X, T) for X, T in data]
     ref = MlpTrainer(gpu, dims, B, Ws, bs, "sgd", lr=0.05)
     want = []
     for X, T in data:
@@ -42,6 +45,11 @@ def test_staged_batches_give_the_same_losses_as_resident_batches(gpu):
     got = gpu.to_numpy(losses)
     for a, b in zip(got, want):
         assert abs(a - b) <= 1e-6 * abs(b), (got, want)
+    for a, b in zip(got, want_cpu):  # a stale or half-copied batch would show up as a different loss curve
+        assert abs(a - b) <= 1e-4 * abs(b), (got, want_cpu)
+    Wg, bg = tr.get_params()
+    for l in range(len(dims) - 1):
+        assert np.abs(Wg[l] - cpu.W[l]).max() <= 1e-4 * np.abs(cpu.W[l]).max()
     with pytest.raises(RuntimeError):
         st.get()
     st.close()

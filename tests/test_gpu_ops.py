@@ -396,3 +396,103 @@ def test_softmax_ce_fast_paths_large_index_labels(gpu, rows, C):
     assert rel_err(got_b, wg.astype(np.float64).sum(0)) <= 1e-4
     for s in (X, T, G, Ls, Bg):
         d.mem_cache_free(s)
+
+
+# ---------------------------------------------------------------- ops of the interface beyond the training step
+@pytest.mark.parametrize("e", [2.0, 0.5, 3.0, -1.5])
+def test_pow_forward_in_place_and_backward(gpu, e):
+    g = rng(int(e * 10) + 40)
+    x = g.uniform(0.05, 4.0, 4099).astype(np.float32)
+    x[:3] = [0.0, 1e-13, 1.0]
+    be = GpuBackend(gpu)
+    want = ORC.pow_fwd(x, e)
+    with np.errstate(divide="ignore"):
+        np.testing.assert_allclose(be.pow_fwd(x, e), want, rtol=2e-6, atol=0)           # powf vs libm pow: a few ulp
+        np.testing.assert_allclose(be.pow_fwd(x, e, inplace=True), want, rtol=2e-6, atol=0)
+    xg, yg = g.standard_normal(x.size).astype(np.float32), g.standard_normal(x.size).astype(np.float32)
+    # entries below eps (the first two) must come back untouched
+    got, wantg = be.pow_bwd(x, xg, yg, e, 1e-12), ORC.pow_bwd(x, xg, yg, e, 1e-12)
+    np.testing.assert_array_equal(got[:2], xg[:2])
+    np.testing.assert_allclose(got, wantg, rtol=1e-5, atol=1e-6)
+
+
+def test_sqrt_in_place_bit_exact(gpu):
+    x = rng(3).uniform(0.0, 9.0, 1027).astype(np.float32)
+    np.testing.assert_array_equal(GpuBackend(gpu).sqrt_inplace(x), ORC.unary("sqrt", x))
+
+
+@pytest.mark.parametrize("name", ["tanh", "sigm"])
+@pytest.mark.parametrize("n", [1, 33, 4099])
+def test_inplace_backward_of_tanh_and_sigmoid_bit_exact(gpu, name, n):
+    g = rng(n + 77)
+    y = ORC.unary(name, g.standard_normal(n).astype(np.float32))   # the op reads the activation's output
+    xg = g.standard_normal(n).astype(np.float32)
+    # two correctly rounded multiplies and one subtraction, compiled without contraction on both sides
+    np.testing.assert_array_equal(GpuBackend(gpu).inplace_bwd(name, y, xg), ORC.inplace_bwd(name, y, xg))
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 63, 64, 1000, 4099, (1 << 18) + 3])
+def test_byte_mask_relu_bit_exact(gpu, n):
+    g = rng(n + 5)
+    x = g.standard_normal(n).astype(np.float32)
+    x[::7] = 0.0
+    if n > 2:
+        x[1] = -0.0
+    be = GpuBackend(gpu)
+    got_x, got_m = be.relu_mask_fwd(x)
+    want_x, want_m = ORC.relu_mask_fwd(x)
+    np.testing.assert_array_equal(got_m, want_m)   # includes the unused high bits of the last byte: zero
+    np.testing.assert_array_equal(got_x, want_x)
+    xg = g.standard_normal(n).astype(np.float32)
+    np.testing.assert_array_equal(be.relu_mask_bwd(xg, want_m), ORC.relu_mask_bwd(xg, want_m))
+
+
+@pytest.mark.parametrize("n", [1, 8, 13, 64, 1001, 4099])
+def test_byte_mask_clamp_bit_exact(gpu, n):
+    g = rng(n + 9)
+    x = (g.standard_normal(n) * 2).astype(np.float32)
+    x[0] = 1.0  # on the bound: clamping leaves it unchanged, bit clear
+    be = GpuBackend(gpu)
+    got_y, got_m = be.clamp_mask_fwd(x, -1.0, 1.0)
+    want_y, want_m = ORC.clamp_mask_fwd(x, -1.0, 1.0)
+    np.testing.assert_array_equal(got_m, want_m)
+    np.testing.assert_array_equal(got_y, want_y)
+    np.testing.assert_array_equal(got_y, x)        # the reference stores x itself, not the clamped value
+    xg, yg = g.standard_normal(n).astype(np.float32), g.standard_normal(n).astype(np.float32)
+    np.testing.assert_array_equal(be.clamp_mask_bwd(xg, yg, want_m), ORC.clamp_mask_bwd(xg, yg, want_m))
+
+
+@pytest.mark.parametrize("n_blocks,stride,n_seg", [(1, 1, 1), (100, 16, 7), (4099, 7, 300), (2708, 33, 2708), (5000, 128, 11)])
+def test_scatter_add_2d(gpu, n_blocks, stride, n_seg):
+    g = rng(n_blocks + stride)
+    src = g.standard_normal((n_blocks, stride)).astype(np.float32)
+    idx = g.integers(0, n_seg, n_blocks).astype(np.uint64)
+    dst = g.standard_normal((n_seg, stride)).astype(np.float32)
+    got, want = GpuBackend(gpu).scatter_add_2d(src, idx, dst, stride), ORC.scatter_add_2d(src, idx, dst, stride)
+    # duplicates land in a different order than the host loop: a few ulp of the running sums
+    np.testing.assert_allclose(got, want, rtol=0, atol=2e-5 * max(1.0, float(np.abs(want).max())))
+    uniq = np.arange(min(n_blocks, n_seg), dtype=np.uint64)  # no duplicates: exact
+    g2 = GpuBackend(gpu).scatter_add_2d(src[:uniq.size], uniq, dst, stride)
+    np.testing.assert_array_equal(g2, ORC.scatter_add_2d(src[:uniq.size], uniq, dst, stride))
+
+
+def _csr(g, n_seg, max_len):
+    lens = g.integers(0, max_len + 1, n_seg)
+    lens[::5] = 0                                    # empty segments
+    return np.concatenate([[0], np.cumsum(lens)]).astype(np.uint64)
+
+
+@pytest.mark.parametrize("n_seg,max_len", [(1, 5), (100, 9), (2708, 40), (37, 5000)])
+def test_csr_scatter_add_exact_and_segment_sum(gpu, n_seg, max_len):
+    g = rng(n_seg + max_len)
+    row_ptr = _csr(g, n_seg, max_len)
+    total = int(row_ptr[-1])
+    be = GpuBackend(gpu)
+    src = g.standard_normal(n_seg).astype(np.float32)
+    dst = g.standard_normal(max(total, 1)).astype(np.float32)
+    np.testing.assert_array_equal(be.scatter_add_csr(src, row_ptr, dst), ORC.scatter_add_csr(src, row_ptr, dst))
+    data = g.standard_normal(max(total, 1)).astype(np.float32)
+    got, want = be.segment_sum_csr(data, row_ptr), ORC.segment_sum_csr(data, row_ptr)
+    short = np.diff(row_ptr.astype(np.int64)) <= 32
+    np.testing.assert_array_equal(got[short], want[short])   # left-to-right like the host loop
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-5 * np.sqrt(max_len))

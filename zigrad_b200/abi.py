@@ -76,7 +76,7 @@ class Segment(C.Structure):
 ADD, MIN, MAX, MUL = 0, 1, 2, 3
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_RELU_MASK = 0, 1, 2, 3
 MATH_FP32X3, MATH_TF32, MATH_FFMA = 0, 1, 2
-UN_EXP, UN_SQRT, UN_RSQRT, UN_TANH, UN_SIGM = 0, 1, 2, 3, 4
+UN_EXP, UN_SQRT, UN_RSQRT, UN_TANH, UN_SIGM, UN_POW = 0, 1, 2, 3, 4, 5
 LABEL_ONEHOT, LABEL_INDEX = 0, 1
 SMAX_FAST, SMAX_MAX, SMAX_LOG = 0, 1, 2
 RDX_NONE, RDX_MEAN, RDX_SUM = 0, 1, 2
@@ -107,6 +107,10 @@ SIGNATURES = {
     "deinit_stream": (None, [S]),
     "stream_synchronize": (None, [S]),
     "zg_stream_wait": (None, [S, S]),
+    "zg_event_create": (vp, []),
+    "zg_event_destroy": (None, [vp]),
+    "zg_event_record": (None, [vp, S]),
+    "zg_stream_wait_event": (None, [S, vp]),
     "zg_host_alloc_pinned": (vp, [len_t]),
     "zg_host_free_pinned": (None, [vp]),
     "init_cublas_handle": (CB, [S]),
@@ -175,6 +179,12 @@ SIGNATURES = {
     "zg_clamp_bwd": (None, [dtype_t, S, vp, vp, vp, len_t, dbl, dbl]),
     "zg_unary_fwd": (None, [dtype_t, S, i32, vp, vp, len_t, dbl]),
     "zg_unary_bwd": (None, [dtype_t, S, i32, vp, vp, vp, len_t, dbl]),
+    "zg_pow_bwd": (None, [dtype_t, S, vp, vp, vp, len_t, dbl, dbl]),
+    "zg_unary_inplace_bwd": (None, [dtype_t, S, i32, vp, vp, len_t]),
+    "zg_relu_mask_fwd": (None, [dtype_t, S, vp, vp, len_t]),
+    "zg_relu_mask_bwd": (None, [dtype_t, S, vp, vp, len_t]),
+    "zg_clamp_mask_fwd": (None, [dtype_t, S, vp, vp, vp, len_t, dbl, dbl]),
+    "zg_clamp_mask_bwd": (None, [dtype_t, S, vp, vp, vp, len_t]),
     "zg_transpose": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl]),
     "zg_fold_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl, dbl]),
     "zg_fold_rows_noalloc": (None, [dtype_t, S, vp, vp, len_t, len_t, dbl, dbl]),
@@ -197,9 +207,13 @@ SIGNATURES = {
     "zg_ipc_open": (vp, [u8p]),
     "zg_ipc_close": (None, [vp]),
     "zg_comm_error": (C.c_int, [vp, S]),
+    "zg_comm_set_spin_limit": (None, [C.c_uint]),
     "zg_allreduce_oneshot": (None, [S, vp, len_t, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
     "zg_allreduce_sgd_oneshot": (None, [S, vp, vp, len_t, dbl, C.c_uint, C.c_uint, C.POINTER(vp), len_t, i32]),
     "zg_scatter_add": (None, [dtype_t, S, vp, vp, len_t, vp]),
+    "zg_scatter_add_2d": (None, [dtype_t, S, vp, vp, len_t, len_t, vp]),
+    "zg_scatter_add_csr": (None, [dtype_t, S, vp, vp, len_t, vp]),
+    "zg_segment_sum_csr": (None, [dtype_t, S, vp, vp, len_t, vp]),
     "zg_gather_rows": (None, [dtype_t, S, vp, vp, len_t, len_t, vp, vp]),
     "zg_scatter_gcn_deg_scaled": (None, [dtype_t, S, vp, vp, vp, vp, vp, len_t, len_t]),
     "zg_scatter_gcn_deg_scaled_bwd": (None, [dtype_t, S, vp, vp, vp, vp, vp, vp, vp, len_t, len_t]),

@@ -21,8 +21,9 @@
 // overwrites words that are still being read.  The epoch lives in device memory
 // and advances by one per launch, which keeps the kernel replayable from a
 // captured graph.  The sum is formed in rank order on every rank: bit-identical
-// replicas.  Polls are bounded; a rank that gives up sets the error word and
-// leaves its buffer partly reduced.
+// replicas.  Polls are bounded (zg_comm_set_spin_limit / ZG_SPIN_LIMIT); a rank
+// that gives up sets the error word and the library's time-out flag and leaves
+// its buffer partly reduced.
 #include <cstdlib>
 #include <cstring>
 
@@ -32,7 +33,7 @@ namespace zg {
 
 constexpr int kArThreads = 256;
 constexpr int kArMaxWorld = 8;
-constexpr unsigned kArSpinLimit = 1u << 24;  // polls (with back-off) before a wait gives up: seconds
+constexpr unsigned kArSpinLimit = 1u << 24;  // default polls (with back-off) before a wait gives up: seconds
 constexpr size_t kArHeader = 512;
 
 struct ArArgs {
@@ -42,8 +43,17 @@ struct ArArgs {
   int zero_grads;  // with params: leave zeros instead of the sum in grads
   size_t n, cap_pairs;
   unsigned rank, world;
+  unsigned spin_limit;  // polls before a wait on a peer's word gives up
+  int* timeout_flag;    // the per-device flag that stream_synchronize turns into kKernelTimeout
   char* comm[kArMaxWorld];
 };
+
+// A wait ran out: the comm region's error word (zg_comm_error reads and clears it) and the
+// library-wide time-out flag are raised; the kernel goes on to its epilogue and returns.
+__device__ __forceinline__ void ar_report_gave_up(unsigned* ctl, const ArArgs& a) {
+  ctl[2] = 1;
+  if (a.timeout_flag) *a.timeout_flag = 1;
+}
 
 __device__ __forceinline__ void st_word_pair(uint4* p, uint4 v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -88,7 +98,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
       }
       const uint4* src = slot(a.rank, p) + i;
       uint4 w = ld_word_pair(src);
-      for (unsigned it = 0; (w.y != e || w.w != e) && it < kArSpinLimit; ++it) {
+      for (unsigned it = 0; (w.y != e || w.w != e) && it < a.spin_limit; ++it) {
         if (it > 64) __nanosleep(it > 4096 ? 200 : 20);
         w = ld_word_pair(src);
       }
@@ -104,7 +114,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
       if (2 * i + 1 < a.n) a.params[2 * i + 1] = fmaf(a.nlr, s1, a.params[2 * i + 1]);
     }
   }
-  if (gave_up) ctl[2] = 1;
+  if (gave_up) ar_report_gave_up(ctl, a);
   // ---- the last CTA to finish advances the epoch
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -143,7 +153,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArA
   };
   auto poll = [&](const uint4* src, uint4& w) -> bool {
     w = ld_word_pair(src);
-    for (unsigned it = 0; (w.y != e || w.w != e) && it < kArSpinLimit; ++it) {
+    for (unsigned it = 0; (w.y != e || w.w != e) && it < a.spin_limit; ++it) {
       if (it > 64) __nanosleep(it > 4096 ? 200 : 20);
       w = ld_word_pair(src);
     }
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArA
     if (!poll(gather_slot(a.rank, owner) + (i - (size_t)owner * S), w)) { gave_up = true; break; }
     store_result(i, __uint_as_float(w.x), __uint_as_float(w.z));
   }
-  if (gave_up) ctl[2] = 1;
+  if (gave_up) ar_report_gave_up(ctl, a);
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned t = atomicAdd(&ctl[1], 1u);
@@ -259,7 +269,21 @@ extern "C" int zg_comm_error(void* region, StreamWrapper stream) {
   unsigned v = 0;
   if (!ZG_CUDA(cudaMemcpyAsync(&v, static_cast<char*>(region) + 8, 4, cudaMemcpyDeviceToHost, as_stream(stream)))) return -1;
   if (!ZG_CUDA(cudaStreamSynchronize(as_stream(stream)))) return -1;
+  // read-and-clear: one failed launch is reported once, later launches start clean
+  if (v && !ZG_CUDA(cudaMemsetAsync(static_cast<char*>(region) + 8, 0, 4, as_stream(stream)))) return -1;
+  if (v && !ZG_CUDA(cudaStreamSynchronize(as_stream(stream)))) return -1;
   return (int)v;
+}
+
+static unsigned g_spin_limit = 0;  // 0 = not set yet
+extern "C" void zg_comm_set_spin_limit(unsigned polls) { g_spin_limit = polls ? polls : kArSpinLimit; }
+static unsigned spin_limit() {
+  if (g_spin_limit == 0) {
+    const char* v = getenv("ZG_SPIN_LIMIT");
+    const long n = v ? atol(v) : 0;
+    g_spin_limit = n > 0 ? (unsigned)n : kArSpinLimit;
+  }
+  return g_spin_limit;
 }
 
 static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigned rank, unsigned world, void* const* comm, len_t cap_elems,
@@ -289,6 +313,8 @@ static void allreduce_launch(StreamWrapper stream, void* grads, len_t n, unsigne
   a.nlr = -(float)lr;
   a.zero_grads = (params && zero_grads) ? 1 : 0;
   a.n = n; a.cap_pairs = cap_elems / 2; a.rank = rank; a.world = world;
+  a.spin_limit = spin_limit();
+  a.timeout_flag = kernel_timeout_flag();
   for (unsigned p = 0; p < world; ++p) {
     if (!comm[p]) { set_error(kBadArgument, "zg_allreduce_oneshot: comm region of rank %u is NULL", p); return; }
     a.comm[p] = static_cast<char*>(comm[p]);

@@ -240,12 +240,16 @@ __device__ __forceinline__ double dev_sqrt(double x) { return sqrt(x); }
 __device__ __forceinline__ float dev_tanh(float x) { return tanhf(x); }
 __device__ __forceinline__ double dev_tanh(double x) { return tanh(x); }
 
+__device__ __forceinline__ float dev_pow(float x, float e) { return powf(x, e); }
+__device__ __forceinline__ double dev_pow(double x, double e) { return pow(x, e); }
+
 template <typename T>
 struct UnaryF {
   int op;
   T p;
   __device__ T operator()(T x, T, T) const {
     switch (op) {
+      case ZG_UN_POW: return dev_pow(x, p);  // p = exponent
       case ZG_UN_EXP: return dev_exp(x);
       case ZG_UN_SQRT: return dev_sqrt(x);
       case ZG_UN_RSQRT: return T(1) / dev_sqrt(x > p ? x : p);  // 1/sqrt(max(x, eps))
@@ -272,6 +276,95 @@ struct UnaryBwdF {  // inputs (v, y_g, x_g)
     }
   }
 };
+
+// pow_bwd (host_device.zig:365-379): x_g += exp * x^(exp-1) * y_g, nothing where x < eps.  inputs (x, y_g, x_g)
+template <typename T>
+struct PowBwdF {
+  T e, em1, eps;
+  __device__ T operator()(T x, T yg, T xg) const { return (x < eps) ? xg : xg + e * dev_pow(x, em1) * yg; }
+};
+// tanh_inplace_bwd / sigm_inplace_bwd (host_device.zig:557-559, 569-571): the gradient is rescaled in
+// place by the derivative written in terms of the activation's OUTPUT x.  inputs (x, x_g)
+struct TanhInplaceBwdF { template <typename T> __device__ T operator()(T x, T xg, T) const { return xg * (T(1) - (x * x)); } };
+struct SigmInplaceBwdF { template <typename T> __device__ T operator()(T x, T xg, T) const { return xg * (x * (T(1) - x)); } };
+
+// ------------------------------------------------------------ byte-mask ops
+// One bit per element, eight elements per mask byte, bit b of byte i/8 for
+// element i (std.bit_set.IntegerBitSet(8), host_device.zig:16).  A thread owns
+// the eight elements of one mask byte: two 128-bit accesses per operand when the
+// pointers allow, one byte store (or load) for the mask.
+//   MODE 0 relu_mask_fwd  (host_device.zig:652-678): x <= 0 -> x = 0, bit set
+//   MODE 1 relu_mask_bwd  (:680-701):                bit set -> x_g = 0
+//   MODE 2 clamp_mask_fwd (:600-628): y = x (the reference stores the unclamped value), bit set where
+//                                      clamping changes x
+//   MODE 3 clamp_mask_bwd (:630-650): bit set -> x_g += y_g
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads) byte_mask_kernel(T* a, const T* b, unsigned char* mask, size_t n, T lo, T hi) {
+  const size_t nbytes = (n + 7) / 8, nth = (size_t)gridDim.x * blockDim.x;
+  const bool vec = aligned16(a) && (b == nullptr || aligned16(b));
+  ClampF<T> cl{lo, hi};
+  for (size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x; g < nbytes; g += nth) {
+    const size_t e0 = g * 8;
+    const int cnt = (int)((n - e0) < 8 ? (n - e0) : 8);
+    T va[8], vb[8];
+    const T* src = (MODE == 2) ? b : a;  // clamp_mask_fwd reads x (b) and writes y (a)
+    if (cnt == 8 && vec) {
+      constexpr int N = VecOf<T>::N;
+#pragma unroll
+      for (int q = 0; q < 8 / N; ++q) {
+        const Pack<T, N> pk = ldv(src + e0 + q * N);
+#pragma unroll
+        for (int j = 0; j < N; ++j) va[q * N + j] = pk.v[j];
+        if constexpr (MODE == 3) {
+          const Pack<T, N> pb = ldv(b + e0 + q * N);
+#pragma unroll
+          for (int j = 0; j < N; ++j) vb[q * N + j] = pb.v[j];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        va[j] = j < cnt ? src[e0 + j] : T(0);
+        if constexpr (MODE == 3) vb[j] = j < cnt ? b[e0 + j] : T(0);
+      }
+    }
+    unsigned bits = (MODE == 1 || MODE == 3) ? mask[g] : 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if constexpr (MODE == 0) {
+        if (j < cnt && va[j] <= T(0)) { va[j] = T(0); bits |= 1u << j; }
+      } else if constexpr (MODE == 1) {
+        if (bits & (1u << j)) va[j] = T(0);
+      } else if constexpr (MODE == 2) {
+        if (j < cnt && va[j] != cl(va[j], T(0), T(0))) bits |= 1u << j;
+      } else {
+        if (bits & (1u << j)) va[j] = va[j] + vb[j];
+      }
+    }
+    if constexpr (MODE == 0 || MODE == 2) mask[g] = (unsigned char)bits;
+    if (cnt == 8 && vec) {
+      constexpr int N = VecOf<T>::N;
+#pragma unroll
+      for (int q = 0; q < 8 / N; ++q) {
+        Pack<T, N> pk;
+#pragma unroll
+        for (int j = 0; j < N; ++j) pk.v[j] = va[q * N + j];
+        stv(a + e0 + q * N, pk);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < cnt) a[e0 + j] = va[j];
+    }
+  }
+}
+
+template <typename T, int MODE>
+void launch_byte_mask(cudaStream_t s, T* a, const T* b, unsigned char* mask, size_t n, T lo, T hi) {
+  if (n == 0) return;
+  byte_mask_kernel<T, MODE><<<grid_for((n + 7) / 8, kThreads * 2), kThreads, 0, s>>>(a, b, mask, n, lo, hi);
+  ZG_LAUNCH_CHECK();
+}
 
 // fp32 <-> bf16 casts
 __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
@@ -422,12 +515,38 @@ extern "C" void pow_exp(dtype id, StreamWrapper w, const void* x, void* y, len_t
   zg_unary_fwd(id, w, ZG_UN_EXP, x, y, n, 0.0);
 }
 extern "C" void zg_unary_fwd(dtype id, StreamWrapper w, int op, const void* x, void* y, len_t n, double p) {
-  if (op < ZG_UN_EXP || op > ZG_UN_SIGM) { set_error(kBadArgument, "zg_unary_fwd: unknown op %d", op); return; }
+  if (op < ZG_UN_EXP || op > ZG_UN_POW) { set_error(kBadArgument, "zg_unary_fwd: unknown op %d", op); return; }
   ZG_FLOAT_SWITCH("zg_unary_fwd", id, (launch_map<T, 1>(as_stream(w), (T*)y, (const T*)x, (const T*)nullptr, (const T*)nullptr, n, UnaryF<T>{op, (T)p})));
 }
 extern "C" void zg_unary_bwd(dtype id, StreamWrapper w, int op, const void* v, const void* y_g, void* x_g, len_t n, double p) {
   if (op < ZG_UN_EXP || op > ZG_UN_SIGM) { set_error(kBadArgument, "zg_unary_bwd: unknown op %d", op); return; }
   ZG_FLOAT_SWITCH("zg_unary_bwd", id, (launch_map<T, 3>(as_stream(w), (T*)x_g, (const T*)v, (const T*)y_g, (const T*)x_g, n, UnaryBwdF<T>{op, (T)p})));
+}
+
+extern "C" void zg_pow_bwd(dtype id, StreamWrapper w, const void* x, const void* y_g, void* x_g, len_t n, double exponent, double eps) {
+  ZG_FLOAT_SWITCH("zg_pow_bwd", id, (launch_map<T, 3>(as_stream(w), (T*)x_g, (const T*)x, (const T*)y_g, (const T*)x_g, n,
+                                                      PowBwdF<T>{(T)exponent, (T)exponent - T(1), (T)(float)eps})));
+}
+extern "C" void zg_unary_inplace_bwd(dtype id, StreamWrapper w, int op, const void* x, void* x_g, len_t n) {
+  if (op == ZG_UN_TANH) {
+    ZG_FLOAT_SWITCH("zg_unary_inplace_bwd", id, (launch_map<T, 2>(as_stream(w), (T*)x_g, (const T*)x, (const T*)x_g, (const T*)nullptr, n, TanhInplaceBwdF{})));
+  } else if (op == ZG_UN_SIGM) {
+    ZG_FLOAT_SWITCH("zg_unary_inplace_bwd", id, (launch_map<T, 2>(as_stream(w), (T*)x_g, (const T*)x, (const T*)x_g, (const T*)nullptr, n, SigmInplaceBwdF{})));
+  } else {
+    set_error(kBadArgument, "zg_unary_inplace_bwd: op %d has no in-place backward (tanh and sigmoid do)", op);
+  }
+}
+extern "C" void zg_relu_mask_fwd(dtype id, StreamWrapper w, void* x, unsigned char* mask, len_t n) {
+  ZG_FLOAT_SWITCH("zg_relu_mask_fwd", id, (launch_byte_mask<T, 0>(as_stream(w), (T*)x, (const T*)nullptr, mask, n, T(0), T(0))));
+}
+extern "C" void zg_relu_mask_bwd(dtype id, StreamWrapper w, void* x_g, const unsigned char* mask, len_t n) {
+  ZG_FLOAT_SWITCH("zg_relu_mask_bwd", id, (launch_byte_mask<T, 1>(as_stream(w), (T*)x_g, (const T*)nullptr, const_cast<unsigned char*>(mask), n, T(0), T(0))));
+}
+extern "C" void zg_clamp_mask_fwd(dtype id, StreamWrapper w, const void* x, void* y, unsigned char* mask, len_t n, double lo, double hi) {
+  ZG_FLOAT_SWITCH("zg_clamp_mask_fwd", id, (launch_byte_mask<T, 2>(as_stream(w), (T*)y, (const T*)x, mask, n, (T)lo, (T)hi)));
+}
+extern "C" void zg_clamp_mask_bwd(dtype id, StreamWrapper w, void* x_g, const void* y_g, const unsigned char* mask, len_t n) {
+  ZG_FLOAT_SWITCH("zg_clamp_mask_bwd", id, (launch_byte_mask<T, 3>(as_stream(w), (T*)x_g, (const T*)y_g, const_cast<unsigned char*>(mask), n, T(0), T(0))));
 }
 
 extern "C" void scale(dtype id, CublasWrapper w, void* a_data, len_t n, double alpha) {

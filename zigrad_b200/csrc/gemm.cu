@@ -196,7 +196,9 @@ static int* tc_error_flag() {
   if (!flags[dev]) {
     int* p = nullptr;
     if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    // the legacy stream does not order against the library's non-blocking streams: finish the clear here
     cudaMemset(p, 0, sizeof(int));
+    cudaDeviceSynchronize();
     flags[dev] = p;
   }
   return flags[dev];
@@ -486,6 +488,7 @@ void check_tc_errors() {
   int v = 0;
   if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && v) {
     cudaMemset(f, 0, sizeof(int));
+    cudaDeviceSynchronize();
     set_error(kKernelTimeout, "a kernel gave up waiting on a pipeline barrier");
   }
 }

@@ -1,6 +1,7 @@
-// Index ops: scatter_add, row gather, and the GCN degree-scaled edge scatter
-// with its backward.  Semantics: src/device/host_device.zig:1039-1086,
-// :1356-1403 and src/ndarray.zig:593-633.
+// Index ops: scatter_add (flat, blocked and CSR forms), CSR segment sums, row
+// gather, and the GCN degree-scaled edge scatter with its backward.  Semantics:
+// src/device/host_device.zig:1039-1086, :1137-1160, :1325-1351, :1356-1403 and
+// src/ndarray.zig:593-633.
 //
 // Accumulation into shared destinations uses red.global.add.f32; the values
 // added are the reference's, the order in which duplicates land is not.
@@ -123,9 +124,89 @@ __global__ void __launch_bounds__(kIThreads) csr_gcn_propagate_kernel(float* out
   }
 }
 
+// scatter_add_2d (host_device.zig:1137-1160): dst[indices[i], :] += src[i, :] for blocks of `stride`
+// contiguous elements; one thread per (block, element), consecutive threads on consecutive
+// elements of a block so both sides are coalesced.
+template <typename T>
+__global__ void __launch_bounds__(kIThreads) scatter_add_2d_kernel(const T* __restrict__ src, const len_t* __restrict__ indices, size_t n_blocks,
+                                                                   size_t stride, T* dst) {
+  const size_t total = n_blocks * stride, nth = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nth) {
+    const size_t blk = i / stride, j = i - blk * stride;
+    atomicAdd(dst + indices[blk] * stride + j, src[i]);
+  }
+}
+
+// scatter_add_csr (host_device.zig:1325-1335): dst[j] += src[i] for j in [row_ptr[i], row_ptr[i+1]).
+// A warp walks a segment; segments do not overlap, so no atomics and the result is exact.
+template <typename T>
+__global__ void __launch_bounds__(kIThreads) scatter_add_csr_kernel(const T* __restrict__ src, const len_t* __restrict__ row_ptr, size_t n_seg, T* dst) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_seg; r += warps) {
+    const len_t k0 = row_ptr[r], k1 = row_ptr[r + 1];
+    const T v = src[r];
+    for (len_t j = k0 + lane; j < k1; j += 32) dst[j] += v;
+  }
+}
+
+// segment_sum_csr (host_device.zig:1337-1351): dst[i] = sum of src[row_offsets[i] .. row_offsets[i+1]).
+// A warp per segment: lane l adds elements l, l+32, ... in order, then the 32 partial sums are
+// folded by a shuffle tree (fixed order, so repeatable; not the host's left-to-right order).
+template <typename T>
+__global__ void __launch_bounds__(kIThreads) segment_sum_csr_kernel(const T* __restrict__ src, const len_t* __restrict__ row_ptr, size_t n_seg, T* __restrict__ dst) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_seg; r += warps) {
+    const len_t k0 = row_ptr[r], k1 = row_ptr[r + 1];
+    T acc = T(0);
+    if (k1 - k0 <= 32) {  // short segment: lane 0 adds left to right, the host's order exactly
+      const T v = (k0 + lane < k1) ? src[k0 + lane] : T(0);
+      for (int l = 0; l < 32; ++l) {
+        const T u = __shfl_sync(0xffffffffu, v, l);
+        if ((len_t)l < k1 - k0) acc += u;
+      }
+    } else {
+      for (len_t j = k0 + lane; j < k1; j += 32) acc += src[j];
+      acc = warp_sum(acc);
+    }
+    if (lane == 0) dst[r] = acc;
+  }
+}
+
 }  // namespace zg
 
 using namespace zg;
+
+extern "C" void zg_scatter_add_2d(dtype id, StreamWrapper w, const void* src, const len_t* indices, len_t n_blocks, len_t stride, void* dst) {
+  if (n_blocks == 0 || stride == 0) return;
+  cudaStream_t s = as_stream(w);
+  const unsigned g = grid_for((size_t)n_blocks * stride, kIThreads * 2);
+  if (id == SINGLE) scatter_add_2d_kernel<float><<<g, kIThreads, 0, s>>>((const float*)src, indices, n_blocks, stride, (float*)dst);
+  else if (id == DOUBLE) scatter_add_2d_kernel<double><<<g, kIThreads, 0, s>>>((const double*)src, indices, n_blocks, stride, (double*)dst);
+  else { set_error(kUnsupported, "zg_scatter_add_2d: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_scatter_add_csr(dtype id, StreamWrapper w, const void* src, const len_t* row_ptr, len_t n_segments, void* dst) {
+  if (n_segments == 0) return;
+  cudaStream_t s = as_stream(w);
+  const unsigned g = grid_for(n_segments, kIThreads / 32);
+  if (id == SINGLE) scatter_add_csr_kernel<float><<<g, kIThreads, 0, s>>>((const float*)src, row_ptr, n_segments, (float*)dst);
+  else if (id == DOUBLE) scatter_add_csr_kernel<double><<<g, kIThreads, 0, s>>>((const double*)src, row_ptr, n_segments, (double*)dst);
+  else { set_error(kUnsupported, "zg_scatter_add_csr: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
+
+extern "C" void zg_segment_sum_csr(dtype id, StreamWrapper w, const void* src, const len_t* row_offsets, len_t n_segments, void* dst) {
+  if (n_segments == 0) return;
+  cudaStream_t s = as_stream(w);
+  const unsigned g = grid_for(n_segments, kIThreads / 32);
+  if (id == SINGLE) segment_sum_csr_kernel<float><<<g, kIThreads, 0, s>>>((const float*)src, row_offsets, n_segments, (float*)dst);
+  else if (id == DOUBLE) segment_sum_csr_kernel<double><<<g, kIThreads, 0, s>>>((const double*)src, row_offsets, n_segments, (double*)dst);
+  else { set_error(kUnsupported, "zg_segment_sum_csr: unsupported dtype %d", (int)id); return; }
+  ZG_LAUNCH_CHECK();
+}
 
 extern "C" void zg_scatter_add(dtype id, StreamWrapper w, const void* src, const len_t* offsets, len_t n, void* dst) {
   if (n == 0) return;

@@ -158,7 +158,8 @@ __global__ void random_kernel(T* __restrict__ p, size_t n, int normal, uint32_t 
 // Library-owned scratch ("workspace") per stream: partial results of the
 // two-stage reductions and split-K GEMMs live here.  Grown with cudaMalloc on
 // demand (so the first call of a given size must happen outside a stream
-// capture); never shrinks.  The first 256 bytes hold counters that kernels
+// capture); never shrinks, and an outgrown buffer stays allocated, so a graph
+// captured while it was current remains valid to replay.  The first 256 bytes hold counters that kernels
 // leave at zero when they finish.  Slot 0 holds kernel partials; slot 1 holds
 // intermediates of multi-stage host-sequenced reductions (which themselves
 // launch kernels that use slot 0).
@@ -168,6 +169,7 @@ struct Workspace {
 };
 static std::mutex g_ws_mu;
 static std::map<std::pair<std::pair<int, int>, cudaStream_t>, Workspace> g_ws;
+static std::vector<void*> g_ws_retired;
 
 bool pdl_enabled() {
   static const bool on = [] {
@@ -194,11 +196,13 @@ void* workspace(cudaStream_t s, size_t bytes, unsigned** counters, int slot) {
     }
     void* p = nullptr;
     if (!ZG_CUDA(cudaMalloc(&p, cap))) return nullptr;
-    if (!ZG_CUDA(cudaMemset(p, 0, cap))) return nullptr;  // counters (and slot 2, which its users keep at zero) start cleared
-    if (w.base) {
-      cudaStreamSynchronize(s);  // earlier kernels may still read the old buffer
-      cudaFree(w.base);
-    }
+    // counters (and slot 2, which its users keep at zero) start cleared; the clear is enqueued on the
+    // stream that will use the buffer, so the kernel launched next is ordered after it
+    if (!ZG_CUDA(cudaMemsetAsync(p, 0, cap, s))) return nullptr;
+    // The outgrown buffer is retired, not freed: graphs captured earlier on this stream hold its
+    // address in their kernel nodes and may be replayed after this call.  Capacities double, so all
+    // retired buffers together are smaller than the live one; they go back with the process.
+    if (w.base) g_ws_retired.push_back(w.base);
     w.base = p;
     w.bytes = cap;
   }
@@ -335,6 +339,24 @@ extern "C" void zg_stream_wait(StreamWrapper waiter, StreamWrapper signaller) {
   }
   if (!ZG_CUDA(cudaEventRecord(ev, as_stream(signaller)))) return;
   ZG_CUDA(cudaStreamWaitEvent(as_stream(waiter), ev, 0));
+}
+
+// Explicit events: a point of one stream that another stream (or the same one later) waits for.
+extern "C" void* zg_event_create(void) {
+  cudaEvent_t ev = nullptr;
+  if (!ZG_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming))) return nullptr;
+  return ev;
+}
+extern "C" void zg_event_destroy(void* event) {
+  if (event) ZG_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+}
+extern "C" void zg_event_record(void* event, StreamWrapper stream) {
+  if (!event) { set_error(kBadArgument, "zg_event_record: NULL event"); return; }
+  ZG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), as_stream(stream)));
+}
+extern "C" void zg_stream_wait_event(StreamWrapper stream, void* event) {
+  if (!event) { set_error(kBadArgument, "zg_stream_wait_event: NULL event"); return; }
+  ZG_CUDA(cudaStreamWaitEvent(as_stream(stream), static_cast<cudaEvent_t>(event), 0));
 }
 
 extern "C" void stream_synchronize(StreamWrapper stream) {

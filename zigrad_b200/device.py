@@ -24,6 +24,7 @@ from .abi import BF16, DOUBLE, SINGLE
 _NP2ID = {np.dtype(np.float32): SINGLE, np.dtype(np.float64): DOUBLE}
 _ITEMSIZE = {SINGLE: 4, DOUBLE: 8, BF16: 2}
 USIZE = 100  # pseudo dtype id for index buffers (u64); never passed to the library
+U8 = 101     # pseudo dtype id for byte masks (mem_alloc_byte_mask); never passed to the library
 
 
 @dataclass
@@ -37,7 +38,7 @@ class DeviceSlice:
 
     @property
     def itemsize(self) -> int:
-        return 8 if self.dtype == USIZE else _ITEMSIZE[self.dtype]
+        return 8 if self.dtype == USIZE else (1 if self.dtype == U8 else _ITEMSIZE[self.dtype])
 
     @property
     def nbytes(self) -> int:
@@ -216,6 +217,17 @@ class CudaDevice:
             raise DeviceOOM("mem_alloc(%d bytes)" % size)
         return DeviceSlice(p, n, dtype)
 
+    def mem_alloc_byte_mask(self, n: int) -> DeviceSlice:
+        """One bit per element: ceil(n/8) bytes (device_reference.zig:41-43)."""
+        nb = (n + 7) // 8
+        if nb == 0:
+            return DeviceSlice(0, 0, U8)
+        p = self.L.mem_alloc(nb, self.stream)
+        if not p:
+            abi.check()
+            raise DeviceOOM("mem_alloc_byte_mask(%d bytes)" % nb)
+        return DeviceSlice(p, nb, U8)
+
     def mem_free(self, s: DeviceSlice):
         if s.len:
             self.L.mem_free(s.ptr, self.stream)
@@ -266,6 +278,8 @@ class CudaDevice:
             dt = USIZE
         elif a.dtype == np.uint16:
             dt = BF16  # raw bfloat16 bit patterns
+        elif a.dtype == np.uint8:
+            dt = U8    # byte masks
         else:
             dt = _NP2ID[a.dtype]
         s = self.mem_cache_alloc(dt, a.size) if cached else self.mem_alloc(dt, a.size)
@@ -275,7 +289,7 @@ class CudaDevice:
         return s
 
     def to_numpy(self, s: DeviceSlice, shape=None) -> np.ndarray:
-        npdt = {SINGLE: np.float32, DOUBLE: np.float64, USIZE: np.uint64, BF16: np.uint16}[s.dtype]
+        npdt = {SINGLE: np.float32, DOUBLE: np.float64, USIZE: np.uint64, BF16: np.uint16, U8: np.uint8}[s.dtype]
         out = np.empty(s.len, npdt)
         if s.len:
             self.mem_transfer_dtoh(s, out)
@@ -391,6 +405,36 @@ class CudaDevice:
     def rsqrt_bwd(self, p):
         self.L.zg_unary_bwd(p.x.dtype, self.stream, abi.UN_RSQRT, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.eps)
 
+    def pow_fwd(self, p):
+        self.L.zg_unary_fwd(p.x.dtype, self.stream, abi.UN_POW, p.x.ptr, p.y.ptr, p.x.len, p.exp)
+
+    def pow_fwd_(self, p):
+        self.L.zg_unary_fwd(p.x.dtype, self.stream, abi.UN_POW, p.x.ptr, p.x.ptr, p.x.len, p.exp)
+
+    def pow_bwd(self, p):
+        self.L.zg_pow_bwd(p.x.dtype, self.stream, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.exp, p.eps)
+
+    def sqrt_fwd_(self, p):
+        self.L.zg_unary_fwd(p.x.dtype, self.stream, abi.UN_SQRT, p.x.ptr, p.x.ptr, p.x.len, 0.0)
+
+    def tanh_inplace_bwd(self, p):
+        self.L.zg_unary_inplace_bwd(p.x.dtype, self.stream, abi.UN_TANH, p.x.ptr, p.x_g.ptr, p.x.len)
+
+    def sigm_inplace_bwd(self, p):
+        self.L.zg_unary_inplace_bwd(p.x.dtype, self.stream, abi.UN_SIGM, p.x.ptr, p.x_g.ptr, p.x.len)
+
+    def relu_mask_fwd(self, p):
+        self.L.zg_relu_mask_fwd(p.x.dtype, self.stream, p.x.ptr, p.mask.ptr, p.x.len)
+
+    def relu_mask_bwd(self, p):
+        self.L.zg_relu_mask_bwd(p.x_g.dtype, self.stream, p.x_g.ptr, p.mask.ptr, p.x_g.len)
+
+    def clamp_mask_fwd(self, p):
+        self.L.zg_clamp_mask_fwd(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.mask.ptr, p.x.len, p.min, p.max)
+
+    def clamp_mask_bwd(self, p):
+        self.L.zg_clamp_mask_bwd(p.x_g.dtype, self.stream, p.x_g.ptr, p.y_g.ptr, p.mask.ptr, p.x_g.len)
+
     def relu_fwd(self, p):
         self.L.relu_fwd(p.x.dtype, self.stream, p.x.ptr, p.y.ptr, p.x.len)
 
@@ -430,6 +474,15 @@ class CudaDevice:
     # index ----------------------------------------------------------------------
     def scatter_add(self, p):
         self.L.zg_scatter_add(p.src.dtype, self.stream, p.src.ptr, p.offsets.ptr, p.src.len, p.dst.ptr)
+
+    def scatter_add_2d(self, p):
+        self.L.zg_scatter_add_2d(p.src.dtype, self.stream, p.src.ptr, p.indices.ptr, p.indices.len, p.stride, p.dst.ptr)
+
+    def scatter_add_csr(self, p):
+        self.L.zg_scatter_add_csr(p.src.dtype, self.stream, p.src.ptr, p.row_ptr.ptr, p.src.len, p.dst.ptr)
+
+    def segment_sum_csr(self, p):
+        self.L.zg_segment_sum_csr(p.src.dtype, self.stream, p.src.ptr, p.row_offsets.ptr, p.dst.len, p.dst.ptr)
 
     def scatter_gcn_deg_scaled(self, p):
         self.L.zg_scatter_gcn_deg_scaled(p.h.dtype, self.stream, p.dst.ptr, p.h.ptr, p.deg.ptr, p.src_indices.ptr,

@@ -171,6 +171,35 @@ class CudaDevice {
   template <typename T> void op(const opspec::relu_inplace_bwd<T>& p) { zg_relu_inplace_bwd(dtype_of<T>(), cur(), p.x.ptr, p.x_g.ptr, p.x.len); }
   template <typename T> void op(const opspec::clamp_fwd<T>& p) { clamp(dtype_of<T>(), cur(), p.x.ptr, p.y.ptr, p.x.len, p.min, p.max); }
   template <typename T> void op(const opspec::clamp_bwd<T>& p) { zg_clamp_bwd(dtype_of<T>(), cur(), p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.min, p.max); }
+  template <typename T> void op(const opspec::exp_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_EXP, p.x.ptr, p.y.ptr, p.x.len, 0.0); }
+  template <typename T> void op(const opspec::sqrt_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_SQRT, p.x.ptr, p.y.ptr, p.x.len, 0.0); }
+  template <typename T> void op(const opspec::sqrt_fwd_<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_SQRT, p.x.ptr, p.x.ptr, p.x.len, 0.0); }
+  template <typename T> void op(const opspec::rsqrt_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_RSQRT, p.x.ptr, p.y.ptr, p.x.len, p.eps); }
+  template <typename T> void op(const opspec::tanh_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_TANH, p.x.ptr, p.y.ptr, p.x.len, 0.0); }
+  template <typename T> void op(const opspec::sigm_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_SIGM, p.x.ptr, p.y.ptr, p.x.len, 0.0); }
+  template <typename T> void op(const opspec::pow_fwd<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_POW, p.x.ptr, p.y.ptr, p.x.len, p.exp); }
+  template <typename T> void op(const opspec::pow_fwd_<T>& p) { zg_unary_fwd(dtype_of<T>(), cur(), ZG_UN_POW, p.x.ptr, p.x.ptr, p.x.len, p.exp); }
+  template <typename T> void op(const opspec::exp_bwd<T>& p) { zg_unary_bwd(dtype_of<T>(), cur(), ZG_UN_EXP, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0); }
+  template <typename T> void op(const opspec::tanh_bwd<T>& p) { zg_unary_bwd(dtype_of<T>(), cur(), ZG_UN_TANH, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0); }
+  template <typename T> void op(const opspec::sigm_bwd<T>& p) { zg_unary_bwd(dtype_of<T>(), cur(), ZG_UN_SIGM, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0.0); }
+  template <typename T> void op(const opspec::sqrt_bwd<T>& p) { zg_unary_bwd(dtype_of<T>(), cur(), ZG_UN_SQRT, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.eps); }
+  template <typename T> void op(const opspec::rsqrt_bwd<T>& p) { zg_unary_bwd(dtype_of<T>(), cur(), ZG_UN_RSQRT, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.eps); }
+  template <typename T> void op(const opspec::pow_bwd<T>& p) { zg_pow_bwd(dtype_of<T>(), cur(), p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.exp, p.eps); }
+  template <typename T> void op(const opspec::tanh_inplace_bwd<T>& p) { zg_unary_inplace_bwd(dtype_of<T>(), cur(), ZG_UN_TANH, p.x.ptr, p.x_g.ptr, p.x.len); }
+  template <typename T> void op(const opspec::sigm_inplace_bwd<T>& p) { zg_unary_inplace_bwd(dtype_of<T>(), cur(), ZG_UN_SIGM, p.x.ptr, p.x_g.ptr, p.x.len); }
+  template <typename T> void op(const opspec::relu_mask_fwd<T>& p) { zg_relu_mask_fwd(dtype_of<T>(), cur(), p.x.ptr, p.mask.ptr, p.x.len); }
+  template <typename T> void op(const opspec::relu_mask_bwd<T>& p) { zg_relu_mask_bwd(dtype_of<T>(), cur(), p.x_g.ptr, p.mask.ptr, p.x_g.len); }
+  template <typename T> void op(const opspec::clamp_mask_fwd<T>& p) { zg_clamp_mask_fwd(dtype_of<T>(), cur(), p.x.ptr, p.y.ptr, p.mask.ptr, p.x.len, p.min, p.max); }
+  template <typename T> void op(const opspec::clamp_mask_bwd<T>& p) { zg_clamp_mask_bwd(dtype_of<T>(), cur(), p.x_g.ptr, p.y_g.ptr, p.mask.ptr, p.x_g.len); }
+  template <typename T> void op(const opspec::scatter_add_2d<T>& p) {
+    zg_scatter_add_2d(dtype_of<T>(), cur(), p.src.ptr, reinterpret_cast<const len_t*>(p.indices.ptr), p.indices.len, p.stride, p.dst.ptr);
+  }
+  template <typename T> void op(const opspec::scatter_add_csr<T>& p) {
+    zg_scatter_add_csr(dtype_of<T>(), cur(), p.src.ptr, reinterpret_cast<const len_t*>(p.row_ptr.ptr), p.src.len, p.dst.ptr);
+  }
+  template <typename T> void op(const opspec::segment_sum_csr<T>& p) {
+    zg_segment_sum_csr(dtype_of<T>(), cur(), p.src.ptr, reinterpret_cast<const len_t*>(p.row_offsets.ptr), p.dst.len, p.dst.ptr);
+  }
   template <typename T> void op(const opspec::max_fwd<T>& p) { ::max_fwd(dtype_of<T>(), cur(), p.x.ptr, p.y.ptr, p.x.len); }
   template <typename T> void op(const opspec::unbroadcast<T>& p) {
     std::vector<len_t> xs(p.x_shape.begin(), p.x_shape.end()), ys(p.y_shape.begin(), p.y_shape.end());

@@ -152,7 +152,120 @@ struct max_fwd {
   Slice<T> y;
 };
 
-// ---- shape-aware reductions (opspec.zig:457-531)
+// unary maps and their backward passes (opspec.zig:205-393)
+#define ZG_UNARY_FWD(NAME)                     \
+  template <typename T>                        \
+  struct NAME {                                \
+    static constexpr const char* name = #NAME; \
+    Slice<const T> x;                          \
+    Slice<T> y;                                \
+  };
+ZG_UNARY_FWD(exp_fwd)
+ZG_UNARY_FWD(sqrt_fwd)
+ZG_UNARY_FWD(tanh_fwd)
+ZG_UNARY_FWD(sigm_fwd)
+#undef ZG_UNARY_FWD
+#define ZG_UNARY_BWD_Y(NAME)                   \
+  template <typename T>                        \
+  struct NAME {                                \
+    static constexpr const char* name = #NAME; \
+    Slice<T> x_g;                              \
+    Slice<const T> y, y_g;                     \
+  };
+ZG_UNARY_BWD_Y(exp_bwd)
+ZG_UNARY_BWD_Y(tanh_bwd)
+ZG_UNARY_BWD_Y(sigm_bwd)
+#undef ZG_UNARY_BWD_Y
+#define ZG_INPLACE_BWD(NAME)                   \
+  template <typename T>                        \
+  struct NAME {                                \
+    static constexpr const char* name = #NAME; \
+    Slice<const T> x;                          \
+    Slice<T> x_g;                              \
+  };
+ZG_INPLACE_BWD(tanh_inplace_bwd)
+ZG_INPLACE_BWD(sigm_inplace_bwd)
+#undef ZG_INPLACE_BWD
+template <typename T>
+struct rsqrt_fwd {
+  static constexpr const char* name = "rsqrt_fwd";
+  Slice<const T> x;
+  Slice<T> y;
+  float eps;
+};
+template <typename T>
+struct sqrt_bwd {
+  static constexpr const char* name = "sqrt_bwd";
+  Slice<const T> x;
+  Slice<T> x_g;
+  Slice<const T> y_g;
+  float eps;
+};
+template <typename T>
+struct rsqrt_bwd {
+  static constexpr const char* name = "rsqrt_bwd";
+  Slice<const T> x;
+  Slice<T> x_g;
+  Slice<const T> y_g;
+  float eps;
+};
+template <typename T>
+struct sqrt_fwd_ {
+  static constexpr const char* name = "sqrt_fwd_";
+  Slice<T> x;
+};
+template <typename T>
+struct pow_fwd {
+  static constexpr const char* name = "pow_fwd";
+  Slice<const T> x;
+  T exp;
+  Slice<T> y;
+};
+template <typename T>
+struct pow_fwd_ {
+  static constexpr const char* name = "pow_fwd_";
+  Slice<T> x;
+  T exp;
+};
+template <typename T>
+struct pow_bwd {
+  static constexpr const char* name = "pow_bwd";
+  Slice<const T> x;
+  Slice<T> x_g;
+  T exp;
+  Slice<const T> y_g;
+  float eps;
+};
+// byte-mask activations (opspec.zig:438-475): one bit per element, ceil(n/8) mask bytes
+template <typename T>
+struct clamp_mask_fwd {
+  static constexpr const char* name = "clamp_mask_fwd";
+  Slice<const T> x;
+  Slice<T> y;
+  T min, max;
+  Slice<unsigned char> mask;
+};
+template <typename T>
+struct clamp_mask_bwd {
+  static constexpr const char* name = "clamp_mask_bwd";
+  Slice<T> x_g;
+  Slice<const T> y_g;
+  Slice<unsigned char> mask;
+};
+template <typename T>
+struct relu_mask_fwd {
+  static constexpr const char* name = "relu_mask_fwd";
+  Slice<T> x;
+  Slice<unsigned char> mask;
+};
+template <typename T>
+struct relu_mask_bwd {
+  static constexpr const char* name = "relu_mask_bwd";
+  Slice<T> x_g;
+  Slice<unsigned char> mask;
+};
+
+// ---- shape-aware reductions (opspec.zig:477-531)
 template <typename T>
 struct unbroadcast {
   static constexpr const char* name = "unbroadcast";
@@ -188,6 +301,29 @@ struct scatter_add {
   Slice<const T> src;
   Slice<const std::size_t> offsets;
   Slice<T> dst;
+};
+
+template <typename T>
+struct scatter_add_2d {
+  static constexpr const char* name = "scatter_add_2d";
+  Slice<const T> src;                  // [n_blocks, stride]
+  Slice<const std::size_t> indices;    // [n_blocks]
+  Slice<T> dst;                        // [n_segments, stride]
+  std::size_t stride;
+};
+template <typename T>
+struct scatter_add_csr {
+  static constexpr const char* name = "scatter_add_csr";
+  Slice<const T> src;                  // [n_segments]
+  Slice<const std::size_t> row_ptr;    // [n_segments + 1]
+  Slice<T> dst;                        // [total_elements]
+};
+template <typename T>
+struct segment_sum_csr {
+  static constexpr const char* name = "segment_sum_csr";
+  Slice<const T> src;                    // [total_elems]
+  Slice<const std::size_t> row_offsets;  // [n_segments + 1]
+  Slice<T> dst;                          // [n_segments]
 };
 
 // ---------------------------------------------------------------------------

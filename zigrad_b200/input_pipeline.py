@@ -6,8 +6,12 @@ The reference's MNIST loader builds one tensor per sample from CSV text and the
 step consumes host tensors directly (``examples/mnist/src/dataset.zig:11-67``);
 on a GPU the host-to-device copy of a batch (26 MB at batch 8192) costs more
 than the step itself, so it is overlapped here.  Ordering between the two
-streams uses ``zg_stream_wait`` only (no host synchronisation in steady
-state):
+streams uses one pair of events per staging slot (no host synchronisation in
+steady state): ``put`` records the slot's "copied" event right after that
+slot's copies and ``get`` makes the compute stream wait for the event of the
+slot it returns -- not for copies enqueued later; ``release`` records the
+slot's "consumed" event on the compute stream and the next ``put`` into that
+slot makes the copy stream wait for it -- not for later steps:
 
     stager = BatchStager(dev, [(B * 784, SINGLE), (B * 10, SINGLE)])
     stager.put([X0, T0])                       # pinned host arrays (stager.pinned_like / .pinned)
@@ -39,6 +43,10 @@ class BatchStager:
         self.slots: List[List[DeviceSlice]] = [[dev.mem_cache_alloc(dt, n) for n, dt in self.spec] for _ in range(self.depth)]
         self._pinned = []
         self._put = self._got = 0
+        self._copied = [dev.L.zg_event_create() for _ in range(self.depth)]
+        self._consumed = [dev.L.zg_event_create() for _ in range(self.depth)]
+        self._was_consumed = [False] * self.depth
+        abi.check()
         dev.sync()
 
     # ------------------------------------------------------------ host memory
@@ -65,28 +73,35 @@ class BatchStager:
         (asynchronous when the arrays are page-locked)."""
         if self._put - self._got >= self.depth:
             raise RuntimeError("all %d slots hold batches that were not released yet" % self.depth)
-        slot = self.slots[self._put % self.depth]
+        k = self._put % self.depth
+        slot = self.slots[k]
+        if self._was_consumed[k]:  # the step that last read this slot must be done before it is overwritten
+            self.dev.L.zg_stream_wait_event(self.copy_stream, self._consumed[k])
         for a, d in zip(arrays, slot):
             if a.nbytes != d.nbytes:
                 raise ValueError("batch tensor of %d bytes, slot holds %d" % (a.nbytes, d.nbytes))
             self.dev.L.memcpy_HtoD(d.ptr, a.ctypes.data, a.nbytes, self.copy_stream)
+        self.dev.L.zg_event_record(self._copied[k], self.copy_stream)
         self._put += 1
 
     def get(self) -> List[DeviceSlice]:
         """The oldest staged batch; the compute stream waits for its copy."""
         if self._got >= self._put:
             raise RuntimeError("no staged batch")
-        self.dev.L.zg_stream_wait(self.dev.stream, self.copy_stream)
-        return self.slots[self._got % self.depth]
+        k = self._got % self.depth
+        self.dev.L.zg_stream_wait_event(self.dev.stream, self._copied[k])
+        return self.slots[k]
 
     def current_slot(self) -> int:
         """Index of the slot get() returns next (for callers that keep one captured graph per slot)."""
         return self._got % self.depth
 
     def release(self) -> None:
-        """Call after the step that consumed get()'s batch was enqueued: later
-        copies into that slot wait for the compute stream up to this point."""
-        self.dev.L.zg_stream_wait(self.copy_stream, self.dev.stream)
+        """Call after the step that consumed get()'s batch was enqueued: the next
+        copy into that slot waits for the compute stream up to this point."""
+        k = self._got % self.depth
+        self.dev.L.zg_event_record(self._consumed[k], self.dev.stream)
+        self._was_consumed[k] = True
         self._got += 1
 
     def bytes_per_batch(self) -> int:
@@ -102,4 +117,7 @@ class BatchStager:
         for p in self._pinned:
             self.dev.L.zg_host_free_pinned(p)
         self._pinned = []
+        for ev in self._copied + self._consumed:
+            self.dev.L.zg_event_destroy(ev)
+        self._copied, self._consumed = [], []
         self.dev.L.deinit_stream(self.copy_stream)

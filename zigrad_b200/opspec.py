@@ -157,7 +157,34 @@ class clip_nrm2:
     delta: float
 
 
-# ---- non-linear (opspec.zig:205-455)
+# ---- non-linear (opspec.zig:205-475)
+@_op("pow_fwd")
+class pow_fwd:
+    x: Any
+    exp: float
+    y: Any
+
+
+@_op("pow_fwd_")
+class pow_fwd_:
+    x: Any
+    exp: float
+
+
+@_op("pow_bwd")
+class pow_bwd:
+    x: Any
+    x_g: Any
+    exp: float
+    y_g: Any
+    eps: float
+
+
+@_op("sqrt_fwd_")
+class sqrt_fwd_:
+    x: Any
+
+
 @_op("sqrt_fwd")
 class sqrt_fwd:
     x: Any
@@ -232,6 +259,18 @@ class tanh_bwd:
     y_g: Any
 
 
+@_op("tanh_inplace_bwd")
+class tanh_inplace_bwd:
+    x: Any
+    x_g: Any
+
+
+@_op("sigm_inplace_bwd")
+class sigm_inplace_bwd:
+    x: Any
+    x_g: Any
+
+
 @_op("sigm_fwd")
 class sigm_fwd:
     x: Any
@@ -276,7 +315,35 @@ class clamp_bwd:
     max: float
 
 
-# ---- shape-aware reductions (opspec.zig:457-531)
+@_op("clamp_mask_fwd")
+class clamp_mask_fwd:
+    x: Any
+    y: Any
+    min: float
+    max: float
+    mask: Any  # u8 device slice of ceil(n/8) bytes (mem_alloc_byte_mask)
+
+
+@_op("clamp_mask_bwd")
+class clamp_mask_bwd:
+    x_g: Any
+    y_g: Any
+    mask: Any
+
+
+@_op("relu_mask_fwd")
+class relu_mask_fwd:
+    x: Any
+    mask: Any
+
+
+@_op("relu_mask_bwd")
+class relu_mask_bwd:
+    x_g: Any
+    mask: Any
+
+
+# ---- shape-aware reductions (opspec.zig:477-531)
 @_op("unbroadcast")
 class unbroadcast:
     x: Any
@@ -326,6 +393,28 @@ class scatter_add:
     src: Any
     offsets: Any
     dst: Any
+
+
+@_op("scatter_add_2d")
+class scatter_add_2d:
+    src: Any       # [n_blocks, stride]
+    indices: Any   # u64 [n_blocks]
+    dst: Any       # [n_segments, stride]
+    stride: int
+
+
+@_op("scatter_add_csr")
+class scatter_add_csr:
+    src: Any       # [n_segments]
+    row_ptr: Any   # u64 [n_segments + 1]
+    dst: Any       # [total_elements]
+
+
+@_op("segment_sum_csr")
+class segment_sum_csr:
+    src: Any          # [total_elems]
+    row_offsets: Any  # u64 [n_segments + 1]
+    dst: Any          # [n_segments]
 
 
 @_op("scatter_gcn_deg_scaled")

@@ -176,6 +176,36 @@ pub fn sigm_fwd(self: *const Self, T: type, p: opspec.sigm_fwd(T)) void {
 pub fn sigm_bwd(self: *const Self, T: type, p: opspec.sigm_bwd(T)) void {
     cuda.zg_unary_bwd(dtype(T), self.context.stream, cuda.ZG_UN_SIGM, p.y.ptr, p.y_g.ptr, p.x_g.ptr, p.y.len, 0);
 }
+pub fn pow_fwd(self: *const Self, T: type, p: opspec.pow_fwd(T)) void {
+    cuda.zg_unary_fwd(dtype(T), self.context.stream, cuda.ZG_UN_POW, p.x.ptr, p.y.ptr, p.x.len, p.exp);
+}
+pub fn pow_fwd_(self: *const Self, T: type, p: opspec.pow_fwd_(T)) void {
+    cuda.zg_unary_fwd(dtype(T), self.context.stream, cuda.ZG_UN_POW, p.x.ptr, p.x.ptr, p.x.len, p.exp);
+}
+pub fn pow_bwd(self: *const Self, T: type, p: opspec.pow_bwd(T)) void {
+    cuda.zg_pow_bwd(dtype(T), self.context.stream, p.x.ptr, p.y_g.ptr, p.x_g.ptr, p.x.len, p.exp, p.eps);
+}
+pub fn sqrt_fwd_(self: *const Self, T: type, p: opspec.sqrt_fwd_(T)) void {
+    cuda.zg_unary_fwd(dtype(T), self.context.stream, cuda.ZG_UN_SQRT, p.x.ptr, p.x.ptr, p.x.len, 0);
+}
+pub fn tanh_inplace_bwd(self: *const Self, T: type, p: opspec.tanh_inplace_bwd(T)) void {
+    cuda.zg_unary_inplace_bwd(dtype(T), self.context.stream, cuda.ZG_UN_TANH, p.x.ptr, p.x_g.ptr, p.x.len);
+}
+pub fn sigm_inplace_bwd(self: *const Self, T: type, p: opspec.sigm_inplace_bwd(T)) void {
+    cuda.zg_unary_inplace_bwd(dtype(T), self.context.stream, cuda.ZG_UN_SIGM, p.x.ptr, p.x_g.ptr, p.x.len);
+}
+pub fn relu_mask_fwd(self: *const Self, T: type, p: opspec.relu_mask_fwd(T)) void {
+    cuda.zg_relu_mask_fwd(dtype(T), self.context.stream, p.x.ptr, p.mask.ptr, p.x.len);
+}
+pub fn relu_mask_bwd(self: *const Self, T: type, p: opspec.relu_mask_bwd(T)) void {
+    cuda.zg_relu_mask_bwd(dtype(T), self.context.stream, p.x_g.ptr, p.mask.ptr, p.x_g.len);
+}
+pub fn clamp_mask_fwd(self: *const Self, T: type, p: opspec.clamp_mask_fwd(T)) void {
+    cuda.zg_clamp_mask_fwd(dtype(T), self.context.stream, p.x.ptr, p.y.ptr, p.mask.ptr, p.x.len, p.min, p.max);
+}
+pub fn clamp_mask_bwd(self: *const Self, T: type, p: opspec.clamp_mask_bwd(T)) void {
+    cuda.zg_clamp_mask_bwd(dtype(T), self.context.stream, p.x_g.ptr, p.y_g.ptr, p.mask.ptr, p.x_g.len);
+}
 pub fn relu_fwd(self: *const Self, T: type, p: opspec.relu_fwd(T)) void {
     cuda.relu_fwd(dtype(T), self.context.stream, p.x.ptr, p.y.ptr, p.x.len);
 }
@@ -215,6 +245,15 @@ pub fn max_along(self: *const Self, T: type, p: opspec.max_along(T)) void {
 // ----------------------------------------------------------------------- index
 pub fn scatter_add(self: *const Self, T: type, p: opspec.scatter_add(T)) void {
     cuda.zg_scatter_add(dtype(T), self.context.stream, p.src.ptr, p.offsets.ptr, p.src.len, p.dst.ptr);
+}
+pub fn scatter_add_2d(self: *const Self, T: type, p: opspec.scatter_add_2d(T)) void {
+    cuda.zg_scatter_add_2d(dtype(T), self.context.stream, p.src.ptr, p.indices.ptr, p.indices.len, p.stride, p.dst.ptr);
+}
+pub fn scatter_add_csr(self: *const Self, T: type, p: opspec.scatter_add_csr(T)) void {
+    cuda.zg_scatter_add_csr(dtype(T), self.context.stream, p.src.ptr, p.row_ptr.ptr, p.src.len, p.dst.ptr);
+}
+pub fn segment_sum_csr(self: *const Self, T: type, p: opspec.segment_sum_csr(T)) void {
+    cuda.zg_segment_sum_csr(dtype(T), self.context.stream, p.src.ptr, p.row_offsets.ptr, p.dst.len, p.dst.ptr);
 }
 pub fn scatter_gcn_deg_scaled(self: *const Self, T: type, p: opspec.scatter_gcn_deg_scaled(T)) void {
     cuda.zg_scatter_gcn_deg_scaled(dtype(T), self.context.stream, p.dst.ptr, p.h.ptr, p.deg.ptr, p.src_indices.ptr, p.tgt_indices.ptr, p.stride, p.n_edge);
@@ -259,6 +298,15 @@ pub fn mem_alloc(self: *Self, T: type, n: usize) ![]T {
     if (n == 0) return &.{};
     const ptr: [*]T = @ptrCast(@alignCast(cuda.mem_alloc(n * @sizeOf(T), self.context.stream) orelse return Error.DeviceOOM));
     return ptr[0..n];
+}
+/// One bit per element: ceil(n/8) bytes (src/device/cuda_device.zig mem_alloc_byte_mask).
+pub fn mem_alloc_byte_mask(self: *Self, n: usize) ![]u8 {
+    return self.mem_alloc(u8, (n + 7) / 8);
+}
+pub fn mem_dupe(self: *Self, T: type, slice: anytype) ![]T {
+    const dst = try self.mem_alloc(T, slice.len);
+    self.mem_copy(T, slice, dst);
+    return dst;
 }
 pub fn mem_free(self: *Self, slice: anytype) void {
     if (slice.len == 0) return;
