@@ -166,7 +166,9 @@ EXTERN_C void zg_fold_rows(dtype id, StreamWrapper stream, const void* x, void* 
  * (cudaGetSymbolAddress); make that call before starting any stream capture.
  * Every call shares the one array per device and leaves its partial sums
  * there, so calls that overlap on the GPU (other streams) race; issue them on
- * one stream or order them with events. */
+ * one stream or order them with events.  The resolved address is cached per
+ * device for the life of the process: after a cudaDeviceReset of that device it
+ * is stale, so do not reset a device between calls. */
 EXTERN_C void zg_fold_rows_noalloc(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
                                    double alpha, double beta);
 EXTERN_C void zg_fold_cols(dtype id, StreamWrapper stream, const void* x, void* y, len_t row, len_t col,
@@ -342,6 +344,47 @@ EXTERN_C void zg_allreduce_oneshot(StreamWrapper stream, void* buf, len_t n, uns
  * zeros when zero_grads != 0 (the next step's zero_grad, as in zg_sgd_step). */
 EXTERN_C void zg_allreduce_sgd_oneshot(StreamWrapper stream, void* grads, void* params, len_t n, double lr,
                                        unsigned rank, unsigned world, void* const* comm, len_t cap_elems, int zero_grads);
+
+/* ------------------------------------------------------ library collectives
+ * The gradient exchange of a data-parallel step for buffers that are
+ * bandwidth-bound (the wide model's 218 MB of gradients): sum all-reduce,
+ * reduce-scatter and all-gather through NCCL over NVLink / NVSwitch, one
+ * communicator per process (= per GPU).  The reference has no distributed code
+ * (docs/roadmap.norg:74-76); the contract is "the same update as on a single
+ * device": gradients are summed over the ranks BEFORE clipping and the
+ * optimizer (src/nn/optim.zig:100-122, 177-234).
+ *
+ * NCCL is bound at run time: zg_nccl_load(path) loads the given library (NULL:
+ * $ZG_NCCL_LIB, then a copy already loaded in the process, then libnccl.so.2
+ * from the loader path) and returns its version code, 0 if none was found.  The
+ * other calls bind it on first use and set status 5 when there is none.
+ *
+ * Rendezvous: rank 0 calls zg_nccl_unique_id (128 bytes), hands the bytes to the
+ * other ranks over any host channel, then EVERY rank calls zg_comm_init_rank
+ * with its device current (collective, blocking).  All calls below are
+ * asynchronous on `stream`, in place where one buffer is given, and may be
+ * captured into a CUDA graph like any kernel launch.
+ *   zg_allreduce       buf[i] = sum over ranks of buf[i], n elements
+ *   zg_reduce_scatter  recv[i] = sum over ranks of send[rank*recv_n + i]
+ *                      (recv may point into send at rank*recv_n: in place)
+ *   zg_all_gather      recv[r*send_n + i] = rank r's send[i]
+ *                      (send may be recv + rank*send_n: in place)
+ * id is SINGLE, DOUBLE or BF16.
+ * zg_comm_peer_regions does the host-side set-up of the peer-memory all-reduce
+ * above over an existing communicator: exports my_region (from zg_comm_alloc),
+ * all-gathers the IPC handles and maps the peers' regions; regions_out[world]
+ * is then the `comm` argument of zg_allreduce_oneshot.  Returns 0 on success. */
+typedef struct { void* ptr; } CommWrapper;
+EXTERN_C int zg_nccl_load(const char* path);
+EXTERN_C void zg_nccl_unique_id(unsigned char* id_out128);
+EXTERN_C CommWrapper zg_comm_init_rank(const unsigned char* id128, unsigned rank, unsigned world);
+EXTERN_C void zg_comm_destroy(CommWrapper comm);
+EXTERN_C unsigned zg_comm_rank(CommWrapper comm);
+EXTERN_C unsigned zg_comm_world(CommWrapper comm);
+EXTERN_C void zg_allreduce(CommWrapper comm, void* buf, len_t n, dtype id, StreamWrapper stream);
+EXTERN_C void zg_reduce_scatter(CommWrapper comm, const void* send, void* recv, len_t recv_n, dtype id, StreamWrapper stream);
+EXTERN_C void zg_all_gather(CommWrapper comm, const void* send, void* recv, len_t send_n, dtype id, StreamWrapper stream);
+EXTERN_C int zg_comm_peer_regions(CommWrapper comm, void* my_region, void** regions_out, StreamWrapper stream);
 
 /* --------------------------------------------- stream-ordered caching allocator
  * Device-side replacement for the Zig CachingAllocator + BlockPool

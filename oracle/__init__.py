@@ -358,6 +358,10 @@ def unbroadcast_scratch_len(x_shape, y_shape) -> int:
     return 0 if n == xsz else n
 
 
+class ReferenceOutOfBounds(RuntimeError):
+    """The reference's algorithm would write past an output for these shapes."""
+
+
 def unbroadcast(x, x_shape, y, y_shape, alpha=1.0, beta=0.0):
     # the reference's own sizing rule (unbroadcast_scratch_len) under-allocates
     # when a leading fold is followed by an interior reduction; give the C
@@ -366,6 +370,8 @@ def unbroadcast(x, x_shape, y, y_shape, alpha=1.0, beta=0.0):
     scratch = np.zeros(max(n, 1), np.float32)
     rc = lib().orc_unbroadcast(_f(x), _shape(x_shape), len_t(len(x_shape)), _f(y), _shape(y_shape),
                                len_t(len(y_shape)), _f(scratch), C.c_float(alpha), C.c_float(beta))
+    if rc == 2:
+        raise ReferenceOutOfBounds("unbroadcast %s -> %s: the host code drops y's trailing ones and mis-aligns (or overruns) y" % (list(x_shape), list(y_shape)))
     assert rc == 0
     return y
 

@@ -527,7 +527,13 @@ int orc_unbroadcast(const float* x, const len_t* x_shape, len_t xnd, float* y,
   std::vector<len_t> xsv(x_shape, x_shape + xnd), ysv(y_shape, y_shape + ynd);
   while (!xsv.empty() && xsv.front() == 1) xsv.erase(xsv.begin());
   while (!ysv.empty() && ysv.front() == 1) ysv.erase(ysv.begin());
-  while (!ysv.empty() && ysv.back() == 1) ysv.pop_back();
+  bool trimmed_back = false;
+  while (!ysv.empty() && ysv.back() == 1) { ysv.pop_back(); trimmed_back = true; }
+  // With trailing ones trimmed off y the reference lines y's dimensions up against the wrong
+  // dimensions of x: for x [4,5,6] -> y [5,1] it folds 6 columns into the 5-element y (one past
+  // its end), for x [4,5,1] -> y [5,1] it writes y[0] only.  The restatement reports these
+  // shapes instead of reproducing an out-of-bounds write.
+  if (trimmed_back) return 2;
   len_t ones = (len_t)std::count(ysv.begin(), ysv.end(), (len_t)1);
   const len_t orig_x_rank = xnd;
   if (xsv.size() > ysv.size()) {

@@ -1,7 +1,10 @@
 """Worker of tests/test_gpu_peer_allreduce.py: one process per GPU (torchrun).
-Each rank fills a buffer with seeded values, all-reduces it with the one-shot
+Each rank fills a buffer with seeded values, all-reduces it with the
 peer-memory kernel several times (eagerly and from a captured graph) and
-compares with the sum computed on the host in rank order."""
+compares with the sum computed on the host in rank order; then the library
+collectives of the C ABI (zg_allreduce / zg_reduce_scatter / zg_all_gather).
+ZG_ALLREDUCE=2 in the environment makes the kernel under test the two-shot
+variant for buffers of 16384 elements and more."""
 import os
 import sys
 
@@ -14,15 +17,16 @@ def main():
     import torch
     import torch.distributed as dist
     from zigrad_b200.device import CudaDevice
-    from zigrad_b200.dp import PeerAllReduce
+    from zigrad_b200.dp import NcclComm, PeerAllReduce
 
     rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(local)
     dist.init_process_group("gloo")  # host channel only: the data path is the kernel under test
     dev = CudaDevice(local)
+    comm = NcclComm.from_torch_distributed(dev)  # carries the IPC handles of the comm regions
     ok = True
     for n in (1, 7, 1024, 109386, 300001):
-        ar = PeerAllReduce(dev, n)
+        ar = PeerAllReduce(dev, n, comm)
         for rep in range(3):
             host = [np.random.Generator(np.random.PCG64(1000 * rep + 10 * r + n % 7)).standard_normal(n).astype(np.float32) for r in range(world)]
             want = np.zeros(n, np.float32)
@@ -79,7 +83,7 @@ def main():
         ar.close()
     if "--time" in sys.argv:  # launch cost of the kernel alone, ranks in lockstep
         n = 109386
-        ar = PeerAllReduce(dev, n)
+        ar = PeerAllReduce(dev, n, comm)
         buf = dev.from_numpy(np.zeros(n, np.float32))
         for _ in range(20):
             ar(buf)
@@ -94,6 +98,34 @@ def main():
         dev.sync()
         print("rank %d: %.2f us per all-reduce of %d floats over %d ranks" % (rank, e0.elapsed_time(e1) * 2.0, n, world), flush=True)
         ar.close()
+    # the library collectives of the same communicator against the host sum (tolerance: the library picks the order)
+    for n in (5, 4096, 300001):
+        host = [np.random.Generator(np.random.PCG64(77 + 10 * r + n % 7)).standard_normal(n).astype(np.float32) for r in range(world)]
+        want = np.sum(np.stack(host).astype(np.float64), axis=0)
+        buf = dev.from_numpy(host[rank])
+        comm.allreduce(buf)
+        got = dev.to_numpy(buf)
+        if np.abs(got - want).max() > 1e-5 * max(1.0, np.abs(want).max()):
+            ok = False
+            print("rank %d: zg_allreduce mismatch n=%d" % (rank, n), flush=True)
+        dev.mem_cache_free(buf)
+    c = 1000
+    full = [np.random.Generator(np.random.PCG64(300 + r)).standard_normal(c * world).astype(np.float32) for r in range(world)]
+    buf = dev.from_numpy(full[rank])
+    comm.reduce_scatter(buf, buf.view(rank * c, c))          # in place: my part of the sum lands in my slice
+    got = dev.to_numpy(buf)[rank * c:(rank + 1) * c]
+    want = np.sum(np.stack(full).astype(np.float64), axis=0)[rank * c:(rank + 1) * c]
+    if np.abs(got - want).max() > 1e-5 * max(1.0, np.abs(want).max()):
+        ok = False
+        print("rank %d: zg_reduce_scatter mismatch" % rank, flush=True)
+    dev.mem_fill(buf, 0.0)
+    dev.mem_transfer_htod(np.full(c, float(rank + 1), np.float32), buf.view(rank * c, c))
+    comm.all_gather(buf.view(rank * c, c), buf)              # in place
+    if not np.array_equal(dev.to_numpy(buf), np.repeat(np.arange(1, world + 1, dtype=np.float32), c)):
+        ok = False
+        print("rank %d: zg_all_gather mismatch" % rank, flush=True)
+    dev.mem_cache_free(buf)
+    comm.close()
     flags = [None] * world
     dist.all_gather_object(flags, ok)
     if rank == 0:

@@ -213,6 +213,26 @@ def test_gemm_bf16_inputs(gpu, trans, m, n, k, c_bf16):
     assert rel_err(out.reshape(m, n), want) <= (4e-3 if c_bf16 else 1e-5), rel_err(out.reshape(m, n), want)
 
 
+def test_persistent_gemm_at_the_wide_mlp_shape_against_openblas(gpu):
+    """8192 x 4096 x 4096, NT, bf16 operands, fp32 result: the forward GEMM of the wide
+    MLP's hidden layers on the persistent 128x256-tile kernel, every element against the
+    CPU oracle (OpenBLAS sgemm on the bf16-rounded operands)."""
+    m, n, k = 8192, 4096, 4096
+    import os
+    oracle.set_threads(os.cpu_count() or 1)
+    g = rng(8192)
+    A, B = g.standard_normal((m, k)).astype(np.float32), g.standard_normal((n, k)).astype(np.float32)
+    Ar, Br = oracle.round_bf16(A.ravel()).reshape(m, k), oracle.round_bf16(B.ravel()).reshape(n, k)
+    want = ORC.bmm_acc(Ar, Br, np.zeros((m, n), np.float32), (1, m, k), (1, k, n), (1, m, n), False, True, k, k, n, 1.0, 0.0)
+    be = GpuBackend(gpu)
+    a, b = be.up(to_bf16_bits(A), np.uint16), be.up(to_bf16_bits(B), np.uint16)
+    c = be.up(np.zeros(m * n, np.float32))
+    gpu.dispatch(opspec.linear(a, b, c, m, n, k, False, True, k, k, n))
+    out = be.down(c).reshape(m, n)
+    # exact bf16 products, fp32 accumulation in a different order than the host's: k = 4096 terms
+    assert rel_err(out, want) <= 2e-5, rel_err(out, want)
+
+
 def test_gemm_double_precision_ffma(gpu):
     g = rng(99)
     A, B = g.standard_normal((70, 50)), g.standard_normal((50, 30))

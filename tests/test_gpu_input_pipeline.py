@@ -56,3 +56,38 @@ def test_staged_batches_give_the_same_losses_as_resident_batches(gpu):
     ref.free()
     tr.free()
     gpu.mem_cache_free(losses)
+
+
+def test_packed_batches_with_index_labels_follow_the_oracle(gpu):
+    """One copy per batch (pixels and u64 class indices packed into one pinned buffer) and the
+    documented put-before-get order: losses follow the CPU oracle fed with one-hot rows."""
+    from zigrad_b200.device import USIZE
+    dims, B, steps = [48, 32, 10], 256, 5
+    g = np.random.Generator(np.random.PCG64(18))
+    Ws, bs = kaiming_uniform(dims, 6)
+    data = []
+    for i in range(steps):
+        X = g.uniform(0, 1, (B, dims[0])).astype(np.float32)
+        lab = g.integers(0, dims[-1], B).astype(np.uint64)
+        data.append((X, lab))
+    cpu = oracle.MlpOracle(dims, Ws, bs, "sgd", lr=0.05)
+    want = [cpu.step(X, np.eye(dims[-1], dtype=np.float32)[lab.astype(np.int64)]) for X, lab in data]
+    tr = MlpTrainer(gpu, dims, B, Ws, bs, "sgd", lr=0.05, index_labels=True)
+    st = BatchStager(gpu, [(B * dims[0], SINGLE), (B, USIZE)], packed=True)
+    assert st.bytes_per_batch() == B * dims[0] * 4 + B * 8   # both sizes are multiples of 256 here: no padding
+    packed = [st.pack([X, lab]) for X, lab in data]
+    losses = gpu.from_numpy(np.zeros(steps, np.float32))
+    st.put(packed[0])
+    for i in range(steps):
+        if i + 1 < steps:
+            st.put(packed[i + 1])
+        Xd, Td = st.get()
+        tr.step(Xd, Td)
+        gpu.mem_copy(tr.loss, losses.view(i, 1))
+        st.release()
+    got = gpu.to_numpy(losses)
+    for a, b in zip(got, want):
+        assert abs(a - b) <= 1e-4 * abs(b), (got, want)
+    st.close()
+    tr.free()
+    gpu.mem_cache_free(losses)

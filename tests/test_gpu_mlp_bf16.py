@@ -119,3 +119,55 @@ def test_bf16_adam_keeps_master_and_copy_in_step(gpu):
     tr.free()
     gpu.mem_cache_free(Xd)
     gpu.mem_cache_free(Td)
+
+
+def test_wide_mlp_full_size_shard_against_the_oracle(gpu):
+    """The wide-MLP configuration at its real size: one GPU's 8192-row shard of
+    4096->4096->4096->4096->1000 (the persistent 128x256-tile bf16 kernels and the
+    staged softmax kernel at the shapes the benchmark runs), one forward/backward
+    against the CPU oracle on bf16-rounded operands.  About 2.4 TFLOP of OpenBLAS
+    on the host cores: seconds."""
+    dims, B = [4096, 4096, 4096, 4096, 1000], 8192
+    oracle.set_threads(__import__("os").cpu_count() or 1)
+    g = rng(4096)
+    Ws, bs = kaiming_uniform(dims, 5)
+    bs = [g.standard_normal(b.size).astype(np.float32) * 0.05 for b in bs]
+    X = g.standard_normal((B, dims[0])).astype(np.float32)
+    labels = g.integers(0, dims[-1], B)
+    want_loss, act, dact, dW, db = bf16_step_oracle(dims, Ws, bs, X, labels, 65536)
+    tr = MlpTrainer(gpu, dims, B, Ws, bs, "none", fused=True, bf16=True, loss_div=65536)
+    Xd, Td = gpu.from_numpy(bits(X)), gpu.from_numpy(labels.astype(np.uint64))
+    tr.step(Xd, Td)
+    assert abs(tr.read_loss() - want_loss) <= 1e-3 * abs(want_loss), (tr.read_loss(), want_loss)
+    L = len(dims) - 1
+    # ReLU is discontinuous in its mask: among 33.5 M pre-activations per layer a few lie within an fp32
+    # accumulation-order difference of zero and land on different sides, which switches that element's
+    # gradient on or off -- and, one layer further down, shifts the WHOLE row of dX = dY.W that the
+    # element feeds.  Such flips must be rare and confined to activations near zero; gradients are
+    # compared on the rows no flip has touched (the large majority), where they must agree to the
+    # stated tolerance.
+    touched = np.zeros(B, bool)
+    for l in range(L - 1, -1, -1):
+        tol = 2e-3 if l + 1 == L else 1e-2
+        got = tr.act_numpy(l)
+        assert rel_err(got, act[l]) <= tol, ("act", l, rel_err(got, act[l]))
+        gd, want_d = tr.act_numpy(l, grad=True), dact[l]
+        if l + 1 < L:
+            flip = (got > 0) != (act[l] > 0)
+            assert flip.mean() <= 1e-4, ("mask flips", l, flip.mean())
+            assert np.all(np.maximum(got, act[l])[flip] <= 1e-2 * np.abs(act[l]).max()), ("flip away from zero", l)
+            gd, want_d = np.where(flip, 0, gd), np.where(flip, 0, want_d)
+        clean = ~touched
+        assert clean.mean() >= 0.5, ("rows without a mask flip above them", l, clean.mean())
+        assert rel_err(gd[clean], want_d[clean]) <= tol, ("dact", l, rel_err(gd[clean], want_d[clean]))
+        # the touched rows are not wild either: a flipped element moves a row by a fraction of the largest entry
+        assert rel_err(gd, want_d) <= 0.2, ("dact, all rows", l, rel_err(gd, want_d))
+        if l + 1 < L:
+            touched |= flip.any(1)
+    gW, gb = tr.get_grads()
+    for l in range(L):
+        assert rel_err(gW[l], dW[l]) <= 2e-3, ("dW", l, rel_err(gW[l], dW[l]))
+        assert rel_err(gb[l], db[l]) <= 2e-3, ("db", l, rel_err(gb[l], db[l]))
+    tr.free()
+    gpu.mem_cache_free(Xd)
+    gpu.mem_cache_free(Td)

@@ -134,12 +134,31 @@ def test_sum_along_and_max_along(gpu, shape, dim):
     np.testing.assert_array_equal(be.max_along(x, shape, dim), ORC.max_along(x, shape, dim))  # selection: bit-exact
 
 
-@pytest.mark.parametrize("xs,ys", [((2, 3, 3), (3,)), ((2, 3, 3), (2, 1, 3)), ((64, 128), (128,)), ((4, 5, 6), (5, 1)),
+@pytest.mark.parametrize("xs,ys", [((2, 3, 3), (3,)), ((2, 3, 3), (2, 1, 3)), ((64, 128), (128,)), ((1, 4, 5), (5,)),
                                    ((4, 5, 6), (1, 5, 6)), ((3, 4), (3, 4)), ((2, 3, 4, 5), (3, 1, 5)), ((8, 7), (1,))])
 def test_unbroadcast(gpu, xs, ys):
     g = rng(len(xs) * 100 + len(ys))
     x, y0 = g.standard_normal(int(np.prod(xs))).astype(np.float32), g.standard_normal(int(np.prod(ys))).astype(np.float32)
     got, want = GpuBackend(gpu).unbroadcast(x, xs, y0, ys, 1.0, 1.0), ORC.unbroadcast(x, xs, y0, ys, 1.0, 1.0)
+    assert rel_err(got, want) <= 2e-6, (got, want)
+
+
+@pytest.mark.parametrize("xs,ys", [((4, 5, 6), (5, 1)), ((3, 2, 7, 4), (2, 1, 1)), ((6, 9), (6, 1)), ((4, 5, 1), (5, 1))])
+def test_unbroadcast_onto_trailing_ones_stays_inside_y(gpu, xs, ys):
+    """y shapes that END in ones: the host code drops them and then lines y up against the wrong
+    dimensions of x -- it folds x's last dimension into y, past y's end, or fills y[0] only (the
+    oracle reports these shapes instead of restating an out-of-bounds write).  The device keeps
+    the alignment: the sums that the broadcasting rule defines, and nothing outside y (the guard
+    regions around y are checked)."""
+    import oracle
+    g = rng(sum(xs) + len(ys))
+    x, y0 = g.standard_normal(int(np.prod(xs))).astype(np.float32), g.standard_normal(int(np.prod(ys))).astype(np.float32)
+    with pytest.raises(oracle.ReferenceOutOfBounds):
+        ORC.unbroadcast(x, xs, y0, ys, 1.0, 1.0)
+    lead = len(xs) - len(ys)
+    axes = tuple(range(lead)) + tuple(lead + i for i, (a, b) in enumerate(zip(xs[lead:], ys)) if b == 1 and a != 1)
+    want = 0.5 * x.reshape(xs).astype(np.float64).sum(axes).ravel() + 2.0 * y0
+    got = GpuBackend(gpu).unbroadcast(x, xs, y0, ys, 0.5, 2.0)
     assert rel_err(got, want) <= 2e-6, (got, want)
 
 

@@ -10,15 +10,19 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_peer_allreduce_matches_host_sum_on_all_ranks():
+@pytest.mark.parametrize("variant", ["default", "two-shot"])
+def test_peer_allreduce_matches_host_sum_on_all_ranks(variant):
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    world = 4 if n >= 4 else 2
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
-           "--master-port", "29631", os.path.join(here, "peer_allreduce_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+           "--master-port", "29631" if variant == "default" else "29633", os.path.join(here, "peer_allreduce_worker.py")]
+    env = dict(os.environ)
+    if variant == "two-shot":  # what 8 ranks run by default for the step's gradient buffer; forced here at any world size
+        env["ZG_ALLREDUCE"] = "2"
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "PEER_ALLREDUCE_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -14,17 +14,14 @@ def main():
     import torch.distributed as dist
     from zigrad_b200.abi import BF16
     from zigrad_b200.device import CudaDevice
-    from zigrad_b200.dp import OverlappedGradAllReduce, ZeroShardedAdam
+    from zigrad_b200.dp import NcclComm, OverlappedGradAllReduce, ZeroShardedAdam
     from zigrad_b200.mlp import MlpTrainer, kaiming_uniform
 
     rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ts = torch.cuda.Stream()
-    dev = CudaDevice(local, stream=ts.cuda_stream)
-    with dev.branch():
-        pass
-    side = torch.cuda.ExternalStream(dev._side.ptr)
+    dist.init_process_group("gloo")  # host channel only: the collectives are the library's own (C ABI)
+    dev = CudaDevice(local)
+    comm = NcclComm.from_torch_distributed(dev)
     dims, B = [256, 256, 128, 64], 256
     Ws, bs = kaiming_uniform(dims, 5)
     g = np.random.Generator(np.random.PCG64(100 + rank))
@@ -36,12 +33,12 @@ def main():
     Td = dev.from_numpy(lab)
     mk = lambda: MlpTrainer(dev, dims, B, Ws, bs, "adam", lr=1e-3, clip=True, max_norm=0.05, bf16=True, loss_div=B * world)
     a, b = mk(), mk()
-    red, zopt = OverlappedGradAllReduce(), ZeroShardedAdam(b, ts, side)
+    red, zopt = OverlappedGradAllReduce(comm), ZeroShardedAdam(b, comm)
     ok = True
     for step in range(3):
         a.forward(Xd); a.loss_and_grad(Td)
-        a.backward(Xd, on_layer_grads=lambda l: red.start(a.layer_grads(l), side))
-        red.finish(ts)
+        a.backward(Xd, on_layer_grads=lambda l: red.start(a.layer_grads(l)))
+        red.finish()
         a.update()
         b.forward(Xd); b.loss_and_grad(Td)
         b.backward(Xd, on_layer_grads=zopt.start)
@@ -74,6 +71,7 @@ def main():
     dist.all_gather_object(flags, ok)
     if rank == 0:
         print("ZERO_DP_OK" if all(flags) else "ZERO_DP_FAILED", flush=True)
+    comm.close()
     dist.barrier()
     dist.destroy_process_group()
 

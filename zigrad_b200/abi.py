@@ -61,6 +61,10 @@ class CacheWrapper(_Handle):
     pass
 
 
+class CommWrapper(_Handle):
+    pass
+
+
 class CutensorPlanWrapper(C.Structure):
     _fields_ = [("plan", vp), ("scratch_len", len_t)]
 
@@ -210,6 +214,17 @@ SIGNATURES = {
     "zg_comm_set_spin_limit": (None, [C.c_uint]),
     "zg_allreduce_oneshot": (None, [S, vp, len_t, C.c_uint, C.c_uint, C.POINTER(vp), len_t]),
     "zg_allreduce_sgd_oneshot": (None, [S, vp, vp, len_t, dbl, C.c_uint, C.c_uint, C.POINTER(vp), len_t, i32]),
+    # ---- library collectives (NCCL bound at run time)
+    "zg_nccl_load": (C.c_int, [C.c_char_p]),
+    "zg_nccl_unique_id": (None, [u8p]),
+    "zg_comm_init_rank": (CommWrapper, [u8p, C.c_uint, C.c_uint]),
+    "zg_comm_destroy": (None, [CommWrapper]),
+    "zg_comm_rank": (C.c_uint, [CommWrapper]),
+    "zg_comm_world": (C.c_uint, [CommWrapper]),
+    "zg_allreduce": (None, [CommWrapper, vp, len_t, dtype_t, S]),
+    "zg_reduce_scatter": (None, [CommWrapper, vp, vp, len_t, dtype_t, S]),
+    "zg_all_gather": (None, [CommWrapper, vp, vp, len_t, dtype_t, S]),
+    "zg_comm_peer_regions": (C.c_int, [CommWrapper, vp, C.POINTER(vp), S]),
     "zg_scatter_add": (None, [dtype_t, S, vp, vp, len_t, vp]),
     "zg_scatter_add_2d": (None, [dtype_t, S, vp, vp, len_t, len_t, vp]),
     "zg_scatter_add_csr": (None, [dtype_t, S, vp, vp, len_t, vp]),

@@ -1,7 +1,8 @@
 """Timing of the other benchmark configurations on one GPU (bench.py at the
-repository root covers the headline one, the batch-8192 MLP).
+repository root covers the headline one, the batch-8192 MLP, and calls run()
+and run_c3_dp() of this module for its "configs" record).
 
-    python -m zigrad_b200.configs_bench [--configs c1,c3,c4,c5] [--no-cpu]
+    python -m zigrad_b200.configs_bench [--configs c1,c3,c4,c5]
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m zigrad_b200.configs_bench --dp
 
   c1  MLP 784-128-64-10, batch 64, fp32 (3xTF32), SGD           -> samples/s, us/step
@@ -12,16 +13,16 @@ repository root covers the headline one, the batch-8192 MLP).
 
 Every step is captured into one CUDA graph and replayed; times come from CUDA
 events on the device stream.  Inputs are seeded synthetic tensors
-(zigrad_b200.synthetic).  With the CPU legs enabled, the same steps are timed
-on the host cores through the oracle package (test infrastructure that
-restates the reference's BLAS backend); one JSON line per configuration.
+(zigrad_b200.synthetic).  A caller that wants a host-side timing of the same
+step beside each row passes `host_leg(name, **inputs) -> dict`: it receives the
+host arrays a configuration was built from and returns keys to merge into the
+row (bench.py times the CPU path that way).  One JSON line per configuration.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
-import time
 
 import numpy as np
 
@@ -49,16 +50,7 @@ def _graph_time(dev, ts, fn, reps):
     return us, n
 
 
-def _cpu_time(fn, reps, warm=2):
-    for _ in range(warm):
-        fn()
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        fn()
-    return (time.perf_counter() - t0) / reps * 1e6
-
-
-def run(configs, cpu=True, reps=200):
+def run(configs, reps=200, dev=None, ts=None, host_leg=None):
     import torch
     from . import synthetic
     from .device import CudaDevice
@@ -66,14 +58,10 @@ def run(configs, cpu=True, reps=200):
     from .gcn import GcnTrainer
     from .mlp import MlpTrainer, kaiming_uniform
 
-    ts = torch.cuda.Stream()
-    dev = CudaDevice(0, stream=ts.cuda_stream)
-    cores = os.cpu_count() or 1
-    if cpu:
-        import oracle
-        from oracle.nets import DqnOracle, GcnOracle
-        oracle.lib()
-        oracle.set_threads(cores)
+    if dev is None:
+        ts = torch.cuda.Stream()
+        dev = CudaDevice(0, stream=ts.cuda_stream)
+    leg = host_leg or (lambda name, **kw: {})
     out = []
 
     if "c1" in configs:
@@ -84,12 +72,11 @@ def run(configs, cpu=True, reps=200):
         Xd, Td = dev.from_numpy(X), dev.from_numpy(T)
         us, n = _graph_time(dev, ts, lambda: tr.step(Xd, Td), reps * 5 if reps >= 50 else reps)
         row = {"config": "c1 MLP 784-128-64-10 b64 fp32 SGD", "us_per_step": us, "samples_per_s": B / us * 1e6, "kernels": n}
-        if cpu:
-            m = oracle.MlpOracle(dims, Ws, bs, "sgd", lr=0.01)
-            cus = _cpu_time(lambda: m.step(X, T), 200)
-            row.update(cpu_us_per_step=cus, cpu_samples_per_s=B / cus * 1e6, cpu_cores=cores)
+        row.update(leg("c1", dims=dims, Ws=Ws, bs=bs, X=X, T=T))
         out.append(row)
         tr.free()
+        dev.mem_cache_free(Xd)
+        dev.mem_cache_free(Td)
 
     if "c3" in configs:
         dims, B = [4096, 4096, 4096, 4096, 1000], 8192
@@ -107,8 +94,11 @@ def run(configs, cpu=True, reps=200):
         flops = 293011456.0 * B  # fwd + dW + dX, algorithmic
         row = {"config": "c3 MLP 4096x3-1000 bf16/fp32-acc Adam, 8192-row shard of global 65536", "us_per_step": us,
                "samples_per_s": B / us * 1e6, "TFLOPs": flops / us * 1e-6, "kernels": n}
+        row.update(leg("c3", dims=dims, Ws=Ws, bs=bs, X=X, labels=lab))
         out.append(row)
         tr.free()
+        for s_ in (xf, Xd, Td):
+            dev.mem_cache_free(s_)
 
     if "c4" in configs:
         N, F, H, C, M = 2708, 1433, 16, 7, 140
@@ -124,10 +114,7 @@ def run(configs, cpu=True, reps=200):
         us, n = _graph_time(dev, ts, lambda: tr.step(Td), reps)
         row = {"config": "c4 GCN dense 2708 nodes, 1433-16-7, Adam", "us_per_step": us, "steps_per_s": 1e6 / us,
                "GFLOPs": 924.8e6 / us * 1e-3, "kernels": n}
-        if cpu:
-            m = GcnOracle(A, W1, b1, W2, b2)
-            cus = _cpu_time(lambda: m.step(X, T, mask), 20)
-            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        row.update(leg("c4", A=A, W1=W1, b1=b1, W2=W2, b2=b2, X=X, T=T, mask=mask))
         out.append(row)
         tr.free()
         # the reference's own algorithm for the same graph: edge scatter (here: CSR walk) instead of the dense product
@@ -135,13 +122,10 @@ def run(configs, cpu=True, reps=200):
         trs = GcnTrainer(dev, None, X, W1, b1, W2, b2, mask, edges=(src, tgt, deg))
         us, n = _graph_time(dev, ts, lambda: trs.step(Td), reps)
         row = {"config": "c4s GCN sparse propagation (edge list, CSR walk), same graph", "us_per_step": us, "steps_per_s": 1e6 / us, "kernels": n}
-        if cpu:
-            from oracle.nets import GcnSparseOracle
-            m = GcnSparseOracle(src, tgt, deg, W1, b1, W2, b2)
-            cus = _cpu_time(lambda: m.step(X, T, mask), 20)
-            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        row.update(leg("c4s", src=src, tgt=tgt, deg=deg, W1=W1, b1=b1, W2=W2, b2=b2, X=X, T=T, mask=mask))
         out.append(row)
         trs.free()
+        dev.mem_cache_free(Td)
 
     if "c5" in configs:
         dims = [4, 128, 128, 2]
@@ -151,38 +135,39 @@ def run(configs, cpu=True, reps=200):
         devb = [dev.from_numpy(x) for x in batch]
         us, n = _graph_time(dev, ts, lambda: tr.step(*devb), reps * 5 if reps >= 50 else reps)
         row = {"config": "c5 DQN 4-128-128-2 x2 nets, b256, Huber, Adam", "us_per_step": us, "kernels": n}
-        if cpu:
-            m = DqnOracle(dims, Ws, bs)
-            cus = _cpu_time(lambda: m.step(*batch), 200)
-            row.update(cpu_us_per_step=cus, cpu_cores=cores)
+        row.update(leg("c5", dims=dims, Ws=Ws, bs=bs, batch=batch))
         out.append(row)
         tr.free()
+        for s_ in devb:
+            dev.mem_cache_free(s_)
     return out
 
 
-def run_c3_dp(steps=20, warmup=5, zero=False):
+def run_c3_dp(steps=20, warmup=5, zero=False, dev=None, ts=None, comm=None, quiet=False):
     """Config c3 data-parallel: one process per GPU (torchrun), 8192 rows per
     GPU (the global batch of 65536 at 8 GPUs; weak scaling below that), the
-    gradient of each layer all-reduced over NCCL as soon as its weight-gradient
-    GEMM has been issued, Adam after the last reduction.  Eager launches (17
-    kernels of ~0.1 ms each per step).  Rank 0 prints one JSON line; the time
-    is the maximum over ranks of the CUDA-event time of `steps` steps."""
+    gradient of each layer reduced through the library's collectives
+    (zg_allreduce, or zg_reduce_scatter with `zero`) on a communication stream
+    as soon as its weight-gradient GEMM has been issued, Adam after the last
+    reduction.  Eager launches (17 kernels of ~0.1 ms each per step).  Returns
+    the result row on rank 0 (and prints it as one JSON line unless `quiet`);
+    the time is the maximum over ranks of the CUDA-event time of `steps` steps."""
     import torch
     import torch.distributed as dist
     from .abi import BF16
     from .device import CudaDevice
-    from .dp import OverlappedGradAllReduce, ZeroShardedAdam
+    from .dp import NcclComm, OverlappedGradAllReduce, ZeroShardedAdam
     from .mlp import MlpTrainer, kaiming_uniform
 
     rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ts = torch.cuda.Stream()
-    dev = CudaDevice(local, stream=ts.cuda_stream)
-    with dev.branch():
-        pass
-    side = torch.cuda.ExternalStream(dev._side.ptr)
+    own = dev is None
+    if own:
+        torch.cuda.set_device(local)
+        if world > 1:
+            dist.init_process_group("gloo")  # host channel for the rendezvous id, barriers and the max over ranks
+        ts = torch.cuda.Stream()
+        dev = CudaDevice(local, stream=ts.cuda_stream)
+        comm = NcclComm.from_torch_distributed(dev) if world > 1 else None
     dims, B = [4096, 4096, 4096, 4096, 1000], 8192
     Ws, bs = kaiming_uniform(dims, 5)  # same seed on every rank: replicated parameters
     g = np.random.Generator(np.random.PCG64(100 + rank))
@@ -193,8 +178,8 @@ def run_c3_dp(steps=20, warmup=5, zero=False):
     Xd = dev.mem_cache_alloc(BF16, X.size)
     dev.cast(xf, Xd)
     Td = dev.from_numpy(lab)
-    red = OverlappedGradAllReduce() if (world > 1 and not zero) else None
-    zopt = ZeroShardedAdam(tr, ts, side) if (world > 1 and zero) else None
+    red = OverlappedGradAllReduce(comm) if (world > 1 and not zero) else None
+    zopt = ZeroShardedAdam(tr, comm) if (world > 1 and zero) else None
 
     def step():
         tr.forward(Xd)
@@ -203,15 +188,15 @@ def run_c3_dp(steps=20, warmup=5, zero=False):
             tr.backward(Xd, on_layer_grads=zopt.start)
             zopt.finish()
             return
-        tr.backward(Xd, on_layer_grads=(lambda l: red.start(tr.layer_grads(l), side)) if red else None)
+        tr.backward(Xd, on_layer_grads=(lambda l: red.start(tr.layer_grads(l))) if red else None)
         if red:
-            red.finish(ts)
+            red.finish()
         tr.update()
 
     def barrier():
         dev.sync()
         if world > 1:
-            dist.barrier()
+            comm.barrier()
         torch.cuda.synchronize()
 
     for _ in range(warmup):
@@ -225,27 +210,40 @@ def run_c3_dp(steps=20, warmup=5, zero=False):
     barrier()
     ms = e0.elapsed_time(e1)
     if world > 1:
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor([ms])
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     loss = tr.read_loss()
+    if world > 1:  # every rank holds its share of the global-batch loss
+        t = torch.tensor([loss])
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        loss = float(t.item())
+    row = None
     if rank == 0:
         us = ms * 1e3 / steps
-        how = ("per-layer NCCL reduce-scatter overlapped with backward, Adam sharded over the ranks, all-gather of the bf16 weights" if zopt
-               else "per-layer NCCL all-reduce overlapped with backward")
-        print(json.dumps({"config": "c3 data-parallel, bf16 + fp32 master, Adam, " + how,
-                          "n_gpus": world, "global_batch": B * world, "us_per_step": us, "samples_per_s": B * world / us * 1e6,
-                          "TFLOPs_per_gpu": 293011456.0 * B / us * 1e-6, "allreduce_bytes_per_step": 4 * tr.n_params,
-                          "loss": loss, "scaling": "weak"}), flush=True)
-    if world > 1:
+        how = ("per-layer reduce-scatter (zg_reduce_scatter) overlapped with backward, Adam sharded over the ranks, all-gather of the bf16 weights"
+               if zopt else "per-layer all-reduce (zg_allreduce) overlapped with backward")
+        row = {"config": "c3 data-parallel, bf16 + fp32 master, Adam, " + how,
+               "n_gpus": world, "global_batch": B * world, "us_per_step": us, "samples_per_s": B * world / us * 1e6,
+               "TFLOPs_per_gpu": 293011456.0 * B / us * 1e-6, "allreduce_bytes_per_step": 4 * tr.n_params,
+               "loss": loss, "scaling": "weak"}
+        if not quiet:
+            print(json.dumps(row), flush=True)
+    if zopt:
+        zopt.free()
+    tr.free()
+    for s_ in (xf, Xd, Td):
+        dev.mem_cache_free(s_)
+    if own and world > 1:
+        comm.close()
         dist.barrier()
         dist.destroy_process_group()
+    return row
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="c1,c3,c4,c5")
-    ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--reps", type=int, default=200, help="graph replays per timing")
     ap.add_argument("--dp", action="store_true", help="config c3 data-parallel under torchrun (one process per GPU)")
     ap.add_argument("--zero", action="store_true", help="with --dp: shard the optimizer over the ranks (reduce-scatter / all-gather)")
@@ -253,5 +251,5 @@ if __name__ == "__main__":
     if a.dp:
         run_c3_dp(zero=a.zero)
         raise SystemExit(0)
-    for r in run(a.configs.split(","), cpu=not a.no_cpu, reps=a.reps):
+    for r in run(a.configs.split(","), reps=a.reps):
         print(json.dumps(r), flush=True)

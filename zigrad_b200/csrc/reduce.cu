@@ -498,7 +498,11 @@ void unbroadcast_impl(cudaStream_t s, const T* x, const len_t* x_shape, size_t x
   std::vector<len_t> xs(x_shape, x_shape + xnd), ys(y_shape, y_shape + ynd);
   while (!xs.empty() && xs.front() == 1) xs.erase(xs.begin());
   while (!ys.empty() && ys.front() == 1) ys.erase(ys.begin());
-  while (!ys.empty() && ys.back() == 1) ys.pop_back();
+  // Trailing ones of y are dropped only together with a trailing one of x.  (The host code drops them
+  // unconditionally, host_device.zig:729-731; for x [4,5,6] -> y [5,1] it then folds 20 rows of 6
+  // columns into the 5-element y, one element past its end.  Here such a y dimension is reduced
+  // like any interior one.)
+  while (!ys.empty() && ys.back() == 1 && !xs.empty() && xs.back() == 1) { ys.pop_back(); xs.pop_back(); }
   size_t ones = 0;
   for (len_t v : ys) ones += (v == 1);
   const bool leading = xs.size() > ys.size();

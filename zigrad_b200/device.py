@@ -190,7 +190,7 @@ class CudaDevice:
 
     # --------------------------------------------------------------- memory
     def mem_cache_alloc(self, dtype: int, n: int) -> DeviceSlice:
-        size = n * (8 if dtype == USIZE else _ITEMSIZE[dtype])
+        size = n * DeviceSlice(0, 0, dtype).itemsize
         blk = self.L.zg_cache_alloc(self.cache, max(size, 1), self.stream)
         if not blk.ptr:
             abi.check()
@@ -210,7 +210,7 @@ class CudaDevice:
     def mem_alloc(self, dtype: int, n: int) -> DeviceSlice:
         if n == 0:
             return DeviceSlice(0, 0, dtype)
-        size = n * (8 if dtype == USIZE else _ITEMSIZE[dtype])
+        size = n * DeviceSlice(0, 0, dtype).itemsize
         p = self.L.mem_alloc(size, self.stream)
         if not p:
             abi.check()

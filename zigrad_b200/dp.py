@@ -3,9 +3,13 @@ contiguous row blocks, ONE all-reduce of the flat gradient buffer between
 backward and the optimizer kernel.
 
 The reference has no distributed code (its roadmap lists "Distributed comms"
-as future work, ``docs/roadmap.norg:74-76``); this module is new.  Plumbing is
-``torch.distributed``: NCCL over NVLink on GPUs, gloo for the CPU tests of the
-host logic.  Parameters and optimizer state are replicated; every rank divides
+as future work, ``docs/roadmap.norg:74-76``); this module is new.  On GPUs the
+data plane is the library's own C ABI -- ``zg_allreduce`` / ``zg_reduce_scatter``
+/ ``zg_all_gather`` (NCCL over NVLink, bound by the library at run time) and the
+peer-memory kernel ``zg_allreduce_oneshot`` -- so a host in any language drives
+the same calls; ``torch.distributed`` is used only as the HOST channel that
+carries the 128-byte rendezvous id (and, with gloo, for the CPU tests of the
+host logic).  Parameters and optimizer state are replicated; every rank divides
 its loss and logits gradient by the GLOBAL batch so that the summed gradients
 equal the single-device gradients, and clipping/updates run after the
 all-reduce, exactly as on one device.
@@ -27,76 +31,137 @@ def shard_rows(global_batch: int, world: int, rank: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
-class _CudaView:
-    """Exposes raw device memory to torch through __cuda_array_interface__."""
+class NcclComm:
+    """One communicator per process (= per GPU) through the C ABI.
 
-    def __init__(self, ptr: int, n: int, typestr: str):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
+    `exchange(id_bytes_or_None) -> id_bytes` is the host channel: rank 0 passes the
+    128-byte id it created, the others pass None, everybody gets rank 0's bytes
+    back.  `from_torch_distributed` builds that channel from an initialised
+    process group (any backend)."""
+
+    def __init__(self, dev, rank: int, world: int, exchange):
+        import ctypes as C
+        from . import abi
+        self.dev, self.rank, self.world = dev, int(rank), int(world)
+        L = dev.L
+        if not L.zg_nccl_load(_bundled_nccl()):
+            abi.check()
+            raise RuntimeError("no NCCL library found")
+        dev.make_current()
+        ident = None
+        if self.rank == 0:
+            buf = (C.c_ubyte * 128)()
+            L.zg_nccl_unique_id(buf)
+            abi.check()
+            ident = bytes(buf)
+        ident = exchange(ident)
+        self.comm = L.zg_comm_init_rank((C.c_ubyte * 128).from_buffer_copy(ident), self.rank, self.world)
+        abi.check()
+        self._one = dev.from_numpy(np.zeros(1, np.float32))
+        self._streams = []
+
+    @classmethod
+    def from_torch_distributed(cls, dev, group=None):
+        import torch.distributed as dist
+
+        def exchange(ident):
+            box = [ident]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            return box[0]
+        return cls(dev, dist.get_rank(group), dist.get_world_size(group), exchange)
+
+    # collectives: asynchronous on `stream` (default: the device's stream), in place
+    def allreduce(self, s, stream=None) -> None:
+        self.dev.L.zg_allreduce(self.comm, s.ptr, s.len, s.dtype, stream or self.dev.stream)
+
+    def reduce_scatter(self, send, recv, stream=None) -> None:
+        self.dev.L.zg_reduce_scatter(self.comm, send.ptr, recv.ptr, recv.len, recv.dtype, stream or self.dev.stream)
+
+    def all_gather(self, send, recv, stream=None) -> None:
+        self.dev.L.zg_all_gather(self.comm, send.ptr, recv.ptr, send.len, send.dtype, stream or self.dev.stream)
+
+    def new_stream(self):
+        """A stream for collectives that should overlap the compute streams."""
+        st = self.dev.L.init_stream()
+        self._streams.append(st)
+        return st
+
+    def barrier(self) -> None:
+        """Host barrier: a one-element all-reduce, then a stream synchronise."""
+        self.allreduce(self._one)
+        self.dev.sync()
+
+    def close(self) -> None:
+        if self.comm is not None:
+            self.dev.sync()
+            for st in self._streams:
+                self.dev.L.stream_synchronize(st)
+                self.dev.L.deinit_stream(st)
+            self._streams = []
+            self.dev.mem_cache_free(self._one)
+            self.dev.L.zg_comm_destroy(self.comm)
+            self.comm = None
+
+
+def _bundled_nccl():
+    """Path of the NCCL that ships with the Python environment (the newest one
+    around), or None to let the library search the loader path."""
+    try:
+        import importlib.util
+        import os
+        spec = importlib.util.find_spec("nvidia.nccl")
+        for base in (spec.submodule_search_locations if spec else []):
+            cand = os.path.join(base, "lib", "libnccl.so.2")
+            if os.path.exists(cand):
+                return cand.encode()
+    except Exception:
+        pass
+    return None
 
 
 class GradAllReduce:
-    """Sum-all-reduce of a gradient buffer over a torch.distributed group."""
+    """Sum-all-reduce of a gradient buffer: `host` over a torch.distributed group
+    (gloo; CPU tests of the host logic), `device` over an NcclComm."""
 
-    def __init__(self, group=None):
-        import torch.distributed as dist
-        self.dist = dist
-        self.group = group
-        self.world = dist.get_world_size(group)
-        self._views = {}
+    def __init__(self, group=None, comm: "NcclComm" = None):
+        self.group, self.comm = group, comm
 
     def host(self, grads: np.ndarray) -> np.ndarray:
         """In-place sum over ranks of a host array (gloo path)."""
         import torch
+        import torch.distributed as dist
         t = torch.from_numpy(grads)
-        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return grads
 
-    def device(self, grads, torch_stream) -> None:
-        """In-place sum over ranks of a DeviceSlice, enqueued on `torch_stream`
-        (the stream the CudaDevice was created on), so it is ordered after
-        the backward kernels and before the optimizer kernel."""
-        import torch
-        key = (grads.ptr, grads.len)
-        t = self._views.get(key)
-        if t is None:
-            t = torch.as_tensor(_CudaView(grads.ptr, grads.len, "<f4"), device=torch_stream.device)
-            self._views[key] = t
-        with torch.cuda.stream(torch_stream):
-            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+    def device(self, grads, stream=None) -> None:
+        """In-place sum over ranks of a DeviceSlice, enqueued on the device's
+        stream: ordered after the backward kernels and before the optimizer."""
+        self.comm.allreduce(grads, stream)
+
+    __call__ = device
 
 
 class OverlappedGradAllReduce:
     """Per-layer all-reduce that overlaps the backward pass.
 
-    `start(slice, stream)` enqueues an asynchronous sum-all-reduce of one slice
-    of the gradient buffer, ordered after the work already on `stream` (the
-    device's side stream, where the layer's weight gradient was just issued);
-    the collective runs on the communication library's own stream, so neither
-    the side stream nor the main stream waits for it.  `finish(main_stream)`
-    makes the main stream wait for every started reduction -- call it before
-    the optimizer kernel."""
+    `start(slice)` enqueues a sum-all-reduce of one slice of the gradient buffer
+    on a communication stream of its own, ordered after the work already on the
+    device's CURRENT stream (the side stream, where the layer's weight gradient
+    was just issued), so neither the side stream nor the main stream waits for
+    it.  `finish()` makes the device's current (main) stream wait for every
+    started reduction -- call it before the optimizer kernel."""
 
-    def __init__(self, group=None):
-        import torch.distributed as dist
-        self.dist, self.group = dist, group
-        self._views, self._pending = {}, []
+    def __init__(self, comm: NcclComm):
+        self.comm, self.dev = comm, comm.dev
+        self.stream = comm.new_stream()
 
-    def start(self, grads, torch_stream) -> None:
-        import torch
-        key = (grads.ptr, grads.len)
-        t = self._views.get(key)
-        if t is None:
-            t = torch.as_tensor(_CudaView(grads.ptr, grads.len, "<f4"), device=torch_stream.device)
-            self._views[key] = t
-        with torch.cuda.stream(torch_stream):
-            self._pending.append(self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True))
+    def start(self, grads) -> None:
+        self.dev.L.zg_stream_wait(self.stream, self.dev.stream)
+        self.comm.allreduce(grads, self.stream)
 
-    def finish(self, torch_stream) -> None:
-        import torch
-        with torch.cuda.stream(torch_stream):
-            for w in self._pending:
-                w.wait()
-        self._pending = []
+    def finish(self) -> None:
+        self.dev.L.zg_stream_wait(self.dev.stream, self.stream)
 
 
 class PeerAllReduce:
@@ -104,14 +169,14 @@ class PeerAllReduce:
     peer memory (zg_allreduce_oneshot): for latency-bound buffers (up to a few
     MB) on the GPUs of one box.  A plain kernel launch on the device stream, so
     the whole data-parallel step -- backward, reduction, update -- can be
-    captured into one CUDA graph.  The host-side exchange of the IPC handles
-    goes through torch.distributed (any backend)."""
+    captured into one CUDA graph.  The IPC handles of the comm regions travel
+    over the communicator (zg_comm_peer_regions)."""
 
-    def __init__(self, dev, n_elems: int, group=None):
+    def __init__(self, dev, n_elems: int, comm: NcclComm):
         import ctypes as C
-        import torch.distributed as dist
-        self.dev, self.dist, self.group = dev, dist, group
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        from . import abi
+        self.dev, self.comm = dev, comm
+        self.rank, self.world = comm.rank, comm.world
         if self.world > 8:
             raise ValueError("PeerAllReduce supports up to 8 ranks")
         self.cap = (int(n_elems) + 3) // 4 * 4
@@ -120,25 +185,14 @@ class PeerAllReduce:
         self.region = L.zg_comm_alloc(self.cap, self.world)
         if not self.region:
             raise MemoryError("comm region")
-        handle = (C.c_ubyte * 64)()
-        L.zg_ipc_export(self.region, handle)
-        from . import abi
-        abi.check()
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle), group=group)
-        self._opened = []
         ptrs = (C.c_void_p * self.world)()
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                ptrs[r] = self.region
-            else:
-                buf = (C.c_ubyte * 64).from_buffer_copy(h)
-                p = L.zg_ipc_open(buf)
-                abi.check()
-                self._opened.append(p)
-                ptrs[r] = p
+        rc = L.zg_comm_peer_regions(comm.comm, self.region, ptrs, dev.stream)
+        abi.check()
+        if rc != 0:
+            raise RuntimeError("exchange of the comm regions failed")
         self.ptrs = ptrs
-        dist.barrier(group=group)  # every region is cleared and mapped before the first launch
+        self._opened = [ptrs[r] for r in range(self.world) if r != self.rank]
+        comm.barrier()  # every region is cleared and mapped before the first launch
 
     def __call__(self, grads) -> None:
         self.dev.L.zg_allreduce_oneshot(self.dev.stream, grads.ptr, grads.len, self.rank, self.world, self.ptrs, self.cap)
@@ -155,7 +209,7 @@ class PeerAllReduce:
 
     def close(self) -> None:
         self.dev.sync()
-        self.dist.barrier(group=self.group)  # nobody still reads a region that is about to go away
+        self.comm.barrier()  # nobody still reads a region that is about to go away
         for p in self._opened:
             self.dev.L.zg_ipc_close(p)
         self._opened = []
@@ -184,18 +238,13 @@ class ZeroShardedAdam:
     those buffers is unused); forward and backward read the bf16 copy.
     Layer slices must divide by the world size (true for 4096-wide layers at 8)."""
 
-    def __init__(self, trainer, main_stream, side_stream, group=None):
-        import torch
-        import torch.distributed as dist
+    def __init__(self, trainer, comm: NcclComm):
         if not trainer.bf16 or trainer.opt != "adam":
             raise ValueError("ZeroShardedAdam drives an MlpTrainer in bf16 mode with Adam")
-        self.tr, self.dist, self.group, self.torch = trainer, dist, group, torch
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.main, self.side = main_stream, side_stream
+        self.tr, self.comm = trainer, comm
+        self.rank, self.world = comm.rank, comm.world
+        self.stream = comm.new_stream()
         tr, W = trainer, self.world
-        dev = torch.device("cuda", torch.cuda.current_device())
-        self.g32 = torch.as_tensor(_CudaView(tr.grads.ptr, tr.grads.len, "<f4"), device=dev)
-        self.w16 = torch.as_tensor(_CudaView(tr.params_bf16.ptr, tr.params_bf16.len, "<i2"), device=dev).view(torch.bfloat16)
         self.layers, self.owned = [], []
         for l in range(tr.L):
             (woff, wn), (boff, bn) = tr.segments[2 * l], tr.segments[2 * l + 1]
@@ -210,39 +259,28 @@ class ZeroShardedAdam:
             b0 = max(lo, boff)
             self.owned.append((b0, max(0, hi - b0)))
         self.sumsq = tr.dev.mem_cache_alloc(0, len(self.owned))
-        self.sumsq_t = torch.as_tensor(_CudaView(self.sumsq.ptr, self.sumsq.len, "<f4"), device=dev)
-        self._pending = []
 
     def start(self, l: int) -> None:
+        """Call on the side stream right after layer l's weight gradient was issued."""
+        tr, d = self.tr, self.tr.dev
         off, n, c = self.layers[l]
-        full = self.g32[off:off + n]
-        mine = self.g32[off + self.rank * c: off + (self.rank + 1) * c]
-        with self.torch.cuda.stream(self.side):
-            self._pending.append(self.dist.reduce_scatter_tensor(mine, full, op=self.dist.ReduceOp.SUM, group=self.group, async_op=True))
+        d.L.zg_stream_wait(self.stream, d.stream)
+        self.comm.reduce_scatter(tr.grads.view(off, n), tr.grads.view(off + self.rank * c, c), self.stream)
 
     def finish(self) -> None:
         from . import opspec
         tr, d = self.tr, self.tr.dev
-        with self.torch.cuda.stream(self.main):
-            for w in self._pending:
-                w.wait()
-        self._pending = []
+        d.L.zg_stream_wait(d.stream, self.stream)
         clip = tr.clip
         if clip:
             d.segment_sumsq(tr.grads, self.owned, self.sumsq)
-            with self.torch.cuda.stream(self.main):
-                self.dist.all_reduce(self.sumsq_t, op=self.dist.ReduceOp.SUM, group=self.group)
+            self.comm.allreduce(self.sumsq)
             d.dispatch(opspec.sqrt_fwd(self.sumsq, self.sumsq))
         d.dispatch(opspec.adam(tr.params, tr.grads, tr.m, tr.v, self.owned, tr.t + 1, tr.lr, tr.beta1, tr.beta2, tr.eps,
                                "given" if clip else False, tr.max_norm, tr.delta, self.sumsq, tr.params_bf16, tr.t_dev))
         tr.t += len(self.owned)
-        works = []
-        with self.torch.cuda.stream(self.main):
-            for off, n, c in self.layers:
-                works.append(self.dist.all_gather_into_tensor(self.w16[off:off + n], self.w16[off + self.rank * c: off + (self.rank + 1) * c],
-                                                              group=self.group, async_op=True))
-            for w in works:
-                w.wait()
+        for off, n, c in self.layers:
+            self.comm.all_gather(tr.params_bf16.view(off + self.rank * c, c), tr.params_bf16.view(off, n))
 
     def free(self) -> None:
         self.tr.dev.mem_cache_free(self.sumsq)

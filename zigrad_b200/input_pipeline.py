@@ -32,15 +32,31 @@ from . import abi
 from .device import CudaDevice, DeviceSlice
 
 _NP = {abi.SINGLE: np.float32, abi.DOUBLE: np.float64, abi.BF16: np.uint16, 100: np.uint64}
+_ALIGN = 256  # tensors of a packed batch start on this boundary (keeps 128-bit and TMA alignment)
 
 
 class BatchStager:
-    def __init__(self, dev: CudaDevice, tensors: Sequence[Tuple[int, int]], depth: int = 2):
-        """tensors: (element count, dtype id) per input tensor of a batch."""
-        self.dev, self.depth = dev, int(depth)
+    def __init__(self, dev: CudaDevice, tensors: Sequence[Tuple[int, int]], depth: int = 2, packed: bool = False):
+        """tensors: (element count, dtype id) per input tensor of a batch.
+        packed: the tensors of a batch live back to back in ONE device block per
+        slot and ONE page-locked host buffer per batch (`pack`), so a batch
+        travels as a single copy (one DMA set-up instead of one per tensor)."""
+        self.dev, self.depth, self.packed = dev, int(depth), bool(packed)
         self.copy_stream = dev.L.init_stream()
         self.spec = [(int(n), int(dt)) for n, dt in tensors]
-        self.slots: List[List[DeviceSlice]] = [[dev.mem_cache_alloc(dt, n) for n, dt in self.spec] for _ in range(self.depth)]
+        self.slots: List[List[DeviceSlice]] = []
+        if packed:
+            self._offsets, off = [], 0
+            for n, dt in self.spec:
+                self._offsets.append(off)
+                off += (n * np.dtype(_NP[dt]).itemsize + _ALIGN - 1) // _ALIGN * _ALIGN
+            self._packed_bytes = off
+            self._blocks = [dev.mem_cache_alloc(abi.SINGLE, off // 4) for _ in range(self.depth)]
+            for blk in self._blocks:
+                self.slots.append([DeviceSlice(blk.ptr + o, n, dt, 0) for o, (n, dt) in zip(self._offsets, self.spec)])
+        else:
+            self._blocks = []
+            self.slots = [[dev.mem_cache_alloc(dt, n) for n, dt in self.spec] for _ in range(self.depth)]
         self._pinned = []
         self._put = self._got = 0
         self._copied = [dev.L.zg_event_create() for _ in range(self.depth)]
@@ -67,16 +83,36 @@ class BatchStager:
         out[...] = a
         return out
 
+    def pack(self, arrays: Sequence[np.ndarray]) -> np.ndarray:
+        """One page-locked byte buffer holding the tensors of a batch at the
+        offsets of a packed slot (packed stagers only); pass it to put()."""
+        if not self.packed:
+            raise RuntimeError("pack() needs a stager created with packed=True")
+        buf = self.pinned((self._packed_bytes,), np.uint8)
+        buf[:] = 0
+        for a, o, (n, dt) in zip(arrays, self._offsets, self.spec):
+            a = np.ascontiguousarray(a, dtype=_NP[dt]).ravel()
+            if a.size != n:
+                raise ValueError("batch tensor of %d elements, slot holds %d" % (a.size, n))
+            buf[o:o + a.nbytes] = a.view(np.uint8)
+        return buf
+
     # ----------------------------------------------------------------- stream
-    def put(self, arrays: Sequence[np.ndarray]) -> None:
+    def put(self, arrays) -> None:
         """Enqueue the host-to-device copy of one batch into the next free slot
-        (asynchronous when the arrays are page-locked)."""
+        (asynchronous when the arrays are page-locked).  `arrays`: the batch's
+        tensors, or for a packed stager the buffer pack() returned."""
         if self._put - self._got >= self.depth:
             raise RuntimeError("all %d slots hold batches that were not released yet" % self.depth)
         k = self._put % self.depth
         slot = self.slots[k]
         if self._was_consumed[k]:  # the step that last read this slot must be done before it is overwritten
             self.dev.L.zg_stream_wait_event(self.copy_stream, self._consumed[k])
+        if self.packed:
+            if arrays.nbytes != self._packed_bytes:
+                raise ValueError("packed batch of %d bytes, slot holds %d" % (arrays.nbytes, self._packed_bytes))
+            self.dev.L.memcpy_HtoD(self._blocks[k].ptr, arrays.ctypes.data, arrays.nbytes, self.copy_stream)
+            arrays = ()
         for a, d in zip(arrays, slot):
             if a.nbytes != d.nbytes:
                 raise ValueError("batch tensor of %d bytes, slot holds %d" % (a.nbytes, d.nbytes))
@@ -105,15 +141,18 @@ class BatchStager:
         self._got += 1
 
     def bytes_per_batch(self) -> int:
-        return sum(d.nbytes for d in self.slots[0])
+        """Bytes one put() copies."""
+        return self._packed_bytes if self.packed else sum(d.nbytes for d in self.slots[0])
 
     def close(self) -> None:
         self.dev.sync()
         self.dev.L.stream_synchronize(self.copy_stream)
-        for slot in self.slots:
+        for blk in self._blocks:
+            self.dev.mem_cache_free(blk)
+        for slot in ([] if self.packed else self.slots):
             for d in slot:
                 self.dev.mem_cache_free(d)
-        self.slots = []
+        self.slots, self._blocks = [], []
         for p in self._pinned:
             self.dev.L.zg_host_free_pinned(p)
         self._pinned = []
