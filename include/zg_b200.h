@@ -217,6 +217,37 @@ EXTERN_C void zg_softmax_ce_fwd_bwd(dtype id, StreamWrapper stream, const void* 
 EXTERN_C void zg_smooth_l1_fwd_bwd(dtype id, StreamWrapper stream, const void* pred, const void* target,
                                    len_t n, double beta, void* loss_out, void* grad);
 
+/* The middle of an MLP training step as ONE launch, for the layer widths of the
+ * MNIST model (h1 = 128 -> h2 = 64 -> C <= 16 classes; examples/mnist/src/model.zig:34-55).
+ * Given act0 [rows, h1] (the post-ReLU output of the preceding layer) it does
+ * what the reference issues as six device calls and two host loops:
+ *   act1 = relu(act0 W1^T + b1)                       bmm_acc, add, relu_fwd (model.zig:100-112, src/nn/nn.zig:39-62)
+ *   logits = act1 W2^T + b2                           bmm_acc, add
+ *   loss_out[0], dlogits = softmax cross-entropy      src/nn/loss.zig:130-215 (as zg_softmax_ce_fwd_bwd, accumulate = 0)
+ *   db2 += colsum(dlogits)                            InplaceAddBwd (src/ndtensor.zig:783-788)
+ *   dact1 = (dlogits W2) where act1 > 0; db1 += ..    BmmAccBwd dX (src/ndtensor.zig:1107-1109) + relu_inplace_bwd
+ *   dact0 = (dact1 W1) where act0 > 0;  db0 += ..     (src/device/host_device.zig:543-547)
+ * W1 [h2, h1], b1 [h2], W2 [C, h2], b2 [C]; logits / dlogits have row stride
+ * ld_out >= C (only C columns are written); act1 / dact1 [rows, h2], dact0
+ * [rows, h1], all fp32 and contiguous.  db2 / db1 / db0 are ADDED to with fp32
+ * atomics (zero them first: in a step they are slices of the zero-filled
+ * gradient buffer).  The weight gradients are NOT formed here: dW2 = dlogits^T
+ * act1, dW1 = dact1^T act0 and the preceding layer's dW = dact0^T x are three
+ * independent zg_bmm calls afterwards.  3xTF32 tensor-core products, fp32
+ * everywhere else.
+ * weights_ready != 0: the caller vouches that W1, b1, W2 and b2 are not written
+ * by the kernel launched immediately before this call on the stream, so they
+ * are fetched while that kernel still runs (true inside a training step, where
+ * that kernel is the preceding layer's forward GEMM).
+ * zg_mlp_tail_supported: 1 when the widths (and the math mode) have a kernel;
+ * otherwise the caller issues the separate ops. */
+EXTERN_C int zg_mlp_tail_supported(dtype id, len_t h1, len_t h2, len_t C);
+EXTERN_C void zg_mlp_tail_fwd_bwd(dtype id, StreamWrapper stream, len_t rows, len_t h1, len_t h2, len_t C,
+                                  const void* act0, const void* W1, const void* b1, const void* W2, const void* b2,
+                                  const void* labels, int label_kind, len_t ld_out, double loss_div,
+                                  void* act1, void* logits, void* loss_out, void* dlogits, void* dact1, void* dact0,
+                                  void* db2, void* db1, void* db0, int weights_ready);
+
 /* -------------------------------------------------------------- optimizers
  * One launch over a whole parameter set.  The tensors of a model live back to
  * back (attach order) in one parameter buffer and one gradient buffer; seg

@@ -146,9 +146,12 @@ def test_wide_mlp_full_size_shard_against_the_oracle(gpu):
     # element feeds.  Such flips must be rare and confined to activations near zero; gradients are
     # compared on the rows no flip has touched (the large majority), where they must agree to the
     # stated tolerance.
+    # Tolerances as in the miniature test, except the logits: they sit behind three bf16-rounded layers
+    # of 4096 terms each, and an activation that rounds to a neighbouring bf16 value on one side moves
+    # 4096 products of the next layer: 4e-3 of the largest logit instead of 2e-3.
     touched = np.zeros(B, bool)
     for l in range(L - 1, -1, -1):
-        tol = 2e-3 if l + 1 == L else 1e-2
+        tol = 4e-3 if l + 1 == L else 1e-2
         got = tr.act_numpy(l)
         assert rel_err(got, act[l]) <= tol, ("act", l, rel_err(got, act[l]))
         gd, want_d = tr.act_numpy(l, grad=True), dact[l]

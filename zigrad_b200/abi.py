@@ -199,6 +199,9 @@ SIGNATURES = {
     "zg_broadcast": (None, [dtype_t, S, vp, len_t, vp, len_t, dbl, dbl]),
     "zg_softmax_ce_fwd_bwd": (None, [dtype_t, S, vp, vp, i32, len_t, len_t, len_t, dbl, vp, vp, i32, vp, vp]),
     "zg_smooth_l1_fwd_bwd": (None, [dtype_t, S, vp, vp, len_t, dbl, vp, vp]),
+    "zg_mlp_tail_supported": (i32, [dtype_t, len_t, len_t, len_t]),
+    "zg_mlp_tail_fwd_bwd": (None, [dtype_t, S, len_t, len_t, len_t, len_t, vp, vp, vp, vp, vp, vp, i32, len_t, dbl,
+                                   vp, vp, vp, vp, vp, vp, vp, vp, vp, i32]),
     "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp, i32]),
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp]),
     "zg_segment_sumsq": (None, [dtype_t, S, vp, C.POINTER(Segment), len_t, vp]),

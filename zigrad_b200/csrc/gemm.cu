@@ -11,6 +11,7 @@
 #include "gemm_tc.cuh"
 #include "gemm_tc_persistent.cuh"
 #include "gemm_skinny.cuh"
+#include "mlp_tail.cuh"
 #include "../../include/blas_conflux.h"
 
 namespace zg {
@@ -304,6 +305,26 @@ static bool try_skinny(dtype id, dtype c_id, cudaStream_t s, const void* A, cons
   p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k;
   p.lda = (uint32_t)lda; p.ldb = (uint32_t)ldb; p.ldc = (uint32_t)ldc;
   p.alpha = (float)alpha; p.beta = (float)beta; p.epilogue = epilogue; p.tb = tb ? 1 : 0;
+  static const bool tn_shadow = [] { const char* e = getenv("ZG_TN_SHADOW"); return e && e[0] == '1'; }();
+  if (tn_shadow && ta && !tb && m <= 64 && n <= 128 && n % 4 == 0 && k >= 1024 && epilogue == ZG_EPI_NONE && !colsum && ldb % 4 == 0 && ldc == n &&
+      host_aligned16(B) && host_aligned16(C)) {
+    // small-output weight gradient (A [k, m], B [k, n], C contiguous): FFMA kernel without shared memory that shares
+    // SMs with a large GEMM running beside it; its partial products are folded by the row-fold kernel
+    const uint32_t tiles_n = (uint32_t)(n / 4), tiles_m = (uint32_t)((m + 3) / 4), tiles = tiles_m * tiles_n;
+    uint32_t groups = skinny::kTnThreads / tiles;
+    if (groups < 1) return false;
+    if (groups > 8) groups = 8;
+    const size_t ctas = std::min<size_t>((k + 8 * groups - 1) / (8 * groups), (size_t)sm_count());
+    const uint32_t rows_per_cta = (uint32_t)((k + ctas - 1) / ctas);
+    const unsigned grid = (unsigned)((k + rows_per_cta - 1) / rows_per_cta);
+    const size_t parts = (size_t)grid * groups;
+    float* partial = static_cast<float*>(workspace(s, sizeof(float) * parts * m * n, nullptr, 1));
+    if (!partial) return true;  // error recorded
+    if (!launch_pdl(skinny::skinny_tn_kernel, dim3(grid), dim3(skinny::kTnThreads), 0, s, p, partial, rows_per_cta, tiles_n, tiles, groups)) return true;
+    // C = alpha * (sum over the parts) + beta * C: the parts are the rows of a [parts, m * n] matrix
+    zg_fold_rows(SINGLE, StreamWrapper{s}, partial, C, parts, m * n, alpha, beta);
+    return true;
+  }
   if (ta) {
     // weight gradient of a narrow layer: A [k, m], B [k, n]
     if (tb || m > 16 || n < 16 || n > 256 || 256 % n != 0 || k < 1024 || epilogue != ZG_EPI_NONE || colsum) return false;
@@ -479,6 +500,68 @@ void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const voi
   else set_error(kUnsupported, "bmm: unsupported dtype combination %d -> %d", (int)id, (int)c_id);
 }
 
+// ---- fused middle of the MLP step (mlp_tail.cuh)
+template <int CP>
+static bool launch_tail_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tk, const CUtensorMap& tn, const CUtensorMap& t1,
+                             const CUtensorMap& td1, const CUtensorMap& td0, const tail::Params& p, unsigned grid) {
+  auto kern = tail::mlp_tail_kernel<CP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tail::kSmemBytes))) return false;
+    attr_set = true;
+  }
+  return launch_pdl(kern, dim3(grid), dim3(tail::kThreads), (size_t)tail::kSmemBytes, s, ta, tk, tn, t1, td1, td0, p);
+}
+
+void mlp_tail_launch(cudaStream_t s, len_t rows, len_t h1, len_t h2, len_t C, const void* act0, const void* W1, const void* b1, const void* W2,
+                     const void* b2, const void* labels, int label_kind, len_t ld_out, double loss_div, void* act1, void* logits, void* loss_out,
+                     void* dlogits, void* dact1, void* dact0, void* db2, void* db1, void* db0, int weights_ready) {
+  if (rows == 0) return;
+  if (h1 != (len_t)tail::kH1 || h2 != (len_t)tail::kH2 || C == 0 || C > (len_t)tail::kCMax) {
+    set_error(kUnsupported, "zg_mlp_tail_fwd_bwd: widths %lu -> %lu -> %lu (built for %d -> %d -> at most %d)", h1, h2, C, tail::kH1, tail::kH2, tail::kCMax);
+    return;
+  }
+  if (rows > 0x7fffffffu || ld_out < C || ld_out > 0xffffffffu) { set_error(kBadArgument, "zg_mlp_tail_fwd_bwd: rows %lu, ld_out %lu", rows, ld_out); return; }
+  if (label_kind != ZG_LABEL_ONEHOT && label_kind != ZG_LABEL_INDEX) { set_error(kBadArgument, "zg_mlp_tail_fwd_bwd: unknown label kind %d", label_kind); return; }
+  const void* ptrs[] = {act0, W1, b1, W2, b2, labels, act1, logits, loss_out, dlogits, dact1, dact0, db2, db1, db0};
+  for (const void* q : ptrs)
+    if (!q) { set_error(kBadArgument, "zg_mlp_tail_fwd_bwd: NULL argument"); return; }
+  if (!host_aligned16(act0) || !host_aligned16(W1) || !host_aligned16(act1) || !host_aligned16(dact1) || !host_aligned16(dact0)) {
+    set_error(kBadArgument, "zg_mlp_tail_fwd_bwd: act0, W1, act1, dact1 and dact0 must be 16-byte aligned");
+    return;
+  }
+  if (ld_out > (len_t)tail::kCMax) { set_error(kBadArgument, "zg_mlp_tail_fwd_bwd: ld_out %lu above %d", ld_out, tail::kCMax); return; }
+  CUtensorMap tmA, tmK, tmN, tm1, tmD1, tmD0;
+  // outputs leave through TMA stores of [128 rows x 32 floats] slabs (rows past the end are clipped)
+  if (!make_tmap(&tm1, false, act1, tail::kH2, rows, 1, tail::kH2, 32, tail::kRows, false)) return;
+  if (!make_tmap(&tmD1, false, dact1, tail::kH2, rows, 1, tail::kH2, 32, tail::kRows, false)) return;
+  if (!make_tmap(&tmD0, false, dact0, tail::kH1, rows, 1, tail::kH1, 32, tail::kRows, false)) return;
+  if (!make_tmap(&tmA, false, act0, tail::kH1, rows, 1, tail::kH1, 32, tail::kRows, false)) return;
+  if (!make_tmap(&tmK, false, W1, tail::kH1, tail::kH2, 1, tail::kH1, 32, tail::kH2, false)) return;   // B of act0 W1^T: [n = 64 rows][k contiguous]
+  if (!make_tmap(&tmN, false, W1, tail::kH1, tail::kH2, 1, tail::kH1, 32, 32, true)) return;           // B of dact1 W1: [k = 64 rows][n contiguous]
+  const unsigned grid = (unsigned)((rows + tail::kRows - 1) / tail::kRows);
+  unsigned* counters = nullptr;
+  float* partial = static_cast<float*>(workspace(s, sizeof(float) * grid, &counters));
+  if (!partial) return;
+  tail::Params p;
+  memset(&p, 0, sizeof(p));
+  p.W2 = static_cast<const float*>(W2); p.b1 = static_cast<const float*>(b1); p.b2 = static_cast<const float*>(b2);
+  p.labels = labels; p.label_index = label_kind == ZG_LABEL_INDEX ? 1 : 0;
+  p.logits = static_cast<float*>(logits); p.dlogits = static_cast<float*>(dlogits);
+  p.db2 = static_cast<float*>(db2); p.db1 = static_cast<float*>(db1); p.db0 = static_cast<float*>(db0);
+  p.loss_out = static_cast<float*>(loss_out); p.loss_partial = partial; p.counter = counters;
+  p.rows = (uint32_t)rows; p.C = (uint32_t)C; p.ld_out = (uint32_t)ld_out;
+  p.divisor = (float)loss_div; p.inv_divisor = 1.f / p.divisor;
+  int e = 0;
+  p.exact_inv = (std::frexp(p.divisor, &e) == 0.5f && std::isnormal(p.inv_divisor)) ? 1 : 0;
+  p.early_weights = weights_ready ? 1 : 0;
+  p.error_flag = tc_error_flag();
+  if (C <= 4) launch_tail_inst<4>(s, tmA, tmK, tmN, tm1, tmD1, tmD0, p, grid);
+  else if (C <= 8) launch_tail_inst<8>(s, tmA, tmK, tmN, tm1, tmD1, tmD0, p, grid);
+  else if (C <= 12) launch_tail_inst<12>(s, tmA, tmK, tmN, tm1, tmD1, tmD0, p, grid);
+  else launch_tail_inst<16>(s, tmA, tmK, tmN, tm1, tmD1, tmD0, p, grid);
+}
+
 int* kernel_timeout_flag() { return tc_error_flag(); }
 
 // Reads (and clears) the device flag that a kernel raises when one of its bounded waits runs out.
@@ -527,6 +610,23 @@ __global__ void __launch_bounds__(256) ger_kernel(const T* __restrict__ a, const
 }  // namespace zg
 
 using namespace zg;
+
+namespace zg {
+void mlp_tail_launch(cudaStream_t s, len_t rows, len_t h1, len_t h2, len_t C, const void* act0, const void* W1, const void* b1, const void* W2,
+                     const void* b2, const void* labels, int label_kind, len_t ld_out, double loss_div, void* act1, void* logits, void* loss_out,
+                     void* dlogits, void* dact1, void* dact0, void* db2, void* db1, void* db0, int weights_ready);
+}
+extern "C" int zg_mlp_tail_supported(dtype id, len_t h1, len_t h2, len_t C) {
+  return (id == SINGLE && g_math_mode != ZG_MATH_FFMA && h1 == (len_t)tail::kH1 && h2 == (len_t)tail::kH2 && C >= 1 && C <= (len_t)tail::kCMax) ? 1 : 0;
+}
+extern "C" void zg_mlp_tail_fwd_bwd(dtype id, StreamWrapper stream, len_t rows, len_t h1, len_t h2, len_t C, const void* act0, const void* W1,
+                                    const void* b1, const void* W2, const void* b2, const void* labels, int label_kind, len_t ld_out,
+                                    double loss_div, void* act1, void* logits, void* loss_out, void* dlogits, void* dact1, void* dact0,
+                                    void* db2, void* db1, void* db0, int weights_ready) {
+  if (id != SINGLE) { set_error(kUnsupported, "zg_mlp_tail_fwd_bwd: only SINGLE is implemented"); return; }
+  mlp_tail_launch(as_stream(stream), rows, h1, h2, C, act0, W1, b1, W2, b2, labels, label_kind, ld_out, loss_div, act1, logits, loss_out,
+                  dlogits, dact1, dact0, db2, db1, db0, weights_ready);
+}
 
 extern "C" void zg_set_math_mode(int mode) {
   if (mode < ZG_MATH_FP32X3 || mode > ZG_MATH_FFMA) { set_error(kBadArgument, "zg_set_math_mode: unknown mode %d", mode); return; }

@@ -133,6 +133,8 @@ class CudaDevice:
         self.cache = self.L.zg_cache_create(self.device_number, cache_max_bytes)
         self.capture = ExecutionGraph(self)
         self._side = None  # second stream for branches of independent work, created on first use
+        self._sides = {}   # further side streams by index (branch(k), k >= 1)
+        self._forked = []  # side streams used since the last join()
         abi.check()
 
     # ------------------------------------------------------------ lifecycle
@@ -148,6 +150,9 @@ class CudaDevice:
         if self._side is not None:
             self.L.deinit_stream(self._side)
             self._side = None
+        for st in self._sides.values():
+            self.L.deinit_stream(st)
+        self._sides = {}
         if self._own_stream:
             self.L.deinit_stream(self.stream)
         self.L = None
@@ -166,27 +171,40 @@ class CudaDevice:
         self.L.zg_set_device(self.device_number)
 
     @contextlib.contextmanager
-    def branch(self):
-        """Ops issued inside the block go to the device's side stream, ordered
-        after everything issued so far on the main stream; they may overlap what
-        the main stream runs next.  `join()` makes the main stream wait for them
-        (required before the results are used and before a capture is saved)."""
+    def branch(self, k: int = 0):
+        """Ops issued inside the block go to the device's k-th side stream,
+        ordered after everything issued so far on the main stream; they may
+        overlap what the main stream (and the other side streams) run next.
+        `join()` makes the main stream wait for them (required before the
+        results are used and before a capture is saved)."""
         if os.environ.get("ZG_NO_BRANCH") == "1":  # everything in issue order on the main stream
             yield
             return
-        if self._side is None:
-            self._side = self.L.init_stream()
+        if k == 0:
+            if self._side is None:
+                self._side = self.L.init_stream()
+            side = self._side
+        else:
+            if k not in self._sides:
+                self._sides[k] = self.L.init_stream()
+            side = self._sides[k]
         main = self.stream
-        self.L.zg_stream_wait(self._side, main)
-        self.stream = self._side
+        self.L.zg_stream_wait(side, main)
+        if all(side.ptr != f.ptr for f in self._forked):
+            self._forked.append(side)
+        self.stream = side
         try:
             yield
         finally:
             self.stream = main
 
     def join(self):
-        if self._side is not None:
-            self.L.zg_stream_wait(self.stream, self._side)
+        """The main stream waits for every side stream used since the last join
+        (only those: a wait on a stream that is not part of a running capture
+        would break the capture)."""
+        for st in self._forked:
+            self.L.zg_stream_wait(self.stream, st)
+        self._forked = []
 
     # --------------------------------------------------------------- memory
     def mem_cache_alloc(self, dtype: int, n: int) -> DeviceSlice:
@@ -511,6 +529,15 @@ class CudaDevice:
                                      p.loss.ptr, p.grad.ptr if p.grad is not None else None, int(p.accumulate),
                                      p.probs.ptr if p.probs is not None else None,
                                      p.bias_grad.ptr if p.bias_grad is not None else None)
+
+    def mlp_tail_supported(self, dtype: int, h1: int, h2: int, classes: int) -> bool:
+        return bool(self.L.zg_mlp_tail_supported(dtype, h1, h2, classes))
+
+    def mlp_tail(self, p):
+        kind = abi.LABEL_INDEX if p.labels.dtype == USIZE else abi.LABEL_ONEHOT
+        self.L.zg_mlp_tail_fwd_bwd(p.act0.dtype, self.stream, p.rows, p.h1, p.h2, p.classes, p.act0.ptr, p.W1.ptr, p.b1.ptr, p.W2.ptr,
+                                   p.b2.ptr, p.labels.ptr, kind, p.ld_out, float(p.loss_div), p.act1.ptr, p.logits.ptr, p.loss.ptr,
+                                   p.dlogits.ptr, p.dact1.ptr, p.dact0.ptr, p.db2.ptr, p.db1.ptr, p.db0.ptr, int(p.weights_ready))
 
     def smooth_l1(self, p):
         self.L.zg_smooth_l1_fwd_bwd(p.pred.dtype, self.stream, p.pred.ptr, p.target.ptr, p.pred.len, p.beta, p.loss.ptr,

@@ -18,7 +18,11 @@ Two op sequences produce the same tensors:
 * ``fused=True``  -- one zero fill of the flat gradient buffer, ``linear`` ops
   with bias / ReLU / ReLU-mask epilogues, bias gradients taken from the loss
   kernel (last layer) and from the dX GEMM epilogues (hidden layers): 10 kernel
-  launches + 1 memset for the three-layer model.
+  launches + 1 memset for the three-layer model.  When the last two layers have
+  the widths the ``mlp_tail`` op is built for (128 -> 64 -> at most 16 classes:
+  the MNIST model), ``step()`` replaces everything between the first layer's
+  forward GEMM and the weight gradients by that one op: 6 launches per step
+  (forward GEMM, tail, three independent weight-gradient GEMMs, update).
 
 Parameters, gradients and optimizer state live in flat buffers in attach
 order (W0, b0, W1, b1, ...), which is what a data-parallel step all-reduces
@@ -52,7 +56,8 @@ class MlpTrainer:
     def __init__(self, dev: CudaDevice, dims: Sequence[int], batch: int, weights, biases, opt: str = "sgd",
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
                  max_norm: float = 10.0, delta: float = 1e-6, fused: bool = True, loss_div: Optional[int] = None,
-                 index_labels: bool = False, bf16: bool = False, pad_logits: bool = True, zero_grads_in_update: bool = False):
+                 index_labels: bool = False, bf16: bool = False, pad_logits: bool = True, zero_grads_in_update: bool = False,
+                 tail: Optional[bool] = None):
         self.dev, self.dims, self.B, self.L = dev, [int(d) for d in dims], int(batch), len(dims) - 1
         self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
         self.clip, self.max_norm, self.delta = clip, max_norm, delta
@@ -66,6 +71,12 @@ class MlpTrainer:
         if zero_grads_in_update and not (fused and opt == "sgd"):
             raise ValueError("zero_grads_in_update needs the fused ops and SGD")
         self.zero_grads_in_update, self._grads_clear = bool(zero_grads_in_update), False
+        # the fused middle of the step (opspec.mlp_tail): on by default wherever the library has a kernel for the widths
+        can_tail = (fused and not bf16 and self.L >= 3 and
+                    dev.mlp_tail_supported(SINGLE, self.dims[-3], self.dims[-2], self.dims[-1]))
+        if tail and not can_tail:
+            raise ValueError("no mlp_tail kernel for the widths %s" % self.dims[-3:])
+        self.tail = can_tail if tail is None else bool(tail)
         # flat parameter layout, attach order
         self.segments, off = [], 0
         for l in range(self.L):
@@ -222,12 +233,50 @@ class MlpTrainer:
         off = self.segments[2 * l][0]
         return self.grads.view(off, self.segments[2 * l][1] + self.segments[2 * l + 1][1])
 
+    def _forward_backward_tail(self, X: DeviceSlice, T: DeviceSlice):
+        """forward, loss and backward with the last two layers, the loss and the
+        dX chain down to dact[L-3] done by one mlp_tail op."""
+        d, B, L = self.dev, self.B, self.L
+        if not self._grads_clear:
+            d.mem_fill(self.grads, 0.0)
+        self._grads_clear = False
+        inp = X
+        for l in range(L - 2):  # the layers in front of the tail
+            K, N = self.dims[l], self.dims[l + 1]
+            d.dispatch(opspec.linear(inp, self.W[l], self.act[l], B, N, K, False, True, K, K, self.ld[l], 1.0, 0.0, "bias_relu", self.b[l]))
+            inp = self.act[l]
+        h1, h2, C = self.dims[L - 2], self.dims[L - 1], self.dims[L]
+        d.dispatch(opspec.mlp_tail(self.act[L - 3], self.W[L - 2], self.b[L - 2], self.W[L - 1], self.b[L - 1], T, B, h1, h2, C,
+                                   self.ld_out, self.loss_div, self.act[L - 2], self.act[L - 1], self.loss, self.dact[L - 1],
+                                   self.dact[L - 2], self.dact[L - 3], self.db[L - 1], self.db[L - 2], self.db[L - 3],
+                                   weights_ready=L - 2 >= 1))
+        # the weight gradients of the two tail layers are independent of each other and of everything that follows:
+        # one side stream each
+        with d.branch(0):
+            d.dispatch(opspec.linear(self.dact[L - 2], self.act[L - 3], self.dW[L - 2], h2, h1, B, True, False, h2, h1, h1, 1.0, 1.0))
+        with d.branch(1):
+            d.dispatch(opspec.linear(self.dact[L - 1], self.act[L - 2], self.dW[L - 1], C, h2, B, True, False, self.ld_out, h2, h2, 1.0, 1.0))
+        for l in range(L - 3, -1, -1):
+            K, N = self.dims[l], self.dims[l + 1]
+            a_in = X if l == 0 else self.act[l - 1]
+            if l == 0:  # nothing else is left on the main stream: the largest weight gradient runs there
+                d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0))
+            else:
+                with d.branch(0):
+                    d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0))
+                d.dispatch(opspec.linear(self.dact[l], self.W[l], self.dact[l - 1], B, K, N, False, False, N, K, K, 1.0, 0.0,
+                                         "relu_mask", None, self.act[l - 1], colsum=self.db[l - 1]))
+        d.join()
+
     def step(self, X: DeviceSlice, T: DeviceSlice, allreduce: Optional[Callable[[DeviceSlice], None]] = None):
         """forward + loss + backward [+ gradient all-reduce] + update, all
         asynchronous on the device stream.  The loss stays in ``self.loss``."""
-        self.forward(X)
-        self.loss_and_grad(T)
-        self.backward(X)
+        if self.tail:
+            self._forward_backward_tail(X, T)
+        else:
+            self.forward(X)
+            self.loss_and_grad(T)
+            self.backward(X)
         if allreduce is not None:
             fused = getattr(allreduce, "reduce_and_sgd", None)
             if fused is not None and self.opt == "sgd" and not self.clip:

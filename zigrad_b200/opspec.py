@@ -8,7 +8,7 @@ dtype) instead of Zig slices.
 
 The last section holds the ops this backend ADDS to the interface (the
 reference runs them as host loops): ``softmax_ce``, ``smooth_l1``, ``sgd``,
-``adam``, ``linear_fwd``.
+``adam``, ``linear``, ``mlp_tail``.
 """
 from __future__ import annotations
 
@@ -460,6 +460,37 @@ class softmax_ce:
     probs: Optional[Any] = None
     ld: int = 0                      # row stride of logits / grad / probs (0 = classes)
     bias_grad: Optional[Any] = None  # [classes]: column sums of the gradient written
+
+
+@_op("mlp_tail")
+class mlp_tail:
+    """The last two Linear layers of an MLP with their loss and the backward pass
+    down to the gradient of the layer before them, as one device op
+    (zg_mlp_tail_fwd_bwd): act1 = relu(act0 W1^T + b1), logits = act1 W2^T + b2,
+    softmax cross-entropy forward/backward, dact1, dact0 and the three bias
+    gradients (added into db2 / db1 / db0)."""
+    act0: Any       # [rows, h1]
+    W1: Any         # [h2, h1]
+    b1: Any
+    W2: Any         # [classes, h2]
+    b2: Any
+    labels: Any     # one-hot fp32 [rows, classes] or u64 [rows]
+    rows: int
+    h1: int
+    h2: int
+    classes: int
+    ld_out: int     # row stride of logits / dlogits
+    loss_div: float
+    act1: Any
+    logits: Any
+    loss: Any
+    dlogits: Any
+    dact1: Any
+    dact0: Any
+    db2: Any
+    db1: Any
+    db0: Any
+    weights_ready: bool = False
 
 
 @_op("smooth_l1")
