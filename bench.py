@@ -246,7 +246,7 @@ class Job:
     """One configuration of the data-parallel MLP step on this rank: trainer,
     reducer, resident batches and one captured graph per resident batch."""
 
-    def __init__(self, dev, comm, rank, world, B, global_B, resident, allreduce_kind, seed_base=1000):
+    def __init__(self, dev, comm, rank, world, B, global_B, resident, allreduce_kind, seed_base=1000, steps_per_graph=1):
         from zigrad_b200.dp import GradAllReduce, PeerAllReduce
         from zigrad_b200.mlp import MlpTrainer, kaiming_uniform
         self.dev, self.comm, self.rank, self.world, self.B, self.global_B = dev, comm, rank, world, B, global_B
@@ -266,6 +266,10 @@ class Job:
         dev.sync()
         self.graphs = [self.capture(lambda X=X, T=T: self.step_eager(X, T)) for X, T in self.resident]
         self.kernels_per_step = self.graphs[0].kernel_count()
+        # one graph over a whole rotation of the resident batches (one step each, in order): a launch per
+        # rotation instead of per step; steps that do not fill a rotation use the per-batch graphs
+        self.rotation = self.capture(lambda: [self.step_eager(X, T) for X, T in self.resident]) if steps_per_graph > 1 else None
+        self.cursor = 0
 
     def step_eager(self, X, T):
         self.tr.step(X, T, self.reducer)
@@ -279,8 +283,21 @@ class Job:
     def step(self, i):
         self.graphs[i % len(self.graphs)].run()
 
+    def run(self, steps):
+        """`steps` steps, the resident batches in rotation: whole rotations as one graph launch each."""
+        R, i = len(self.graphs), 0
+        while i < steps:
+            if self.rotation is not None and self.cursor % R == 0 and steps - i >= R:
+                self.rotation.run()
+                i += R
+                self.cursor += R
+            else:
+                self.graphs[self.cursor % R].run()
+                i += 1
+                self.cursor += 1
+
     def close(self):
-        for g in self.graphs:
+        for g in self.graphs + ([self.rotation] if self.rotation is not None else []):
             g.free()
         if self.peer and self.reducer is not None:
             self.reducer.close()
@@ -316,7 +333,7 @@ def run_gpu(args, rank, local_rank, world):
     global_B = args.batch if strong else args.batch * world
     # resident batches: together larger than L2 whatever the per-rank batch is
     R = args.resident if not strong else args.resident * world
-    job = Job(dev, comm, rank, world, B, global_B, R, args.allreduce)
+    job = Job(dev, comm, rank, world, B, global_B, R, args.allreduce, steps_per_graph=R if args.graph == "rotation" else 1)
     tr = job.tr
 
     def barrier():
@@ -341,13 +358,17 @@ def run_gpu(args, rank, local_rank, world):
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def timed(step_fn, steps):
+    def timed(step_fn, steps, whole=False):
         """K steps between two events on the compute stream, a barrier and a
-        synchronise on both sides; the maximum over the ranks, in ms."""
+        synchronise on both sides; the maximum over the ranks, in ms.
+        `whole`: step_fn takes the number of steps and runs them all."""
         barrier()
         e0.record(ts)
-        for i in range(steps):
-            step_fn(i)
+        if whole:
+            step_fn(steps)
+        else:
+            for i in range(steps):
+                step_fn(i)
         e1.record(ts)
         barrier()
         return max_over_ranks(e0.elapsed_time(e1))
@@ -378,7 +399,7 @@ def run_gpu(args, rank, local_rank, world):
     if rank == 0:
         sampler.start()
     load_until(2, 4.0)
-    times = [timed(job.step, args.steps) for _ in range(REPEATS)]
+    times = [timed(job.run, args.steps, whole=True) for _ in range(REPEATS)]
     load_until(len(sampler.lines) + 3, 2.0)
     clocks = sampler.stop() if rank == 0 else None
     ms = statistics.median(times)
@@ -608,6 +629,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8192, help="rows per GPU (weak) or of the one global batch (strong)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--graph", choices=["rotation", "step"], default="rotation",
+                    help="device-timed leg: one CUDA graph per rotation of the resident batches (a launch per --resident steps) or one per step")
     ap.add_argument("--resident", type=int, default=8, help="distinct batches kept in HBM and rotated")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU legs")
     ap.add_argument("--no-configs", action="store_true", help="skip the other configurations")

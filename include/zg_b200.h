@@ -90,6 +90,12 @@ EXTERN_C int zg_get_math_mode(void);
  * in a separate pass.  Not available together with split-K (plain epilogue,
  * deep k, few tiles). */
 enum { ZG_EPI_NONE = 0, ZG_EPI_BIAS = 1, ZG_EPI_BIAS_RELU = 2, ZG_EPI_RELU_MASK = 3 };
+/* SM budget for the NEXT zg_bmm call of the calling thread (consumed by it; 0 = all SMs).
+ * GEMMs issued on parallel streams (the weight gradients of different layers) each take a
+ * share: the split-K grid is then sized for that many SMs, so that the concurrent launches
+ * fit in one wave together instead of pushing one another's CTAs into a second wave. */
+EXTERN_C void zg_bmm_sm_budget(int sms);
+EXTERN_C int zg_sm_count(void);
 EXTERN_C void zg_bmm(dtype id, dtype c_id, StreamWrapper stream,
                      const void* A, const void* B, void* C,
                      len_t nA, len_t nB, len_t nC, len_t m, len_t n, len_t k,

@@ -177,6 +177,8 @@ SIGNATURES = {
     "zg_capture_kernel_count": (len_t, [GraphWrapper]),
     "zg_set_math_mode": (None, [i32]),
     "zg_get_math_mode": (i32, []),
+    "zg_bmm_sm_budget": (None, [i32]),
+    "zg_sm_count": (i32, []),
     "zg_bmm": (None, [dtype_t, dtype_t, S, vp, vp, vp, len_t, len_t, len_t, len_t, len_t, len_t, b8, b8, len_t, len_t, len_t,
                       dbl, dbl, i32, vp, vp, vp]),
     "zg_relu_inplace_bwd": (None, [dtype_t, S, vp, vp, len_t]),

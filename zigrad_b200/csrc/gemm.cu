@@ -222,7 +222,7 @@ static bool make_tmap(CUtensorMap* map, bool bf16, const void* base, uint64_t in
 }
 
 template <int BN, bool AK, bool BK_, int MODE, bool ATM = false>
-static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tb, const tc::Params& p, dim3 grid) {
+static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tcm, const tc::Params& p, dim3 grid) {
   using SL = tc::SmemLayout<BN, MODE, ATM>;
   auto kern = tc::gemm_tc_kernel<BN, AK, BK_, MODE, ATM>;
   static bool attr_set = false;
@@ -230,7 +230,7 @@ static bool launch_tc_inst(cudaStream_t s, const CUtensorMap& ta, const CUtensor
     if (!ZG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::kTotal))) return false;
     attr_set = true;
   }
-  return launch_pdl(kern, grid, dim3(tc::tc_threads(MODE)), (size_t)SL::kTotal, s, ta, tb, p);
+  return launch_pdl(kern, grid, dim3(tc::tc_threads(MODE)), (size_t)SL::kTotal, s, ta, tb, tcm, p);
 }
 
 // FP32X3: the hi/lo parts of A live in tensor memory (ZG_X3_TMEM_A=0 keeps them in shared memory)
@@ -241,21 +241,21 @@ static bool x3_tmem_a() {
 
 template <int MODE>
 static bool launch_tc_mode(cudaStream_t s, int bn, bool a_kmajor, bool b_kmajor, const CUtensorMap& ta, const CUtensorMap& tb,
-                           const tc::Params& p, dim3 grid) {
+                           const CUtensorMap& tcm, const tc::Params& p, dim3 grid) {
 #define ZG_TC_CASE(BNV)                                                                       \
   if (bn == BNV) {                                                                            \
     if constexpr (MODE == tc::kFP32X3) {                                                      \
       if (x3_tmem_a()) {                                                                      \
-        if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE, true>(s, ta, tb, p, grid);   \
-        if (a_kmajor) return launch_tc_inst<BNV, true, false, MODE, true>(s, ta, tb, p, grid);              \
-        if (b_kmajor) return launch_tc_inst<BNV, false, true, MODE, true>(s, ta, tb, p, grid);              \
-        return launch_tc_inst<BNV, false, false, MODE, true>(s, ta, tb, p, grid);                           \
+        if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE, true>(s, ta, tb, tcm, p, grid);   \
+        if (a_kmajor) return launch_tc_inst<BNV, true, false, MODE, true>(s, ta, tb, tcm, p, grid);              \
+        if (b_kmajor) return launch_tc_inst<BNV, false, true, MODE, true>(s, ta, tb, tcm, p, grid);              \
+        return launch_tc_inst<BNV, false, false, MODE, true>(s, ta, tb, tcm, p, grid);                           \
       }                                                                                       \
     }                                                                                         \
-    if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE>(s, ta, tb, p, grid);   \
-    if (a_kmajor && !b_kmajor) return launch_tc_inst<BNV, true, false, MODE>(s, ta, tb, p, grid); \
-    if (!a_kmajor && b_kmajor) return launch_tc_inst<BNV, false, true, MODE>(s, ta, tb, p, grid); \
-    return launch_tc_inst<BNV, false, false, MODE>(s, ta, tb, p, grid);                       \
+    if (a_kmajor && b_kmajor) return launch_tc_inst<BNV, true, true, MODE>(s, ta, tb, tcm, p, grid);   \
+    if (a_kmajor && !b_kmajor) return launch_tc_inst<BNV, true, false, MODE>(s, ta, tb, tcm, p, grid); \
+    if (!a_kmajor && b_kmajor) return launch_tc_inst<BNV, false, true, MODE>(s, ta, tb, tcm, p, grid); \
+    return launch_tc_inst<BNV, false, false, MODE>(s, ta, tb, tcm, p, grid);                       \
   }
   if constexpr (MODE != tc::kBF16) { ZG_TC_CASE(32) }
   ZG_TC_CASE(64)
@@ -363,6 +363,17 @@ static bool try_skinny(dtype id, dtype c_id, cudaStream_t s, const void* A, cons
   return false;
 }
 
+// SM budget of the zg_bmm call in progress (zg_bmm_sm_budget): GEMMs that run side by side on parallel
+// streams size their split-K grids for a share of the SMs, so that together they fit in one wave
+// (a CTA of these kernels takes a whole SM's shared memory; an oversubscribed launch runs its
+// surplus CTAs in a second wave after the first has drained).
+static thread_local int g_next_sm_budget = 0, g_sm_budget = 0;
+static size_t sm_share() {
+  const size_t all = (size_t)sm_count();
+  return (g_sm_budget > 0 && (size_t)g_sm_budget < all) ? (size_t)g_sm_budget : all;
+}
+extern "C" void zg_bmm_sm_budget(int sms) { g_next_sm_budget = sms > 0 ? sms : 0; }
+
 // Returns true when the tensor-core path took the problem.
 static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC,
                             len_t m, len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta,
@@ -400,8 +411,8 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   // (with a fused epilogue or column sums the last CTA of a tile applies them to the finished sums)
   // and that costs a second pass over the tile, so it is kept for problems with very few tiles)
   const bool deferred = epilogue != ZG_EPI_NONE || colsum;
-  const bool can_split = !persistent && c_id == SINGLE && k >= 512 && (!deferred || tiles * 4 <= (size_t)sm_count());
-  if (!can_split && bn == 128 && tiles * 2 <= (size_t)sm_count() && n > 64) {
+  const bool can_split = !persistent && c_id == SINGLE && k >= 512 && (!deferred || tiles * 4 <= sm_share());
+  if (!can_split && bn == 128 && tiles * 2 <= sm_share() && n > 64) {
     bn = 64;
     tiles = ((m + 127) / 128) * ((n + bn - 1) / bn) * nC;
   }
@@ -418,8 +429,8 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
       if (eff > best + 0.03) { best = eff; splits = sp; }
     }
   }
-  if (can_split && tiles * 2 <= (size_t)sm_count()) {
-    size_t want = (size_t)sm_count() / tiles;
+  if (can_split && tiles * 2 <= sm_share()) {
+    size_t want = sm_share() / tiles;
     size_t maxs = k / (4 * (size_t)bk);  // at least four k-slabs per split
     splits = (unsigned)(want < maxs ? want : maxs);
     if (splits < 1) splits = 1;
@@ -476,15 +487,27 @@ static bool try_tensor_core(dtype id, dtype c_id, cudaStream_t s, const void* A,
   }
   dim3 grid((unsigned)((n + bn - 1) / bn), (unsigned)((m + 127) / 128), (unsigned)(nC * splits));
   if (grid.y > 65535 || grid.z > 65535) return false;
-  if (mode == tc::kBF16) launch_tc_mode<tc::kBF16>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
-  else if (mode == tc::kTF32) launch_tc_mode<tc::kTF32>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
-  else launch_tc_mode<tc::kFP32X3>(s, bn, a_kmajor, b_kmajor, tmA, tmB, p, grid);
+  // Output through the C tensor map where the epilogue needs nothing from global memory but the bias
+  // (ZG_GEMM_TMA_EPILOGUE=0 keeps the register path)
+  CUtensorMap tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  static const bool tma_epi_on = [] { const char* e = getenv("ZG_GEMM_TMA_EPILOGUE"); return !(e && e[0] == '0'); }();
+  if (tma_epi_on && c_id == SINGLE && p.vec_ok && !p.tile_tickets && !p.colsum && nC <= 0x7fffffffu &&
+      (splits > 1 ? epilogue == ZG_EPI_NONE : (beta == 0.0 && epilogue != ZG_EPI_RELU_MASK))) {
+    if (!make_tmap(&tmC, false, C, n, m, nC, ldc, 32, 32, false)) return true;
+    p.tma_epilogue = splits > 1 ? 2 : 1;
+  }
+  if (mode == tc::kBF16) launch_tc_mode<tc::kBF16>(s, bn, a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid);
+  else if (mode == tc::kTF32) launch_tc_mode<tc::kTF32>(s, bn, a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid);
+  else launch_tc_mode<tc::kFP32X3>(s, bn, a_kmajor, b_kmajor, tmA, tmB, tmC, p, grid);
   return true;
 }
 
 void bmm_dispatch(dtype id, dtype c_id, cudaStream_t s, const void* A, const void* B, void* C, len_t nA, len_t nB, len_t nC, len_t m,
                   len_t n, len_t k, bool ta, bool tb, len_t lda, len_t ldb, len_t ldc, double alpha, double beta, int epilogue,
                   const void* bias, const void* mask, void* colsum) {
+  g_sm_budget = g_next_sm_budget;
+  g_next_sm_budget = 0;
   if (m == 0 || n == 0 || nC == 0) return;
   if (nA == 0 || nB == 0) { set_error(kBadArgument, "bmm: empty operand batch"); return; }
   if (epilogue < ZG_EPI_NONE || epilogue > ZG_EPI_RELU_MASK) { set_error(kBadArgument, "bmm: unknown epilogue %d", epilogue); return; }

@@ -78,6 +78,13 @@ struct Params {
   int epilogue;
   int vec_ok;           // C (and mask, bias) rows allow 16-byte accesses at every 32-column boundary
   int* error_flag;      // set to 1 when a bounded wait ran out
+  // Epilogue through the C tensor map (fp32 C with 16-byte-aligned rows): each epilogue warp stages its
+  // 32 rows of a 32-column chunk in shared memory (128-byte swizzle) and one lane hands the box to the
+  // TMA unit -- 1: plain store (no split-K, beta == 0, epilogue NONE / BIAS / BIAS_RELU, no column
+  // sums), 2: reduce-add into C (split-K partial products; C pre-scaled by beta).  Whole 128-byte
+  // lines leave the SM instead of 16-byte pieces of 32 different lines per instruction, and boxes that
+  // hang over the edge of C are clipped by the unit.  0: register path below.
+  int tma_epilogue;
   // Split-K with a fused epilogue: the partial products are added into C (which
   // the launcher scaled by beta first) with the epilogue switched off; every CTA
   // then takes a ticket of its tile, and the one that draws the last applies
@@ -261,6 +268,22 @@ __host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn_major, bo
   return (1u << 4) | ((bf16 ? 1u : 2u) << 7) | ((bf16 ? 1u : 2u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
+
+// shared -> global through a tensor map, tracked by the issuing thread's bulk async-group
+__device__ __forceinline__ void tma_store_box(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_box(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the bulk operations of this thread have READ their shared-memory source (their global writes are
+// complete when the grid completes, which is what a dependent kernel waits for)
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 template <int MODE>
 struct ModeTraits {
@@ -460,7 +483,8 @@ struct SmemLayout {
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int MODE, bool ATM = false>
 __global__ void __launch_bounds__(tc_threads(MODE), 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+               const Params p) {
   static_assert(!ATM || MODE == kFP32X3, "A through tensor memory: FP32X3 only");
   using MT = ModeTraits<MODE>;
   using SL = SmemLayout<BN, MODE, ATM>;
@@ -501,6 +525,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (p.tma_epilogue) prefetch_tmap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(&tmem_base_slot, kTmemCols);
@@ -781,7 +806,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t row = tile_m * kBM + q * 32 + lane;
     const uint64_t c_off = (uint64_t)batch * p.c_batch_stride + (uint64_t)row * p.ldc;
     const bool row_ok = row < p.m;
-    if (KT == 0 || have_acc) {
+    if (p.tma_epilogue && (KT == 0 || have_acc)) {
+      // The stage ring is idle by now (every fetched slab was consumed by MMAs that have completed):
+      // its first bytes stage the output, 4 KB per warp and chunk, 1024-byte aligned for the swizzle.
+      uint8_t* stg = stage_base + q * (BN / 32) * 4096;
+      const bool has_bias = p.epilogue == ZG_EPI_BIAS || p.epilogue == ZG_EPI_BIAS_RELU;
+      int chunks = 0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const uint32_t col0 = tile_n * BN + c * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        if (KT > 0) {
+          tmem_ld32(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(r[j]);
+        if (has_bias) {
+          if (col0 + 32 <= p.n) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+              v[4 * j] += bv.x; v[4 * j + 1] += bv.y; v[4 * j + 2] += bv.z; v[4 * j + 3] += bv.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+          }
+          if (p.epilogue == ZG_EPI_BIAS_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : 0.f;
+          }
+        }
+        uint8_t* rowp = stg + c * 4096 + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(rowp + ((j ^ (lane & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        ++chunks;
+      }
+      fence_async_smem();  // generic-proxy writes -> visible to the TMA unit
+      __syncwarp();
+      if (lane == 0 && tile_m * kBM + q * 32 < p.m) {
+        for (int c = 0; c < chunks; ++c) {
+          const int x = (int)(tile_n * BN) + c * 32, y = (int)(tile_m * kBM) + q * 32;
+          if (p.tma_epilogue == 2) tma_reduce_add_box(&tmC, stg + c * 4096, x, y, (int)batch);
+          else tma_store_box(&tmC, stg + c * 4096, x, y, (int)batch);
+        }
+        bulk_commit_group();
+        bulk_wait_group_read();
+      }
+      __syncwarp();
+    } else if (KT == 0 || have_acc) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const uint32_t col0 = tile_n * BN + c * 32;

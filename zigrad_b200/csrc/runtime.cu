@@ -246,6 +246,7 @@ extern "C" int zg_device_available(void) {
   (void)cudaGetLastError();
   return (e == cudaSuccess && n > 0) ? 1 : 0;
 }
+extern "C" int zg_sm_count(void) { return sm_count(); }
 extern "C" void zg_set_device(unsigned device_number) { ZG_CUDA(cudaSetDevice((int)device_number)); }
 
 // ======================================================================

@@ -371,6 +371,8 @@ class CudaDevice:
     def linear(self, p):
         epi = {"none": abi.EPI_NONE, "bias": abi.EPI_BIAS, "bias_relu": abi.EPI_BIAS_RELU, "relu_mask": abi.EPI_RELU_MASK}[p.epilogue]
         nA, nB, nC = p.n_batch
+        if p.sm_budget:
+            self.L.zg_bmm_sm_budget(p.sm_budget)
         self.L.zg_bmm(p.A.dtype, p.C.dtype, self.stream, p.A.ptr, p.B.ptr, p.C.ptr, nA, nB, nC, p.m, p.n, p.k,
                       p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, epi,
                       p.bias.ptr if p.bias is not None else None, p.mask_src.ptr if p.mask_src is not None else None,
@@ -529,6 +531,9 @@ class CudaDevice:
                                      p.loss.ptr, p.grad.ptr if p.grad is not None else None, int(p.accumulate),
                                      p.probs.ptr if p.probs is not None else None,
                                      p.bias_grad.ptr if p.bias_grad is not None else None)
+
+    def sm_count(self) -> int:
+        return int(self.L.zg_sm_count())
 
     def mlp_tail_supported(self, dtype: int, h1: int, h2: int, classes: int) -> bool:
         return bool(self.L.zg_mlp_tail_supported(dtype, h1, h2, classes))

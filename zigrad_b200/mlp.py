@@ -57,7 +57,7 @@ class MlpTrainer:
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
                  max_norm: float = 10.0, delta: float = 1e-6, fused: bool = True, loss_div: Optional[int] = None,
                  index_labels: bool = False, bf16: bool = False, pad_logits: bool = True, zero_grads_in_update: bool = False,
-                 tail: Optional[bool] = None):
+                 tail: Optional[bool] = None, fuse_update: bool = True):
         self.dev, self.dims, self.B, self.L = dev, [int(d) for d in dims], int(batch), len(dims) - 1
         self.opt, self.lr, self.beta1, self.beta2, self.eps = opt, lr, beta1, beta2, eps
         self.clip, self.max_norm, self.delta = clip, max_norm, delta
@@ -77,6 +77,9 @@ class MlpTrainer:
         if tail and not can_tail:
             raise ValueError("no mlp_tail kernel for the widths %s" % self.dims[-3:])
         self.tail = can_tail if tail is None else bool(tail)
+        self._dw_shares = None
+        # the tail path applies plain SGD from inside the backward pass (see _forward_backward_tail) unless told not to
+        self.fuse_update = bool(fuse_update) and self.tail
         # flat parameter layout, attach order
         self.segments, off = [], 0
         for l in range(self.L):
@@ -233,13 +236,28 @@ class MlpTrainer:
         off = self.segments[2 * l][0]
         return self.grads.view(off, self.segments[2 * l][1] + self.segments[2 * l + 1][1])
 
-    def _forward_backward_tail(self, X: DeviceSlice, T: DeviceSlice):
+    def _forward_backward_tail(self, X: DeviceSlice, T: DeviceSlice, fuse_update: bool = False):
         """forward, loss and backward with the last two layers, the loss and the
-        dX chain down to dact[L-3] done by one mlp_tail op."""
+        dX chain down to dact[L-3] done by one mlp_tail op.
+
+        ``fuse_update`` (plain SGD, no all-reduce in between): the update rides on the
+        backward pass instead of following it.  Each weight gradient of layer 0 and of the
+        two tail layers is followed, on its own stream, by the SGD update of that one
+        tensor (nothing reads those weights any more once their gradient runs), and the
+        biases, whose gradients the tail op has finished, go with the last layer's: no
+        update kernel waits for the join of all streams.  The weights of the layers in
+        between are still read by the dX products and are updated after the join."""
         d, B, L = self.dev, self.B, self.L
         if not self._grads_clear:
             d.mem_fill(self.grads, 0.0)
         self._grads_clear = False
+
+        def update(segs):
+            if fuse_update and segs:
+                d.dispatch(opspec.sgd(self.params, self.grads, segs, self.lr, False, self.max_norm, self.delta, self.norms,
+                                      self.zero_grads_in_update))
+
+        weight, bias = (lambda l: self.segments[2 * l]), (lambda l: self.segments[2 * l + 1])
         inp = X
         for l in range(L - 2):  # the layers in front of the tail
             K, N = self.dims[l], self.dims[l + 1]
@@ -251,28 +269,54 @@ class MlpTrainer:
                                    self.dact[L - 2], self.dact[L - 3], self.db[L - 1], self.db[L - 2], self.db[L - 3],
                                    weights_ready=L - 2 >= 1))
         # the weight gradients of the two tail layers are independent of each other and of everything that follows:
-        # one side stream each
+        # one side stream each.
+        # With one layer in front of the tail, its weight gradient (main stream) runs beside the two of the tail:
+        # the SMs are shared out by output tiles so that the three split-K grids fit in one wave together.
+        share = self._dw_sm_shares() if L == 3 else {}
         with d.branch(0):
-            d.dispatch(opspec.linear(self.dact[L - 2], self.act[L - 3], self.dW[L - 2], h2, h1, B, True, False, h2, h1, h1, 1.0, 1.0))
+            d.dispatch(opspec.linear(self.dact[L - 2], self.act[L - 3], self.dW[L - 2], h2, h1, B, True, False, h2, h1, h1, 1.0, 1.0,
+                                     sm_budget=share.get(L - 2, 0)))
+            update([weight(L - 2)])
         with d.branch(1):
             d.dispatch(opspec.linear(self.dact[L - 1], self.act[L - 2], self.dW[L - 1], C, h2, B, True, False, self.ld_out, h2, h2, 1.0, 1.0))
+            # the tail op wrote the bias gradients of its two layers and of the layer in front of it
+            update([weight(L - 1)] + [bias(l) for l in (L - 3, L - 2, L - 1)])
         for l in range(L - 3, -1, -1):
             K, N = self.dims[l], self.dims[l + 1]
             a_in = X if l == 0 else self.act[l - 1]
             if l == 0:  # nothing else is left on the main stream: the largest weight gradient runs there
-                d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0))
+                d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0, sm_budget=share.get(0, 0)))
+                update([weight(0)])
             else:
                 with d.branch(0):
                     d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0))
                 d.dispatch(opspec.linear(self.dact[l], self.W[l], self.dact[l - 1], B, K, N, False, False, N, K, K, 1.0, 0.0,
                                          "relu_mask", None, self.act[l - 1], colsum=self.db[l - 1]))
         d.join()
+        if fuse_update:
+            # what did not ride on the backward pass: the weights the dX products read and the biases in front of them
+            update([weight(l) for l in range(1, L - 2)] + [bias(l) for l in range(L - 3)])
+            self._grads_clear = self.zero_grads_in_update
+
+    def _dw_sm_shares(self) -> dict:
+        """SMs for each tensor-core weight-gradient GEMM of a three-layer step (layers 0 and 1; the last
+        layer's output is a few rows and goes to a small FFMA kernel that fits beside the others):
+        in proportion to the 128x128 output tiles, the first layer's share a multiple of its tile count."""
+        if self._dw_shares is None:
+            sms = self.dev.sm_count()
+            tiles = [-(-self.dims[l + 1] // 128) * -(-self.dims[l] // 128) for l in (0, 1)]
+            first = sms * tiles[0] // sum(tiles) // tiles[0] * tiles[0]
+            self._dw_shares = {0: first, 1: sms - first} if 0 < first < sms else {}
+        return self._dw_shares
 
     def step(self, X: DeviceSlice, T: DeviceSlice, allreduce: Optional[Callable[[DeviceSlice], None]] = None):
         """forward + loss + backward [+ gradient all-reduce] + update, all
         asynchronous on the device stream.  The loss stays in ``self.loss``."""
         if self.tail:
-            self._forward_backward_tail(X, T)
+            fuse = self.fuse_update and allreduce is None and self.opt == "sgd" and not self.clip
+            self._forward_backward_tail(X, T, fuse_update=fuse)
+            if fuse:
+                return
         else:
             self.forward(X)
             self.loss_and_grad(T)

@@ -580,3 +580,4 @@ class linear:
     mask_src: Optional[Any] = None
     n_batch: tuple = field(default=(1, 1, 1))
     colsum: Optional[Any] = None  # fp32 [n]: column sums of the stored C are added here (a bias gradient)
+    sm_budget: int = 0  # > 0: size the split-K grid for this many SMs (GEMMs that run side by side on parallel streams share them)
