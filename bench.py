@@ -13,8 +13,10 @@ Prints ONE JSON line (rank 0).
 
 * `value`   whole-job samples/s with the input batches already in HBM: the
             median of REPEATS timings of K steps each (`value_spread` holds
-            min/max).  The step is captured once per resident batch into a
-            CUDA graph; the resident batches rotate and together exceed L2.
+            min/max).  The resident batches rotate and together exceed L2;
+            one CUDA graph holds a whole rotation (one step per batch, a
+            launch per `--resident` steps; `--graph step` launches a graph
+            per step instead).
 * `e2e`     the same step fed from pinned HOST memory: the H2D copy of every
             batch and the D2H read of every loss are inside the timed region
             (double-buffered on a copy stream, one packed copy per batch).
@@ -599,7 +601,8 @@ def run_gpu(args, rank, local_rank, world):
                                    + ("one batch of %d sharded over the GPUs" % global_B if strong else "batch %d per GPU" % B),
                        "global_batch": global_B, "per_gpu_batch": B, "parallelism": "dp%d" % world,
                        "l2_policy": "%d resident batches of %.1f MB rotate (%.0f MB > 126 MB L2)" % (R, B * (DIMS[0] + DIMS[-1]) * 4 / 1e6, R * B * (DIMS[0] + DIMS[-1]) * 4 / 1e6),
-                       "step_launch": "CUDA graph per resident batch" + ("" if world == 1 else (
+                       "step_launch": ("one CUDA graph per rotation of the resident batches (%d steps per launch)" % R if job.rotation is not None
+                                       else "CUDA graph per resident batch") + ("" if world == 1 else (
                            " incl. the one-kernel peer-memory (NVLink) all-reduce of the flat gradient buffer fused with the update" if job.peer else
                            " incl. the library all-reduce (zg_allreduce) of the flat gradient buffer and the update kernel"))},
             "clocks": clocks,
