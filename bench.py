@@ -559,10 +559,11 @@ def run_gpu(args, rank, local_rank, world):
     # ---- the other curve of the same job (N > 1, weak run): one batch of 8192 sharded over the ranks
     strong_row = None
     if world > 1 and not strong and args.batch % world == 0 and not args.no_strong:
-        sj = Job(dev, comm, rank, world, args.batch // world, args.batch, args.resident * world, args.allreduce, seed_base=7000)
+        sj = Job(dev, comm, rank, world, args.batch // world, args.batch, args.resident * world, args.allreduce, seed_base=7000,
+                 steps_per_graph=args.resident * world if args.graph == "rotation" else 1)
         for i in range(args.warmup):
             sj.step(i)
-        stimes = [timed(sj.step, args.steps) for _ in range(REPEATS)]
+        stimes = [timed(sj.run, args.steps, whole=True) for _ in range(REPEATS)]
         sms = statistics.median(stimes)
         strong_row = {"scaling": "strong", "global_batch": args.batch, "per_gpu_batch": args.batch // world,
                       "value": args.steps * args.batch / (sms / 1e3), "unit": "samples/s", "ms_per_step": sms / args.steps,

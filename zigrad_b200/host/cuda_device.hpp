@@ -9,6 +9,7 @@
 // turns it into a DeviceError (the Zig shim panics with the same message).
 #pragma once
 
+#include <array>
 #include <cstring>
 #include <stdexcept>
 #include <string>
@@ -95,6 +96,7 @@ class CudaDevice {
     check();
   }
   StreamWrapper stream() const { return stream_; }
+  int sm_count() const { return zg_sm_count(); }
 
   // ------------------------------------------------------------- memory
   template <typename T>
@@ -160,8 +162,17 @@ class CudaDevice {
            p.C_shape[2], p.A_shape[2], p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, ZG_EPI_NONE, nullptr, nullptr, nullptr);
   }
   template <typename T> void op(const opspec::linear<T>& p) {
+    if (p.sm_budget > 0) zg_bmm_sm_budget(p.sm_budget);
     zg_bmm(dtype_of<T>(), dtype_of<T>(), cur(), p.A.ptr, p.B.ptr, p.C.ptr, 1, 1, 1, p.m, p.n, p.k, p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc,
            p.alpha, p.beta, static_cast<int>(p.epilogue), p.bias.ptr, p.mask_src.ptr, p.colsum.ptr);
+  }
+  bool mlp_tail_supported(dtype id, std::size_t h1, std::size_t h2, std::size_t classes) const { return zg_mlp_tail_supported(id, h1, h2, classes) != 0; }
+  template <typename T> void op(const opspec::mlp_tail<T>& p) {
+    const bool idx = p.label_index.ptr != nullptr;
+    zg_mlp_tail_fwd_bwd(dtype_of<T>(), cur(), p.rows, p.h1, p.h2, p.classes, p.act0.ptr, p.W1.ptr, p.b1.ptr, p.W2.ptr, p.b2.ptr,
+                        idx ? static_cast<const void*>(p.label_index.ptr) : p.onehot.ptr, idx ? ZG_LABEL_INDEX : ZG_LABEL_ONEHOT, p.ld_out,
+                        p.loss_div, p.act1.ptr, p.logits.ptr, p.loss.ptr, p.dlogits.ptr, p.dact1.ptr, p.dact0.ptr, p.db2.ptr, p.db1.ptr,
+                        p.db0.ptr, p.weights_ready ? 1 : 0);
   }
   template <typename T> void op(const opspec::sum<T>& p) { reduce_sum(dtype_of<T>(), cublas_, p.x.ptr, p.y.ptr, p.x.len); }
   template <typename T> void op(const opspec::scale<T>& p) { ::scale(dtype_of<T>(), cublas_, p.x.ptr, p.x.len, p.alpha); }
@@ -254,6 +265,41 @@ class CudaDevice {
   CublasWrapper cublas_{nullptr};
   CacheWrapper cache_{nullptr};
   bool in_branch_ = false;
+};
+
+// Library collectives over one communicator per rank (NCCL bound at run time).  Rank 0 makes the
+// 128-byte id (Communicator::unique_id) and hands it to the other ranks over any host channel;
+// every rank then constructs its Communicator with it.
+class Communicator {
+ public:
+  static std::array<unsigned char, 128> unique_id() {
+    std::array<unsigned char, 128> id{};
+    zg_nccl_unique_id(id.data());
+    CudaDevice::check();
+    return id;
+  }
+  Communicator(const std::array<unsigned char, 128>& id, unsigned rank, unsigned world) : comm_(zg_comm_init_rank(id.data(), rank, world)) {
+    CudaDevice::check();
+  }
+  ~Communicator() { if (comm_.ptr) zg_comm_destroy(comm_); }
+  Communicator(const Communicator&) = delete;
+  Communicator& operator=(const Communicator&) = delete;
+  unsigned rank() const { return zg_comm_rank(comm_); }
+  unsigned world() const { return zg_comm_world(comm_); }
+  // buf[i] = sum over the ranks of buf[i]
+  template <typename T> void allreduce(Slice<T> buf, StreamWrapper s) { zg_allreduce(comm_, buf.ptr, buf.len, dtype_of<T>(), s); }
+  // recv[i] = sum over the ranks of send[rank * recv.len + i]
+  template <typename T> void reduce_scatter(Slice<const T> send, Slice<T> recv, StreamWrapper s) {
+    zg_reduce_scatter(comm_, send.ptr, recv.ptr, recv.len, dtype_of<T>(), s);
+  }
+  // recv[r * send.len + i] = rank r's send[i]
+  template <typename T> void all_gather(Slice<const T> send, Slice<T> recv, StreamWrapper s) {
+    zg_all_gather(comm_, send.ptr, recv.ptr, send.len, dtype_of<T>(), s);
+  }
+  CommWrapper handle() const { return comm_; }
+
+ private:
+  CommWrapper comm_{nullptr};
 };
 
 inline void ExecutionGraph::open() {

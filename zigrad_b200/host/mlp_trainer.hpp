@@ -125,10 +125,86 @@ class MlpTrainer {
     p.params = params_.raw; p.grads = grads_.raw; p.segments = segments_; p.lr = lr_;
     d_.dispatch(p);
   }
+  // True when the last two layers, the loss and their backward pass can run as the one fused op
+  bool has_tail() const { return L_ >= 3 && d_.mlp_tail_supported(SINGLE, dims_[L_ - 2], dims_[L_ - 1], dims_[L_]); }
+  // forward + loss + backward with opspec::mlp_tail in the middle (same results as forward / loss_and_grad / backward)
+  void forward_backward_tail(Slice<const float> X, Slice<const float> onehot) {
+    d_.mem_fill(grads_.raw, 0.f);
+    Slice<const float> in = X;
+    for (std::size_t l = 0; l + 2 < L_; ++l) {
+      opspec::linear<float> p;
+      p.A = in; p.B = W(l); p.C = act_[l].raw;
+      p.m = B_; p.n = dims_[l + 1]; p.k = dims_[l];
+      p.trans_a = false; p.trans_b = true;
+      p.lda = dims_[l]; p.ldb = dims_[l]; p.ldc = ld_[l];
+      p.epilogue = opspec::Epilogue::bias_relu;
+      p.bias = b(l);
+      d_.dispatch(p);
+      in = act_[l].raw;
+    }
+    {
+      opspec::mlp_tail<float> p;
+      p.act0 = act_[L_ - 3].raw; p.W1 = W(L_ - 2); p.b1 = b(L_ - 2); p.W2 = W(L_ - 1); p.b2 = b(L_ - 1);
+      p.onehot = onehot;
+      p.rows = B_; p.h1 = dims_[L_ - 2]; p.h2 = dims_[L_ - 1]; p.classes = dims_[L_];
+      p.ld_out = ld_out_; p.loss_div = (double)loss_div_;
+      p.act1 = act_[L_ - 2].raw; p.logits = act_[L_ - 1].raw; p.loss = loss_.raw;
+      p.dlogits = dact_[L_ - 1].raw; p.dact1 = dact_[L_ - 2].raw; p.dact0 = dact_[L_ - 3].raw;
+      p.db2 = db(L_ - 1); p.db1 = db(L_ - 2); p.db0 = db(L_ - 3);
+      p.weights_ready = true;  // the kernel in front is the preceding layer's forward GEMM
+      d_.dispatch(p);
+    }
+    auto weight_grad = [&](std::size_t l, int sm_budget) {
+      opspec::linear<float> p;
+      p.A = dact_[l].raw; p.B = l == 0 ? X : Slice<const float>(act_[l - 1].raw); p.C = dW(l);
+      p.m = dims_[l + 1]; p.n = dims_[l]; p.k = B_;
+      p.trans_a = true; p.trans_b = false;
+      p.lda = ld_[l]; p.ldb = dims_[l]; p.ldc = dims_[l];
+      p.beta = 1.f;
+      p.sm_budget = sm_budget;
+      d_.dispatch(p);
+    };
+    // three layers: dW0 (main stream) runs beside the two weight gradients of the tail layers (side stream),
+    // the SMs shared out by 128 x 128 output tiles
+    int first = 0, second = 0;
+    if (L_ == 3) {
+      const std::size_t t0 = ((dims_[1] + 127) / 128) * ((dims_[0] + 127) / 128), t1 = ((dims_[2] + 127) / 128) * ((dims_[1] + 127) / 128);
+      const std::size_t sms = (std::size_t)d_.sm_count();
+      const std::size_t f = sms * t0 / (t0 + t1) / t0 * t0;
+      if (f > 0 && f < sms) { first = (int)f; second = (int)(sms - f); }
+    }
+    d_.branch();
+    weight_grad(L_ - 2, second);
+    weight_grad(L_ - 1, 0);
+    d_.end_branch();
+    for (std::size_t l = L_ - 2; l-- > 0;) {
+      if (l == 0) {
+        weight_grad(0, first);
+      } else {
+        d_.branch();
+        weight_grad(l, 0);
+        d_.end_branch();
+        opspec::linear<float> p;
+        p.A = dact_[l].raw; p.B = W(l); p.C = dact_[l - 1].raw;
+        p.m = B_; p.n = dims_[l]; p.k = dims_[l + 1];
+        p.trans_a = false; p.trans_b = false;
+        p.lda = ld_[l]; p.ldb = dims_[l]; p.ldc = dims_[l];
+        p.epilogue = opspec::Epilogue::relu_mask;
+        p.mask_src = act_[l - 1].raw;
+        p.colsum = db(l - 1);
+        d_.dispatch(p);
+      }
+    }
+    d_.join();
+  }
   void step(Slice<const float> X, Slice<const float> onehot) {
-    forward(X);
-    loss_and_grad(onehot);
-    backward(X);
+    if (has_tail()) {
+      forward_backward_tail(X, onehot);
+    } else {
+      forward(X);
+      loss_and_grad(onehot);
+      backward(X);
+    }
     update();
   }
   float read_loss() {

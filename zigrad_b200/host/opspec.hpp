@@ -346,6 +346,27 @@ struct linear {
   Slice<const float> bias;      // [n]
   Slice<const T> mask_src;      // C's shape
   Slice<float> colsum;          // [n], optional: column sums of the stored values are added
+  int sm_budget = 0;            // > 0: size the split-K grid for this many SMs (GEMMs side by side on parallel streams share them)
+};
+
+// The last two Linear layers of an MLP, their softmax cross-entropy and the backward pass down to the
+// gradient of the layer in front of them, as one device op (zg_mlp_tail_fwd_bwd): the op sequence of
+// examples/mnist/src/model.zig:34-55 + src/nn/loss.zig:130-171 + the BmmAccBwd / relu backward calls of
+// src/ndtensor.zig:1092-1136 for those two layers.  The three bias gradients are ADDED into db2/db1/db0.
+template <typename T>
+struct mlp_tail {
+  static constexpr const char* name = "mlp_tail";
+  Slice<const T> act0;                      // [rows, h1]
+  Slice<const T> W1, b1;                    // [h2, h1], [h2]
+  Slice<const T> W2, b2;                    // [classes, h2], [classes]
+  Slice<const T> onehot;                    // [rows, classes] probability rows, or
+  Slice<const std::size_t> label_index;     // [rows] class indices (exactly one of the two is set)
+  std::size_t rows, h1, h2, classes;
+  std::size_t ld_out;                       // row stride of logits / dlogits
+  double loss_div;
+  Slice<T> act1, logits, loss, dlogits, dact1, dact0;
+  Slice<float> db2, db1, db0;
+  bool weights_ready = false;               // the kernel launched just before does not write W1/b1/W2/b2
 };
 
 // src/nn/loss.zig:130-215 as one device op

@@ -277,7 +277,46 @@ pub fn adam(self: *const Self, T: type, p: opspec.adam(T)) void {
     cuda.zg_adam_step(dtype(T), self.context.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, p.segments.ptr, p.segments.len, p.t_first, p.lr, p.beta1, p.beta2, p.eps, @intFromBool(p.clip), p.max_norm, p.delta, p.norms.ptr, null, null);
 }
 pub fn linear(self: *const Self, T: type, p: opspec.linear(T)) void {
+    if (p.sm_budget > 0) cuda.zg_bmm_sm_budget(p.sm_budget); // GEMMs side by side on parallel streams share the SMs
     cuda.zg_bmm(dtype(T), dtype(T), self.context.stream, p.A.ptr, p.B.ptr, p.C.ptr, 1, 1, 1, p.m, p.n, p.k, p.trans_a, p.trans_b, p.lda, p.ldb, p.ldc, p.alpha, p.beta, @intFromEnum(p.epilogue), if (p.bias) |b| b.ptr else null, if (p.mask_src) |m| m.ptr else null, if (p.colsum) |c| c.ptr else null);
+}
+/// The last two Linear layers, their softmax cross-entropy and the backward pass down to the gradient of the
+/// layer in front of them as one kernel (the separate ops when `mlp_tail_supported` says no).
+pub fn mlp_tail_supported(_: *const Self, T: type, h1: usize, h2: usize, classes: usize) bool {
+    return cuda.zg_mlp_tail_supported(dtype(T), h1, h2, classes) != 0;
+}
+pub fn mlp_tail(self: *const Self, T: type, p: opspec.mlp_tail(T)) void {
+    const labels: ?*const anyopaque = if (p.label_index) |l| @ptrCast(l.ptr) else @ptrCast(p.onehot.?.ptr);
+    cuda.zg_mlp_tail_fwd_bwd(dtype(T), self.context.stream, p.rows, p.h1, p.h2, p.classes, p.act0.ptr, p.W1.ptr, p.b1.ptr, p.W2.ptr, p.b2.ptr, labels, if (p.label_index != null) cuda.ZG_LABEL_INDEX else cuda.ZG_LABEL_ONEHOT, p.ld_out, p.loss_div, p.act1.ptr, p.logits.ptr, p.loss.ptr, p.dlogits.ptr, p.dact1.ptr, p.dact0.ptr, p.db2.ptr, p.db1.ptr, p.db0.ptr, @intFromBool(p.weights_ready));
+}
+pub fn sm_count(_: *const Self) usize {
+    return @intCast(cuda.zg_sm_count());
+}
+
+// ----------------------------------------------------------------- collectives
+/// Library collectives (NCCL bound at run time).  Rank 0 fills a 128-byte id with `comm_unique_id` and hands it to the
+/// other ranks over any host channel; every rank then calls `comm_init`.
+pub const Communicator = cuda.CommWrapper;
+pub fn comm_unique_id(id: *[128]u8) void {
+    cuda.zg_nccl_unique_id(id);
+}
+pub fn comm_init(self: *const Self, id: *const [128]u8, rank: u32, world: u32) error{CommInitFailed}!Communicator {
+    const c = cuda.zg_comm_init_rank(id, rank, world);
+    self.check();
+    if (c.ptr == null) return error.CommInitFailed;
+    return c;
+}
+pub fn comm_deinit(_: *const Self, comm: Communicator) void {
+    cuda.zg_comm_destroy(comm);
+}
+pub fn allreduce(self: *const Self, T: type, comm: Communicator, buf: []T) void {
+    cuda.zg_allreduce(comm, buf.ptr, buf.len, dtype(T), self.context.stream);
+}
+pub fn reduce_scatter(self: *const Self, T: type, comm: Communicator, send: []const T, recv: []T) void {
+    cuda.zg_reduce_scatter(comm, send.ptr, recv.ptr, recv.len, dtype(T), self.context.stream);
+}
+pub fn all_gather(self: *const Self, T: type, comm: Communicator, send: []const T, recv: []T) void {
+    cuda.zg_all_gather(comm, send.ptr, recv.ptr, send.len, dtype(T), self.context.stream);
 }
 
 // ---------------------------------------------------------------------- memory
