@@ -237,12 +237,12 @@ class GpuBackend:
         self.d.dispatch(opspec.bmm_acc(a, b, c, As, Bs, Cs, ta, tb, lda, ldb, ldc, alpha, beta))
         return self.down(c, np.asarray(C).shape)
 
-    def linear(self, A, B, C, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias=None, mask=None, colsum=None):
+    def linear(self, A, B, C, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bias=None, mask=None, colsum=None, sm_budget=0):
         a, b, c = self.up(A), self.up(B), self.up(C)
         bs = self.up(bias) if bias is not None else None
         mk = self.up(mask) if mask is not None else None
         cs = self.up(colsum) if colsum is not None else None
-        self.d.dispatch(opspec.linear(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bs, mk, colsum=cs))
+        self.d.dispatch(opspec.linear(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, alpha, beta, epilogue, bs, mk, colsum=cs, sm_budget=sm_budget))
         sums = self.d.to_numpy(cs) if cs is not None else None
         out = self.down(c, np.asarray(C).shape)
         return (out, sums) if colsum is not None else out

@@ -83,6 +83,54 @@ def test_gemm_split_k_weight_gradient_shapes(gpu, mode):
         assert rel_err(got, want) <= MODES[mode][1], (mode, m, n, k, rel_err(got, want))
 
 
+@pytest.mark.parametrize("budget", [1, 15, 22, 126, 133, 1000])
+def test_weight_gradient_with_a_share_of_the_sms(gpu, budget):
+    """zg_bmm_sm_budget only changes how many K ranges the split-K grid has: the result stays the
+    product (the guard regions around the operands catch a range that runs past k)."""
+    g = rng(budget)
+    for (m, n, k) in [(128, 784, 8192), (64, 128, 8192), (128, 784, 1000)]:
+        A = g.standard_normal((k, m)).astype(np.float32)
+        B = g.standard_normal((k, n)).astype(np.float32)
+        C0 = g.standard_normal((m, n)).astype(np.float32)
+        got = GpuBackend(gpu).linear(A, B, C0, m, n, k, True, False, m, n, n, 1.0, 1.0, "none", sm_budget=budget)
+        want = ORC.bmm_acc(A, B, C0, (1, m, k), (1, k, n), (1, m, n), True, False, m, n, n, 1.0, 1.0)
+        # 1e-4, the bound of the hot path: with a budget of one SM the 8192 products of an element are
+        # accumulated in ONE tensor-memory accumulator, whose truncation bias grows with the number of steps
+        assert rel_err(got, want) <= 1e-4, (budget, m, n, k, rel_err(got, want))
+    # the budget is consumed by one call: the next product is sized for the whole GPU again
+    assert gpu.sm_count() >= 1
+
+
+@pytest.mark.parametrize("m,n,k,ldc", [(128, 64, 96, 64), (130, 68, 100, 68), (1, 36, 64, 36), (257, 100, 784, 104), (8192, 128, 784, 128),
+                                       (97, 32, 33, 40)])
+@pytest.mark.parametrize("epilogue", ["none", "bias", "bias_relu"])
+def test_output_through_the_tensor_map_on_ragged_edges(gpu, m, n, k, ldc, epilogue):
+    """Forward products whose output leaves through the C tensor map (beta = 0, fp32, 16-byte-aligned
+    rows): tiles that hang over the last rows / columns are clipped by the TMA unit, the padding
+    columns of a wider row stride keep their contents."""
+    g = rng(m + n + k)
+    A = g.standard_normal((m, k)).astype(np.float32)
+    B = g.standard_normal((n, k)).astype(np.float32)
+    bias = g.standard_normal(n).astype(np.float32)
+    C0 = np.full((m, ldc), 7.0, np.float32)
+    lda = ldb = k if k % 4 == 0 else None
+    if lda is None:  # rows of A / B must be 16-byte aligned for the tensor maps: pad k's stride
+        kp = (k + 3) // 4 * 4
+        Ap, Bp = np.zeros((m, kp), np.float32), np.zeros((n, kp), np.float32)
+        Ap[:, :k], Bp[:, :k] = A, B
+        A_, B_, lda, ldb = Ap, Bp, kp, kp
+    else:
+        A_, B_ = A, B
+    got = GpuBackend(gpu).linear(A_, B_, C0, m, n, k, False, True, lda, ldb, ldc, 1.0, 0.0, epilogue, bias if epilogue != "none" else None)
+    want = A.astype(np.float64) @ B.T.astype(np.float64)
+    if epilogue != "none":
+        want = want + bias[None, :]
+    if epilogue == "bias_relu":
+        want = np.maximum(want, 0)
+    assert rel_err(got[:, :n], want) <= 3e-5, rel_err(got[:, :n], want)
+    assert (got[:, n:] == 7.0).all()  # nothing written beyond column n
+
+
 @pytest.mark.parametrize("mode", ["ffma", "fp32x3"])
 def test_bmm_batch_broadcast(gpu, mode):
     g = rng(17)

@@ -105,6 +105,36 @@ def test_update_that_clears_gradients_trains_like_zero_grad(gpu):
         gpu.mem_cache_free(b_)
 
 
+def test_update_behind_each_weight_gradient_equals_the_update_after_the_join(gpu):
+    """fuse_update (the default of the tail path): every tensor is updated by an SGD launch right
+    behind its gradient, on that gradient's stream.  Same kernels, same arithmetic per element as one
+    SGD launch over all tensors after the join; the weight gradients are summed by reductions whose
+    order varies from run to run, hence a tolerance."""
+    B = 2048
+    Ws, bs = kaiming_uniform(DIMS, 99)
+    after = MlpTrainer(gpu, DIMS, B, Ws, bs, "sgd", lr=0.05, zero_grads_in_update=True, fuse_update=False)
+    behind = MlpTrainer(gpu, DIMS, B, Ws, bs, "sgd", lr=0.05, zero_grads_in_update=True, fuse_update=True)
+    assert behind.tail and behind.fuse_update
+    bufs = []
+    for i in range(4):
+        X, T, _ = batch(B, 70 + i)
+        Xd, Td = gpu.from_numpy(X), gpu.from_numpy(T)
+        bufs += [Xd, Td]
+        after.step(Xd, Td)
+        behind.step(Xd, Td)
+        assert abs(after.read_loss() - behind.read_loss()) <= 1e-5 * abs(after.read_loss())
+    assert not gpu.to_numpy(behind.grads).any()  # every gradient was cleared by the launch that applied it
+    aW, ab = after.get_params()
+    bW, bb = behind.get_params()
+    for l in range(3):
+        assert_close("W%d" % l, bW[l], aW[l], 1e-5)
+        assert_close("b%d" % l, bb[l], ab[l], 1e-5)
+    after.free()
+    behind.free()
+    for b_ in bufs:
+        gpu.mem_cache_free(b_)
+
+
 def test_loss_over_100_sgd_steps_config2(gpu):
     """784-128-64-10 at batch 8192, 100 SGD steps over a fixed set of seeded
     batches: per-step loss within 1e-3 relative of the CPU path."""

@@ -300,13 +300,22 @@ class MlpTrainer:
 
     def _dw_sm_shares(self) -> dict:
         """SMs for each tensor-core weight-gradient GEMM of a three-layer step (layers 0 and 1; the last
-        layer's output is a few rows and goes to a small FFMA kernel that fits beside the others):
-        in proportion to the 128x128 output tiles, the first layer's share a multiple of its tile count."""
+        layer's output is a few rows and goes to a small FFMA kernel that fits beside the others).
+        Both are split-K grids of (output tiles x K ranges) CTAs, one CTA per SM, and a CTA's time goes
+        with the 32-deep k-slabs of its range: the first layer (on the critical path) gets as many K
+        ranges as leave the second one a range at most 1.3 times as long."""
         if self._dw_shares is None:
             sms = self.dev.sm_count()
-            tiles = [-(-self.dims[l + 1] // 128) * -(-self.dims[l] // 128) for l in (0, 1)]
-            first = sms * tiles[0] // sum(tiles) // tiles[0] * tiles[0]
-            self._dw_shares = {0: first, 1: sms - first} if 0 < first < sms else {}
+            t0, t1 = (-(-self.dims[l + 1] // 128) * -(-self.dims[l] // 128) for l in (0, 1))
+            slabs = -(-self.B // 32)
+            best = None
+            for s0 in range(1, sms // t0 + 1):
+                s1 = (sms - t0 * s0) // t1
+                if s1 < 1:
+                    break
+                if -(-slabs // s1) <= 1.3 * -(-slabs // s0):
+                    best = (t0 * s0, t1 * s1)
+            self._dw_shares = {0: best[0], 1: best[1]} if best else {}
         return self._dw_shares
 
     def step(self, X: DeviceSlice, T: DeviceSlice, allreduce: Optional[Callable[[DeviceSlice], None]] = None):
