@@ -87,7 +87,8 @@ def test_update_that_clears_gradients_trains_like_zero_grad(gpu):
     plain.step(bufs[0], bufs[1])
     gpu.capture.save()
     graph_plain = gpu.capture.detach()
-    assert graph.kernel_count() == graph_plain.kernel_count() - 1  # no fill of the gradient buffer
+    # no fill of the gradient buffer; with the tail path the three weight updates also ride in their GEMMs' epilogues
+    assert graph.kernel_count() <= graph_plain.kernel_count() - 1
     for _ in range(2):
         graph.run()
         graph_plain.run()

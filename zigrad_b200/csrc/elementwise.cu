@@ -111,9 +111,7 @@ __global__ void __launch_bounds__(kThreads) bcast_kernel(T* out, const T* lng, c
     const size_t nvec = n / N;
     size_t col = (tid * N) % L;
     const size_t step = (nthreads * N) % L;
-    for (size_t v = tid; v < nvec; v += nthreads) {
-      const size_t e = v * N;
-      const Pack<T, N> rl = ldv(lng + e);
+    auto apply = [&](const Pack<T, N>& rl, size_t e) {
       Pack<T, N> r;
       size_t cj = col;
 #pragma unroll
@@ -125,7 +123,17 @@ __global__ void __launch_bounds__(kThreads) bcast_kernel(T* out, const T* lng, c
       stv(out + e, r);
       col += step;
       if (col >= L) col -= L;
+    };
+    size_t v = tid;
+    // four vectors of the long operand in flight per thread before the first store
+    for (; v + (kUnroll - 1) * nthreads < nvec; v += kUnroll * nthreads) {
+      Pack<T, N> rl[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) rl[u] = ldv(lng + (v + u * nthreads) * N);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) apply(rl[u], (v + u * nthreads) * N);
     }
+    for (; v < nvec; v += nthreads) apply(ldv(lng + v * N), v * N);
     for (size_t i = nvec * N + tid; i < n; i += nthreads) {
       const T sv = sht[i % L];
       out[i] = SHORT_IS_X ? f(sv, lng[i]) : f(lng[i], sv);
@@ -387,25 +395,28 @@ __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __re
 }
 __global__ void __launch_bounds__(kThreads) bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t n) {
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-  if (aligned16(src) && aligned16(dst)) {  // 8 elements per trip: one 128-bit load, two 128-bit stores
-    const size_t nv = n / 8;
-    auto put = [&](const uint4& q, size_t v) {  // a bfloat16 is the upper half of the fp32 with the same value
-      float4 lo, hi;
-      lo.x = __uint_as_float(q.x << 16); lo.y = __uint_as_float(q.x & 0xffff0000u);
-      lo.z = __uint_as_float(q.y << 16); lo.w = __uint_as_float(q.y & 0xffff0000u);
-      hi.x = __uint_as_float(q.z << 16); hi.y = __uint_as_float(q.z & 0xffff0000u);
-      hi.z = __uint_as_float(q.w << 16); hi.w = __uint_as_float(q.w & 0xffff0000u);
-      reinterpret_cast<float4*>(dst)[2 * v] = lo;
-      reinterpret_cast<float4*>(dst)[2 * v + 1] = hi;
+  if (((reinterpret_cast<uintptr_t>(src) & 7u) == 0) && aligned16(dst)) {
+    // 4 elements per thread and trip: one 64-bit load, ONE 128-bit store, so that a warp's store covers
+    // 512 contiguous bytes (with 8 elements per thread its two stores each touched every other 16 bytes);
+    // eight trips in flight per thread
+    const size_t nv = n / 4;
+    auto put = [&](const uint2& q, size_t v) {  // a bfloat16 is the upper half of the fp32 with the same value
+      float4 o;
+      o.x = __uint_as_float(q.x << 16); o.y = __uint_as_float(q.x & 0xffff0000u);
+      o.z = __uint_as_float(q.y << 16); o.w = __uint_as_float(q.y & 0xffff0000u);
+      reinterpret_cast<float4*>(dst)[v] = o;
     };
+    const uint2* sv = reinterpret_cast<const uint2*>(src);
     size_t v = tid;
-    for (; v + 3 * nth < nv; v += 4 * nth) {
-      const uint4 q0 = reinterpret_cast<const uint4*>(src)[v], q1 = reinterpret_cast<const uint4*>(src)[v + nth];
-      const uint4 q2 = reinterpret_cast<const uint4*>(src)[v + 2 * nth], q3 = reinterpret_cast<const uint4*>(src)[v + 3 * nth];
-      put(q0, v); put(q1, v + nth); put(q2, v + 2 * nth); put(q3, v + 3 * nth);
+    for (; v + 7 * nth < nv; v += 8 * nth) {
+      uint2 q[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) q[u] = sv[v + u * nth];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) put(q[u], v + u * nth);
     }
-    for (; v < nv; v += nth) put(reinterpret_cast<const uint4*>(src)[v], v);
-    for (size_t i = nv * 8 + tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
+    for (; v < nv; v += nth) put(sv[v], v);
+    for (size_t i = nv * 4 + tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
   } else {
     for (size_t i = tid; i < n; i += nth) dst[i] = __bfloat162float(src[i]);
   }

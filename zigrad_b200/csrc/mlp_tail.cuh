@@ -532,10 +532,24 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(barSplit2);
     }
+    // loss of this warp's rows (the q == 0 warps hold it), handed to thread 0 across the barrier below
+    {
+      const float ws = warp_sum(loss_row);
+      if (lane == 0 && warp < 4) red[warp] = ws;
+    }
     fence_async_smem();  // the staged tiles -> visible to the copy engine
     bar_arrive(2, kBar2);
     // logits / dlogits leave while the second product runs: thread (row, q) copies columns q, q + 4, ..
     bar_sync(1, kRowThreads);
+    // loss: CTA partial -> workspace and a ticket, while the second product runs; the CTA that drew the
+    // last ticket folds the partials at the end of the kernel
+    if (threadIdx.x == 0) {
+      p.loss_partial[blockIdx.x] = (red[0] + red[1]) + (red[2] + red[3]);
+      __threadfence();
+      const unsigned t = atomicAdd(p.counter, 1u);
+      is_last = (t == gridDim.x - 1) ? 1 : 0;
+      if (is_last) *p.counter = 0;
+    }
     if (ok && row_ok) {
       float* gl = p.logits + (size_t)(row0 + row) * ld;
       float* gd = p.dlogits + (size_t)(row0 + row) * ld;
@@ -566,9 +580,6 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     fence_async_smem();
     bar_arrive(3, kBar3);
-    // loss of this warp's rows (the q == 0 warps hold it)
-    const float ws = warp_sum(loss_row);
-    if (lane == 0 && warp < 4) red[warp] = ws;
   }
 
   // ---------------------------------------------------------------- teardown
@@ -578,16 +589,8 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem, kTmCols);
   }
-  // loss: CTA partial -> workspace; the last CTA (ticket) folds the partials in a fixed order
-  if (threadIdx.x == 0) {
-    p.loss_partial[blockIdx.x] = (red[0] + red[1]) + (red[2] + red[3]);
-    __threadfence();
-    const unsigned t = atomicAdd(p.counter, 1u);
-    is_last = (t == gridDim.x - 1) ? 1 : 0;
-    if (is_last) *p.counter = 0;
-    if (failed && p.error_flag) *p.error_flag = 1;
-  }
-  __syncthreads();
+  if (threadIdx.x == 0 && failed && p.error_flag) *p.error_flag = 1;
+  // loss: the CTA that drew the last ticket (all partials are in the workspace then) folds them in a fixed order
   if (is_last) {
     __threadfence();
     float v = 0.f;

@@ -241,18 +241,30 @@ class MlpTrainer:
         dX chain down to dact[L-3] done by one mlp_tail op.
 
         ``fuse_update`` (plain SGD, no all-reduce in between): the update rides on the
-        backward pass instead of following it.  Each weight gradient of layer 0 and of the
-        two tail layers is followed, on its own stream, by the SGD update of that one
-        tensor (nothing reads those weights any more once their gradient runs), and the
-        biases, whose gradients the tail op has finished, go with the last layer's: no
-        update kernel waits for the join of all streams.  The weights of the layers in
-        between are still read by the dX products and are updated after the join."""
+        backward pass instead of following it.  For layer 0 and the two tail layers nothing
+        reads the weights any more once their gradient runs, so
+        * with ``zero_grads_in_update`` (the gradients are not kept past the step) the
+          weight-gradient GEMM accumulates straight into the weights,
+          W += (-lr) * dY^T X (alpha = -lr, beta = 1, C = W): no gradient tensor, no update launch;
+        * otherwise each weight gradient is followed, on its own stream, by the SGD update
+          of that one tensor.
+        The biases, whose gradients the tail op has finished, are updated behind the last
+        layer's product; no update waits for the join of all streams.  The weights of the
+        layers in between are still read by the dX products and are updated after the join."""
         d, B, L = self.dev, self.B, self.L
         if not self._grads_clear:
             d.mem_fill(self.grads, 0.0)
         self._grads_clear = False
 
+        in_gemm = fuse_update and self.zero_grads_in_update
+        nlr = -float(np.float32(self.lr))  # lr cast f64 -> f32, then negated (optim.zig:103)
+
+        def target(l):  # (C, alpha) of layer l's weight-gradient product
+            return (self.W[l], nlr) if in_gemm and l in (0, L - 2, L - 1) else (self.dW[l], 1.0)
+
         def update(segs):
+            if in_gemm:
+                segs = [sg for sg in segs if sg not in [self.segments[2 * l] for l in (0, L - 2, L - 1)]]
             if fuse_update and segs:
                 d.dispatch(opspec.sgd(self.params, self.grads, segs, self.lr, False, self.max_norm, self.delta, self.norms,
                                       self.zero_grads_in_update))
@@ -274,18 +286,21 @@ class MlpTrainer:
         # the SMs are shared out by output tiles so that the three split-K grids fit in one wave together.
         share = self._dw_sm_shares() if L == 3 else {}
         with d.branch(0):
-            d.dispatch(opspec.linear(self.dact[L - 2], self.act[L - 3], self.dW[L - 2], h2, h1, B, True, False, h2, h1, h1, 1.0, 1.0,
+            Cw, a = target(L - 2)
+            d.dispatch(opspec.linear(self.dact[L - 2], self.act[L - 3], Cw, h2, h1, B, True, False, h2, h1, h1, a, 1.0,
                                      sm_budget=share.get(L - 2, 0)))
             update([weight(L - 2)])
         with d.branch(1):
-            d.dispatch(opspec.linear(self.dact[L - 1], self.act[L - 2], self.dW[L - 1], C, h2, B, True, False, self.ld_out, h2, h2, 1.0, 1.0))
+            Cw, a = target(L - 1)
+            d.dispatch(opspec.linear(self.dact[L - 1], self.act[L - 2], Cw, C, h2, B, True, False, self.ld_out, h2, h2, a, 1.0))
             # the tail op wrote the bias gradients of its two layers and of the layer in front of it
             update([weight(L - 1)] + [bias(l) for l in (L - 3, L - 2, L - 1)])
         for l in range(L - 3, -1, -1):
             K, N = self.dims[l], self.dims[l + 1]
             a_in = X if l == 0 else self.act[l - 1]
             if l == 0:  # nothing else is left on the main stream: the largest weight gradient runs there
-                d.dispatch(opspec.linear(self.dact[l], a_in, self.dW[l], N, K, B, True, False, N, K, K, 1.0, 1.0, sm_budget=share.get(0, 0)))
+                Cw, a = target(0)
+                d.dispatch(opspec.linear(self.dact[l], a_in, Cw, N, K, B, True, False, N, K, K, a, 1.0, sm_budget=share.get(0, 0)))
                 update([weight(0)])
             else:
                 with d.branch(0):
