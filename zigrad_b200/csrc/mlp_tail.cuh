@@ -473,8 +473,9 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     bar_sync(1, kRowThreads);
-    // ---- softmax cross-entropy forward and backward for the row (each of its four threads, identically), fused with
-    // the row's dact1 quarter = (dlogits W2) where act1 > 0.  One rolled loop per pass over the C logits.
+    // ---- softmax cross-entropy forward and backward for the row: each of its four threads takes the row's maximum
+    // and sum of exponentials (ten loads and exponentials: cheaper than exchanging them) and then the loss terms and
+    // dlogits of ITS classes q, q + 4, ..; the dlogits meet in shared memory.
     if (ok) {
       const float* lrow = lgs + row * ld;
       float mx = -INFINITY;
@@ -489,20 +490,32 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const len_t l = static_cast<const len_t*>(p.labels)[row0 + row];
         lab = l < (len_t)C ? (int)l : -1;
       }
+#pragma unroll
+      for (int i = 0; i < CP / 4; ++i) {
+        const int c = q + 4 * i;
+        if (c < C) {
+          const float dc = lrow[c] - mx;
+          float gc = 0.f;
+          if (row_ok) {
+            const float t = p.label_index ? ((c == lab) ? 1.f : 0.f) : Ts[row * C + c];
+            if (t != 0.f) loss_row -= t * fminf(fmaxf(dc - lse, kLogPMin), kLogPMax);
+            const float diff = __expf(dc) * inv - t;
+            gc = p.exact_inv ? diff * p.inv_divisor : diff / p.divisor;
+          }
+          dls[row * ld + c] = gc;
+        }
+      }
+    }
+    bar_sync(1, kRowThreads);
+    // ---- the row's dact1 quarter = (dlogits W2) where act1 > 0.  One rolled loop over the C classes.
+    if (ok) {
+      const float* drow = dls + row * ld;
       float x[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) x[j] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
       for (int c = 0; c < C; ++c) {
-        const float dc = lrow[c] - mx;
-        float gc = 0.f;
-        if (row_ok) {
-          const float t = p.label_index ? ((c == lab) ? 1.f : 0.f) : Ts[row * C + c];
-          if (q == 0 && t != 0.f) loss_row -= t * fminf(fmaxf(dc - lse, kLogPMin), kLogPMax);  // counted once per row
-          const float diff = __expf(dc) * inv - t;
-          gc = p.exact_inv ? diff * p.inv_divisor : diff / p.divisor;
-        }
-        if (q == 0) dls[row * ld + c] = gc;
+        const float gc = drow[c];
         const float4* w = reinterpret_cast<const float4*>(W2s + c * kH2 + q * 16);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -532,10 +545,10 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(barSplit2);
     }
-    // loss of this warp's rows (the q == 0 warps hold it), handed to thread 0 across the barrier below
+    // loss terms of this warp's (row, class) pairs, handed to thread 0 across the barrier below
     {
       const float ws = warp_sum(loss_row);
-      if (lane == 0 && warp < 4) red[warp] = ws;
+      if (lane == 0) red[warp] = ws;  // all 16 row warps: every thread holds the loss terms of its classes
     }
     fence_async_smem();  // the staged tiles -> visible to the copy engine
     bar_arrive(2, kBar2);
@@ -544,7 +557,10 @@ mlp_tail_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // loss: CTA partial -> workspace and a ticket, while the second product runs; the CTA that drew the
     // last ticket folds the partials at the end of the kernel
     if (threadIdx.x == 0) {
-      p.loss_partial[blockIdx.x] = (red[0] + red[1]) + (red[2] + red[3]);
+      float cta_loss = 0.f;
+#pragma unroll
+      for (int w = 0; w < kRowThreads / 32; ++w) cta_loss += red[w];
+      p.loss_partial[blockIdx.x] = cta_loss;
       __threadfence();
       const unsigned t = atomicAdd(p.counter, 1u);
       is_last = (t == gridDim.x - 1) ? 1 : 0;
