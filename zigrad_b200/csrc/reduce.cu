@@ -23,7 +23,7 @@ constexpr int kRThreads = 256;
 // x: [batch][row][col] -> y: [batch][col];  y = alpha * sum_rows + beta * y.
 // Grid: (row_chunks, col_tiles, batch).  A CTA is 8 warps; with VEC a warp
 // spans 128 columns (one float4 per lane) and the 8 warps take 8 rows per
-// trip, 4 trips unrolled, so a CTA has 32 x 512-byte row segments in flight.
+// trip, 8 trips unrolled, so a CTA has 64 x 512-byte row segments in flight.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kRThreads) fold_rows_kernel(const T* __restrict__ x, T* y, T* __restrict__ partial,
                                                               unsigned* counters, size_t row, size_t col, T alpha, T beta) {
@@ -42,6 +42,13 @@ __global__ void __launch_bounds__(kRThreads) fold_rows_kernel(const T* __restric
     size_t r = (size_t)blockIdx.x * 8 + warp;
     const size_t rstep = chunks * 8;
     if constexpr (VEC) {
+      for (; r + 7 * rstep < row; r += 8 * rstep) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(xb + (r + u * rstep) * col + c0);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { acc[0] += v[u].x; acc[1] += v[u].y; acc[2] += v[u].z; acc[3] += v[u].w; }
+      }
       for (; r + 3 * rstep < row; r += 4 * rstep) {
         float4 v[4];
 #pragma unroll
@@ -127,9 +134,9 @@ void fold_rows_launch(cudaStream_t s, const T* x, T* y, size_t batch, size_t row
   const bool vec = sizeof(T) == 4 && (col % 4 == 0) && host_aligned16(x);
   const size_t tile = vec ? 128 : 32;
   const size_t col_tiles = (col + tile - 1) / tile;
-  // row chunks: enough CTAs for ~2 per SM, at least 64 rows per CTA, and a
-  // final fold that stays short (<= 64 chunks)
-  size_t want = (size_t)2 * sm_count() / (col_tiles * batch);
+  // row chunks: enough CTAs for ~4 per SM (64 KB of loads in flight on each), at least 64 rows per CTA,
+  // and a final fold that stays short (<= 64 chunks)
+  size_t want = (size_t)4 * sm_count() / (col_tiles * batch);
   if (want < 1) want = 1;
   size_t by_rows = (row + 63) / 64;
   size_t chunks = want < by_rows ? want : by_rows;
