@@ -289,6 +289,17 @@ EXTERN_C void zg_adam_step(dtype id, StreamWrapper stream, void* params, void* g
                            const zg_segment* seg, len_t n_seg, len_t t_first,
                            double lr, double beta1, double beta2, double eps,
                            int clip, double max_norm, double delta, void* norms, void* bf16_copy, void* step_counter);
+/* The same over PART of a model: seg lists every tensor of the model in attach order with
+ * length 0 for those this call leaves alone (an empty segment costs nothing and keeps the
+ * positions, hence the per-tensor step counts, of the others).  advance_counter = 0 reads
+ * step_counter without advancing it, so that the tensors of one optimizer step can be
+ * updated by several calls (a layer at a time, as its gradient becomes final during the
+ * backward pass); the last call of the step passes 1. */
+EXTERN_C void zg_adam_step_part(dtype id, StreamWrapper stream, void* params, void* grads, void* m, void* v,
+                                const zg_segment* seg, len_t n_seg, len_t t_first,
+                                double lr, double beta1, double beta2, double eps,
+                                int clip, double max_norm, double delta, void* norms, void* bf16_copy, void* step_counter,
+                                int advance_counter);
 /* out[j] = sum of squares of segment j (fp64 accumulation, deterministic two-stage): the
  * shard-local part of the per-tensor gradient norm of host_device.zig:339-346 */
 EXTERN_C void zg_segment_sumsq(dtype id, StreamWrapper stream, const void* x, const zg_segment* seg, len_t n_seg, void* out);

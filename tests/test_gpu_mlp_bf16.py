@@ -123,6 +123,50 @@ def test_bf16_adam_keeps_master_and_copy_in_step(gpu):
     gpu.mem_cache_free(Td)
 
 
+@pytest.mark.parametrize("clip", [False, True])
+def test_adam_a_layer_at_a_time_during_backward_equals_one_update_after_it(gpu, clip):
+    """update_by_layer: every layer's tensors are updated on a side stream as soon as the layer's
+    gradients are final and nothing reads its weights any more.  Same kernels and segment positions
+    as one Adam launch over the whole model; the step counts agree exactly, parameters and moments
+    to the run-to-run spread of the split-K weight gradients (their partial products are summed in
+    an order that varies), eagerly and from a replayed graph."""
+    dims, B = [256, 384, 128, 64], 512
+    g = rng(31)
+    Ws, bs = kaiming_uniform(dims, 8)
+    X = g.standard_normal((B, dims[0])).astype(np.float32)
+    labels = g.integers(0, dims[-1], B)
+    one = MlpTrainer(gpu, dims, B, Ws, bs, "adam", lr=1e-3, fused=True, bf16=True, clip=clip, max_norm=0.05, update_by_layer=False)
+    lay = MlpTrainer(gpu, dims, B, Ws, bs, "adam", lr=1e-3, fused=True, bf16=True, clip=clip, max_norm=0.05, update_by_layer=True)
+    Xd, Td = gpu.from_numpy(bits(X)), gpu.from_numpy(labels.astype(np.uint64))
+    for _ in range(3):
+        one.step(Xd, Td)
+        lay.step(Xd, Td)
+    graphs = []
+    for tr in (one, lay):
+        gpu.sync()
+        gpu.capture.open()
+        tr.step(Xd, Td)
+        gpu.capture.save()
+        graphs.append(gpu.capture.detach())
+    for _ in range(2):
+        for gr in graphs:
+            gr.run()
+    gpu.sync()
+    assert one.read_t() == lay.read_t() == 6 * 5  # six tensors, five steps (three eager, two replays; capturing runs nothing)
+    for name, tol in (("params", 1e-5), ("m", 1e-4), ("v", 1e-4)):
+        assert rel_err(gpu.to_numpy(getattr(lay, name)), gpu.to_numpy(getattr(one, name))) <= tol, name
+    widen = lambda a: (a.astype(np.uint32) << 16).view(np.float32)
+    assert rel_err(widen(gpu.to_numpy(lay.params_bf16)), widen(gpu.to_numpy(one.params_bf16))) <= 8e-3  # a bf16 ulp where a rounding flips
+    np.testing.assert_array_equal(gpu.to_numpy(lay.params_bf16), bits(gpu.to_numpy(lay.params)))  # the copy is the rounding of ITS master
+    assert abs(one.read_loss() - lay.read_loss()) <= 1e-5 * abs(one.read_loss())
+    for gr in graphs:
+        gr.free()
+    one.free()
+    lay.free()
+    gpu.mem_cache_free(Xd)
+    gpu.mem_cache_free(Td)
+
+
 def test_wide_mlp_full_size_shard_against_the_oracle(gpu):
     """The wide-MLP configuration at its real size: one GPU's 8192-row shard of
     4096->4096->4096->4096->1000 (the persistent 128x256-tile bf16 kernels and the

@@ -206,6 +206,7 @@ SIGNATURES = {
                                    vp, vp, vp, vp, vp, vp, vp, vp, vp, i32]),
     "zg_sgd_step": (None, [dtype_t, S, vp, vp, C.POINTER(Segment), len_t, dbl, i32, dbl, dbl, vp, i32]),
     "zg_adam_step": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp]),
+    "zg_adam_step_part": (None, [dtype_t, S, vp, vp, vp, vp, C.POINTER(Segment), len_t, len_t, dbl, dbl, dbl, dbl, i32, dbl, dbl, vp, vp, vp, i32]),
     "zg_segment_sumsq": (None, [dtype_t, S, vp, C.POINTER(Segment), len_t, vp]),
     "zg_soft_update": (None, [dtype_t, S, vp, vp, len_t, dbl]),
     "zg_cast": (None, [dtype_t, dtype_t, S, vp, vp, len_t]),

@@ -263,9 +263,9 @@ extern "C" void zg_sgd_step(dtype id, StreamWrapper w, void* params, void* grads
   }
 }
 
-extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grads, void* m, void* v, const zg_segment* seg, len_t n_seg,
-                             len_t t_first, double lr_, double beta1_, double beta2_, double eps_, int clip, double max_norm, double delta,
-                             void* norms, void* bf16_copy, void* step_counter) {
+extern "C" void zg_adam_step_part(dtype id, StreamWrapper w, void* params, void* grads, void* m, void* v, const zg_segment* seg, len_t n_seg,
+                                  len_t t_first, double lr_, double beta1_, double beta2_, double eps_, int clip, double max_norm, double delta,
+                                  void* norms, void* bf16_copy, void* step_counter, int advance_counter) {
   if (id != SINGLE) { set_error(kUnsupported, "zg_adam_step: only SINGLE is implemented"); return; }
   const unsigned long long* TD = static_cast<const unsigned long long*>(step_counter);
   if (n_seg == 0) return;
@@ -295,9 +295,15 @@ extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grad
     else if (cp) launch_pdl(adam_kernel<false, true>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, (const float*)nullptr, 0.f, 0.f, cp, TD, lr);
     else launch_pdl(adam_kernel<false, false>, grid, blk, 0, s, P, G, M, V, tab, beta1, beta2, eps, (const float*)nullptr, 0.f, 0.f, no_copy, TD, lr);
   }
-  if (step_counter) {  // advance the device counter once per tensor, after every update kernel has read it
+  if (step_counter && advance_counter) {  // advance the device counter once per tensor, after every update kernel has read it
     launch_pdl(counter_add_kernel, dim3(1), dim3(1), 0, s, static_cast<unsigned long long*>(step_counter), (unsigned long long)n_seg);
   }
+}
+
+extern "C" void zg_adam_step(dtype id, StreamWrapper w, void* params, void* grads, void* m, void* v, const zg_segment* seg, len_t n_seg,
+                             len_t t_first, double lr, double beta1, double beta2, double eps, int clip, double max_norm, double delta,
+                             void* norms, void* bf16_copy, void* step_counter) {
+  zg_adam_step_part(id, w, params, grads, m, v, seg, n_seg, t_first, lr, beta1, beta2, eps, clip, max_norm, delta, norms, bf16_copy, step_counter, 1);
 }
 
 extern "C" void zg_segment_sumsq(dtype id, StreamWrapper w, const void* x, const zg_segment* seg, len_t n_seg, void* out) {

@@ -171,9 +171,10 @@ class CudaDevice:
         self.L.zg_set_device(self.device_number)
 
     @contextlib.contextmanager
-    def branch(self, k: int = 0):
+    def branch(self, k: int = 0, after=()):
         """Ops issued inside the block go to the device's k-th side stream,
-        ordered after everything issued so far on the main stream; they may
+        ordered after everything issued so far on the main stream (and on the
+        side streams listed in `after`); they may
         overlap what the main stream (and the other side streams) run next.
         `join()` makes the main stream wait for them (required before the
         results are used and before a capture is saved)."""
@@ -190,6 +191,10 @@ class CudaDevice:
             side = self._sides[k]
         main = self.stream
         self.L.zg_stream_wait(side, main)
+        for j in after:
+            other = self._side if j == 0 else self._sides.get(j)
+            if other is not None and other.ptr != side.ptr:
+                self.L.zg_stream_wait(side, other)
         if all(side.ptr != f.ptr for f in self._forked):
             self._forked.append(side)
         self.stream = side
@@ -561,12 +566,12 @@ class CudaDevice:
                            int(bool(getattr(p, 'zero_grads', False))))
 
     def adam(self, p):
-        self.L.zg_adam_step(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr,
-                            self._segments(p.segments), len(p.segments), p.t_first, p.lr, p.beta1, p.beta2, p.eps,
-                            2 if p.clip == "given" else int(bool(p.clip)), p.max_norm, p.delta,
-                            p.norms.ptr if p.norms is not None else None,
-                            p.bf16_copy.ptr if p.bf16_copy is not None else None,
-                            p.step_counter.ptr if p.step_counter is not None else None)
+        self.L.zg_adam_step_part(p.params.dtype, self.stream, p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr,
+                                 self._segments(p.segments), len(p.segments), p.t_first, p.lr, p.beta1, p.beta2, p.eps,
+                                 2 if p.clip == "given" else int(bool(p.clip)), p.max_norm, p.delta,
+                                 p.norms.ptr if p.norms is not None else None,
+                                 p.bf16_copy.ptr if p.bf16_copy is not None else None,
+                                 p.step_counter.ptr if p.step_counter is not None else None, 1 if p.advance_counter else 0)
 
     def segment_sumsq(self, x: DeviceSlice, segments, out: DeviceSlice):
         self.L.zg_segment_sumsq(x.dtype, self.stream, x.ptr, self._segments(segments), len(segments), out.ptr)

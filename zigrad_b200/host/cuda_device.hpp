@@ -243,8 +243,8 @@ class CudaDevice {
   }
   template <typename T> void op(const opspec::adam<T>& p) {
     const std::vector<zg_segment> seg = segments(p.segments);
-    zg_adam_step(dtype_of<T>(), cur(), p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, seg.data(), seg.size(), p.t_first, p.lr, p.beta1, p.beta2,
-                 p.eps, p.clip ? 1 : 0, p.max_norm, p.delta, p.norms.ptr, nullptr, p.step_counter.ptr);
+    zg_adam_step_part(dtype_of<T>(), cur(), p.params.ptr, p.grads.ptr, p.m.ptr, p.v.ptr, seg.data(), seg.size(), p.t_first, p.lr, p.beta1,
+                      p.beta2, p.eps, p.clip ? 1 : 0, p.max_norm, p.delta, p.norms.ptr, nullptr, p.step_counter.ptr, p.advance_counter ? 1 : 0);
   }
 
   ExecutionGraph capture;

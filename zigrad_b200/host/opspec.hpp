@@ -422,6 +422,7 @@ struct adam {
   double max_norm = 10.0, delta = 1e-6;
   Slice<float> norms;
   Slice<std::uint64_t> step_counter;  // optional device counter (graph replay)
+  bool advance_counter = true;        // false: read step_counter without advancing it (one step as several calls over parts of the model)
 };
 
 }  // namespace opspec

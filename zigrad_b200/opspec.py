@@ -536,6 +536,7 @@ class adam:
     norms: Optional[Any] = None
     bf16_copy: Optional[Any] = None
     step_counter: Optional[Any] = None  # device u64: tensor updates so far (graph-replay safe step count)
+    advance_counter: bool = True  # False: read step_counter without advancing it (one optimizer step as several calls, see zg_adam_step_part)
 
 
 @_op("csr_gcn_propagate")
