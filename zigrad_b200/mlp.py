@@ -52,6 +52,21 @@ def kaiming_uniform(dims: Sequence[int], seed: int):
     return Ws, bs
 
 
+def split_sm_shares(sms: int, tiles0: int, tiles1: int, k_slabs: int):
+    """Shares of `sms` SMs for two split-K GEMMs that run side by side, the first on the critical
+    path.  Both are grids of (output tiles x K ranges) CTAs, one CTA per SM, and a CTA's time goes
+    with the 32-deep k-slabs of its range: the first gets as many K ranges as leave the second a
+    range at most 1.3 times as long.  Returns (SMs of the first, SMs of the second) or None."""
+    best = None
+    for s0 in range(1, sms // tiles0 + 1):
+        s1 = (sms - tiles0 * s0) // tiles1
+        if s1 < 1:
+            break
+        if -(-k_slabs // s1) <= 1.3 * -(-k_slabs // s0):
+            best = (tiles0 * s0, tiles1 * s1)
+    return best
+
+
 class MlpTrainer:
     def __init__(self, dev: CudaDevice, dims: Sequence[int], batch: int, weights, biases, opt: str = "sgd",
                  lr: float = 0.01, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, clip: bool = False,
@@ -340,21 +355,10 @@ class MlpTrainer:
 
     def _dw_sm_shares(self) -> dict:
         """SMs for each tensor-core weight-gradient GEMM of a three-layer step (layers 0 and 1; the last
-        layer's output is a few rows and goes to a small FFMA kernel that fits beside the others).
-        Both are split-K grids of (output tiles x K ranges) CTAs, one CTA per SM, and a CTA's time goes
-        with the 32-deep k-slabs of its range: the first layer (on the critical path) gets as many K
-        ranges as leave the second one a range at most 1.3 times as long."""
+        layer's output is a few rows and goes to a small FFMA kernel that fits beside the others)."""
         if self._dw_shares is None:
-            sms = self.dev.sm_count()
             t0, t1 = (-(-self.dims[l + 1] // 128) * -(-self.dims[l] // 128) for l in (0, 1))
-            slabs = -(-self.B // 32)
-            best = None
-            for s0 in range(1, sms // t0 + 1):
-                s1 = (sms - t0 * s0) // t1
-                if s1 < 1:
-                    break
-                if -(-slabs // s1) <= 1.3 * -(-slabs // s0):
-                    best = (t0 * s0, t1 * s1)
+            best = split_sm_shares(self.dev.sm_count(), t0, t1, -(-self.B // 32))
             self._dw_shares = {0: best[0], 1: best[1]} if best else {}
         return self._dw_shares
 
