@@ -84,9 +84,15 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
     for (unsigned p = 0; p < kArMaxWorld; ++p)
       if (p < a.world && p != a.rank) st_word_pair(slot(p, a.rank) + i, w);
   }
-  // ---- 2. sum, in rank order, my own values and what the peers pushed to me
+  // ---- 2. sum, in rank order, my own values and what the peers pushed to me.  The words of all
+  // peers are requested before the first is looked at (one memory round trip when they have
+  // all arrived, instead of one per peer); only a word that is not there yet is polled.
   bool gave_up = false;
   for (size_t i = tid; i < npairs && !gave_up; i += nth) {
+    uint4 w[kArMaxWorld];
+#pragma unroll
+    for (unsigned p = 0; p < kArMaxWorld; ++p)
+      if (p < a.world && p != a.rank) w[p] = ld_word_pair(slot(a.rank, p) + i);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (unsigned p = 0; p < kArMaxWorld; ++p) {
@@ -97,14 +103,13 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArA
         continue;
       }
       const uint4* src = slot(a.rank, p) + i;
-      uint4 w = ld_word_pair(src);
-      for (unsigned it = 0; (w.y != e || w.w != e) && it < a.spin_limit; ++it) {
+      for (unsigned it = 0; (w[p].y != e || w[p].w != e) && it < a.spin_limit; ++it) {
         if (it > 64) __nanosleep(it > 4096 ? 200 : 20);
-        w = ld_word_pair(src);
+        w[p] = ld_word_pair(src);
       }
-      if (w.y != e || w.w != e) { gave_up = true; break; }
-      s0 += __uint_as_float(w.x);
-      s1 += __uint_as_float(w.z);
+      if (w[p].y != e || w[p].w != e) { gave_up = true; break; }
+      s0 += __uint_as_float(w[p].x);
+      s1 += __uint_as_float(w[p].z);
     }
     if (gave_up) break;
     a.grads[2 * i] = a.zero_grads ? 0.f : s0;
@@ -187,16 +192,22 @@ __global__ void __launch_bounds__(kArThreads) allreduce_twoshot_kernel(const ArA
   const size_t my0 = (size_t)a.rank * S;
   const size_t my_n = my0 < npairs ? ((npairs - my0) < S ? (npairs - my0) : S) : 0;
   for (size_t j = tid; j < my_n && !gave_up; j += nth) {
+    // the contributions of all peers are requested before the first is looked at
+    uint4 c[kArMaxWorld];
+#pragma unroll
+    for (unsigned p = 0; p < kArMaxWorld; ++p)
+      if (p < W && p != a.rank) c[p] = ld_word_pair(scatter_slot(a.rank, p) + j);
     float s0 = 0.f, s1 = 0.f;
-    for (unsigned p = 0; p < W; ++p) {
+#pragma unroll
+    for (unsigned p = 0; p < kArMaxWorld; ++p) {
+      if (p >= W) continue;
       if (p == a.rank) {
         float v0, v1;
         local_pair(my0 + j, v0, v1);
         s0 += v0; s1 += v1;
       } else {
-        uint4 w;
-        if (!poll(scatter_slot(a.rank, p) + j, w)) { gave_up = true; break; }
-        s0 += __uint_as_float(w.x); s1 += __uint_as_float(w.z);
+        if ((c[p].y != e || c[p].w != e) && !poll(scatter_slot(a.rank, p) + j, c[p])) { gave_up = true; break; }
+        s0 += __uint_as_float(c[p].x); s1 += __uint_as_float(c[p].z);
       }
     }
     if (gave_up) break;
