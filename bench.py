@@ -246,7 +246,8 @@ def bind_to_numa_node(node):
 # ----------------------------------------------------------------------------
 class Job:
     """One configuration of the data-parallel MLP step on this rank: trainer,
-    reducer, resident batches and one captured graph per resident batch."""
+    reducer, resident batches, one captured graph per resident batch and one over a
+    whole rotation of them."""
 
     def __init__(self, dev, comm, rank, world, B, global_B, resident, allreduce_kind, seed_base=1000, steps_per_graph=1):
         from zigrad_b200.dp import GradAllReduce, PeerAllReduce

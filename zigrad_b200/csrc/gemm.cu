@@ -305,26 +305,6 @@ static bool try_skinny(dtype id, dtype c_id, cudaStream_t s, const void* A, cons
   p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k;
   p.lda = (uint32_t)lda; p.ldb = (uint32_t)ldb; p.ldc = (uint32_t)ldc;
   p.alpha = (float)alpha; p.beta = (float)beta; p.epilogue = epilogue; p.tb = tb ? 1 : 0;
-  static const bool tn_shadow = [] { const char* e = getenv("ZG_TN_SHADOW"); return e && e[0] == '1'; }();
-  if (tn_shadow && ta && !tb && m <= 64 && n <= 128 && n % 4 == 0 && k >= 1024 && epilogue == ZG_EPI_NONE && !colsum && ldb % 4 == 0 && ldc == n &&
-      host_aligned16(B) && host_aligned16(C)) {
-    // small-output weight gradient (A [k, m], B [k, n], C contiguous): FFMA kernel without shared memory that shares
-    // SMs with a large GEMM running beside it; its partial products are folded by the row-fold kernel
-    const uint32_t tiles_n = (uint32_t)(n / 4), tiles_m = (uint32_t)((m + 3) / 4), tiles = tiles_m * tiles_n;
-    uint32_t groups = skinny::kTnThreads / tiles;
-    if (groups < 1) return false;
-    if (groups > 8) groups = 8;
-    const size_t ctas = std::min<size_t>((k + 8 * groups - 1) / (8 * groups), (size_t)sm_count());
-    const uint32_t rows_per_cta = (uint32_t)((k + ctas - 1) / ctas);
-    const unsigned grid = (unsigned)((k + rows_per_cta - 1) / rows_per_cta);
-    const size_t parts = (size_t)grid * groups;
-    float* partial = static_cast<float*>(workspace(s, sizeof(float) * parts * m * n, nullptr, 1));
-    if (!partial) return true;  // error recorded
-    if (!launch_pdl(skinny::skinny_tn_kernel, dim3(grid), dim3(skinny::kTnThreads), 0, s, p, partial, rows_per_cta, tiles_n, tiles, groups)) return true;
-    // C = alpha * (sum over the parts) + beta * C: the parts are the rows of a [parts, m * n] matrix
-    zg_fold_rows(SINGLE, StreamWrapper{s}, partial, C, parts, m * n, alpha, beta);
-    return true;
-  }
   if (ta) {
     // weight gradient of a narrow layer: A [k, m], B [k, n]
     if (tb || m > 16 || n < 16 || n > 256 || 256 % n != 0 || k < 1024 || epilogue != ZG_EPI_NONE || colsum) return false;

@@ -221,70 +221,5 @@ __global__ void __launch_bounds__(kThreads) skinny_m_kernel(const Params p, cons
   }
 }
 
-// C[m,n] += alpha A^T B with A stored [k, m], B stored [k, n], a SMALL output (m <= 64, n <= 128) and a
-// deep k: the weight gradients of the narrow layers of an MLP (dW = dY^T X with k = batch rows).  On the
-// tensor-core path such a problem is one output tile cut into k-splits whose CTAs each take a whole SM's
-// shared memory -- SMs that the large weight gradient of the first layer, launched beside it, needs.
-// This kernel uses no shared memory and few registers, so its CTAs run on the same SMs as that GEMM's
-// (which mostly wait on TMA and the tensor pipe): a thread owns a 4 x 4 block of C and every G-th row of
-// the CTA's block of k rows, reads one 16-byte word of A and one of B per row (the words a warp asks for
-// are few and shared: L1 broadcasts), eight rows in flight.  The (CTA, row group) partial products go to
-// a workspace [parts][m * n] -- a fold over the parts (deterministic, no atomics: one atomic per
-// element and CTA measured 15 us for a 64 x 128 output, the atomics alone) finishes alpha * sum + beta * C.
-// Plain fp32 FFMA.
-constexpr int kTnThreads = 512;
-__global__ void __launch_bounds__(kTnThreads) skinny_tn_kernel(const Params p, float* __restrict__ partial, const uint32_t rows_per_cta,
-                                                               const uint32_t tiles_n, const uint32_t tiles, const uint32_t groups) {
-  pdl_sync();
-  const uint32_t g = threadIdx.x / tiles, t = threadIdx.x - g * tiles;
-  if (g >= groups) return;
-  const uint32_t tm = t / tiles_n, tn = t - tm * tiles_n;
-  const uint32_t r0 = blockIdx.x * rows_per_cta;
-  const uint32_t r1 = (r0 + rows_per_cta < p.k) ? r0 + rows_per_cta : p.k;
-  // the last block of A columns may be ragged (m = 10: columns 8, 9 valid, 10, 11 not): A's rows are then read
-  // by elements; B and C columns are whole words (n a multiple of 4)
-  const bool a_full = 4 * tm + 4 <= p.m && (p.lda & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.A) & 15u) == 0;
-  float acc[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  auto load_a = [&](uint32_t r) -> float4 {
-    const float* ar = p.A + (size_t)r * p.lda + 4 * tm;
-    if (a_full) return __ldg(reinterpret_cast<const float4*>(ar));
-    float4 v;
-    v.x = (4 * tm + 0 < p.m) ? __ldg(ar + 0) : 0.f;
-    v.y = (4 * tm + 1 < p.m) ? __ldg(ar + 1) : 0.f;
-    v.z = (4 * tm + 2 < p.m) ? __ldg(ar + 2) : 0.f;
-    v.w = (4 * tm + 3 < p.m) ? __ldg(ar + 3) : 0.f;
-    return v;
-  };
-  auto mac = [&](const float4 a, const float4 b) {
-    const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-  };
-  uint32_t r = r0 + g;
-  // eight rows in flight
-  for (; r + 7 * groups < r1; r += 8 * groups) {
-    float4 a[8], b[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      a[u] = load_a(r + u * groups);
-      b[u] = __ldg(reinterpret_cast<const float4*>(p.B + (size_t)(r + u * groups) * p.ldb + 4 * tn));
-    }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) mac(a[u], b[u]);
-  }
-  for (; r < r1; r += groups) mac(load_a(r), __ldg(reinterpret_cast<const float4*>(p.B + (size_t)r * p.ldb + 4 * tn)));
-  // partial [part][m][n]
-  float* dst = partial + ((size_t)(blockIdx.x * groups + g) * p.m + 4 * tm) * p.n + 4 * tn;
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    if (4 * tm + i < p.m) *reinterpret_cast<float4*>(dst + (size_t)i * p.n) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-}
-
 }  // namespace skinny
 }  // namespace zg

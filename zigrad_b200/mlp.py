@@ -21,8 +21,10 @@ Two op sequences produce the same tensors:
   launches + 1 memset for the three-layer model.  When the last two layers have
   the widths the ``mlp_tail`` op is built for (128 -> 64 -> at most 16 classes:
   the MNIST model), ``step()`` replaces everything between the first layer's
-  forward GEMM and the weight gradients by that one op: 6 launches per step
-  (forward GEMM, tail, three independent weight-gradient GEMMs, update).
+  forward GEMM and the weight gradients by that one op; with plain SGD and no
+  reduction between backward and update the weight updates then ride in the
+  gradient GEMMs' epilogues (``fuse_update``): 6 launches per step (forward
+  GEMM, tail, three independent weight-gradient GEMMs, the biases' update).
 
 Parameters, gradients and optimizer state live in flat buffers in attach
 order (W0, b0, W1, b1, ...), which is what a data-parallel step all-reduces
