@@ -21,7 +21,7 @@ def test_peer_allreduce_matches_host_sum_on_all_ranks(variant):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
            "--master-port", "29631" if variant == "default" else "29633", os.path.join(here, "peer_allreduce_worker.py")]
     env = dict(os.environ)
-    if variant == "two-shot":  # what 8 ranks run by default for the step's gradient buffer; forced here at any world size
+    if variant == "two-shot":  # what 4 and more ranks run by default for the step's gradient buffer; forced here at any world size
         env["ZG_ALLREDUCE"] = "2"
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
