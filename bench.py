@@ -545,7 +545,10 @@ def run_gpu(args, rank, local_rank, world):
         roofline = {"kernel": top, "bound": "hbm", "achieved": kt["GBps"], "peak": hbm, "unit": "GB/s", "frac": kt["GBps"] / hbm,
                     "traffic": tr_entry.get("dram_bytes_per_launch"), "traffic_source": tr_entry.get("source", "no capture for this batch size"),
                     "peak_origin": "of " + origin, "us_per_launch": kt["us_per_op"],
-                    "algorithmic_bytes": kt["bytes"], "tensor_TFLOPs_algorithmic": kt["TFLOPs"]}
+                    "algorithmic_bytes": kt["bytes"], "tensor_TFLOPs_algorithmic": kt["TFLOPs"],
+                    "limiter": "shared-memory pipe: 3xTF32 moves ~710 128-byte wavefronts per 32-deep k-slab (TMA write, hi/lo split, "
+                               "tensor-core reads of B) for 384 cycles of tensor work; DRAM traffic equals the algorithmic bytes "
+                               "(profiles/gemm_tc_fp32x3_mlp_step_gemms_b8192.md)"}
 
     # ---- CPU baseline (bounded sample), rank 0 at N=1 only
     cpu = None
