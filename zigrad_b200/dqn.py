@@ -47,24 +47,28 @@ class DqnTrainer:
              dones: DeviceSlice):
         d, B, C, qc = self.dev, self.B, self.C, self.q_clip
         pol, tgt = self.policy, self.target
-        # ---- targets (gradients disabled in the reference)
-        qn = tgt.forward(next_states)
-        d.dispatch(opspec.clamp_fwd(qn, qn, -qc, qc))
-        d.dispatch(opspec.max_along(qn, [B, C], self.maxq, [B, 1], 1))
-        d.dispatch(opspec.mul(self.maxq, self.gamma_s, self.tmp))          # gamma * max
-        d.dispatch(opspec.sub(self.one_s, dones, self.targets))            # 1 - done
-        d.dispatch(opspec.mul(self.tmp, self.targets, self.tmp))           # masked
-        d.dispatch(opspec.add(rewards, self.tmp, self.targets))            # r + ...
-        d.dispatch(opspec.clamp_fwd(self.targets, self.targets, -qc, qc))
+        # ---- targets (gradients disabled in the reference): a chain of small kernels that does not depend
+        # on the policy net, so it runs on a side stream beside the policy forward
+        with d.branch(1):
+            qn = tgt.forward(next_states)
+            d.dispatch(opspec.clamp_fwd(qn, qn, -qc, qc))
+            d.dispatch(opspec.max_along(qn, [B, C], self.maxq, [B, 1], 1))
+            d.dispatch(opspec.mul(self.maxq, self.gamma_s, self.tmp))          # gamma * max
+            d.dispatch(opspec.sub(self.one_s, dones, self.targets))            # 1 - done
+            d.dispatch(opspec.mul(self.tmp, self.targets, self.tmp))           # masked
+            d.dispatch(opspec.add(rewards, self.tmp, self.targets))            # r + ...
+            d.dispatch(opspec.clamp_fwd(self.targets, self.targets, -qc, qc))
+            # the two zero fills the loss and the gather backward accumulate into (ensure_grad(0))
+            d.mem_fill(self.dq, 0.0)
+            d.mem_fill(pol.dact[-1], 0.0)
         # ---- policy forward, clamp outside the graph, gather by action
         q_all = pol.forward(states)
         d.dispatch(opspec.clamp_fwd(q_all, q_all, -qc, qc))
         d.gather_rows(q_all, actions, B, C, self.q, self.offsets)
+        d.join()  # the targets and the cleared gradients are ready
         # ---- loss and its gradient w.r.t. the gathered values
-        d.mem_fill(self.dq, 0.0)
         d.dispatch(opspec.smooth_l1(self.q, self.targets, 1.0, self.loss, self.dq))
         # ---- gather backward: scatter into a zero gradient of all Q values
-        d.mem_fill(pol.dact[-1], 0.0)
         d.dispatch(opspec.scatter_add(self.dq, self.offsets, pol.dact[-1]))
         pol.backward(states, last_bias_done=False)
         pol.update()
