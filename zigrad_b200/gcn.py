@@ -108,7 +108,11 @@ class GcnTrainer:
     def step(self, T_masked: DeviceSlice):
         """T_masked: one-hot targets of the masked rows, fp32 [M, C] contiguous."""
         d, N, F, H, C, Fp, Cp, M = self.dev, self.N, self.F, self.H, self.C, self.Fp, self.Cp, self.M
-        d.mem_fill(self.grads, 0.0)  # zero_grad (model.zig:49-54)
+        # zero_grad (model.zig:49-54) and the zero gradient the MaskLayer backward scatters into: nothing in
+        # the forward pass needs them, so the two fills run on a side stream beside it
+        with d.branch(1):
+            d.mem_fill(self.grads, 0.0)
+            d.mem_fill(self.dlog, 0.0)
         # ---- forward
         self._mm(self.X, self.W1, self.h1, N, H, F, False, True, Fp, Fp, H)                       # h1 = X . W1^T
         self._prop(self.h1, self.a1, H, H, "bias_relu", self.b1)                                   # relu(A.h1 + b1)
@@ -116,17 +120,19 @@ class GcnTrainer:
         self._prop(self.h2, self.logits, C, Cp, "bias", self.b2)                                   # A.h2 + b2
         # ---- mask rows, loss, gradient of the masked logits (+ db2 = its column sums)
         d.mem_take(self.logits, self.offsets, self.mlog)
+        d.join()  # the cleared gradient buffers
         d.dispatch(opspec.softmax_ce(self.mlog, T_masked, M, C, self.loss, self.dm, float(M), accumulate=False, ld=Cp,
                                      bias_grad=self.db2))
-        d.mem_fill(self.dlog, 0.0)
         d.dispatch(opspec.scatter_add(self.dm, self.offsets, self.dlog))                            # MaskLayer backward
         # ---- backward
         self._prop(self.dlog, self.dh2, C, Cp, transpose=True)                                    # dh2 = A^T . dlogits
-        self._mm(self.dh2, self.a1, self.dW2, C, H, N, True, False, Cp, H, H, 1.0)                # dW2 += dh2^T . a1
+        with d.branch(0):  # nothing below reads dW2: beside the rest of the backward pass
+            self._mm(self.dh2, self.a1, self.dW2, C, H, N, True, False, Cp, H, H, 1.0)            # dW2 += dh2^T . a1
         self._mm(self.dh2, self.W2, self.da1, N, H, C, False, False, Cp, H, H, 0.0, "relu_mask", None, self.a1,
                  colsum=self.db1)                                                                   # da1, db1
         self._prop(self.da1, self.dh1, H, H, transpose=True)                                      # dh1 = A^T . da1
         self._mm(self.dh1, self.X, self.dW1, H, F, N, True, False, H, Fp, Fp, 1.0)                # dW1 += dh1^T . X
+        d.join()
         # ---- update
         if self.opt == "adam":
             d.dispatch(opspec.adam(self.params, self.grads, self.m, self.v, self.segments, self.t + 1, self.lr, self.beta1,
