@@ -28,14 +28,17 @@
 //     act0 and column block q of dact0.  The full act1 row is exchanged through the
 //     shared-memory tile that also feeds its TMA store; thread q forms the logits
 //     of classes q, q+4, .. in FFMA against W2 in shared memory (broadcast reads);
-//     the C logits are exchanged through the logits staging tile; softmax, loss and
-//     dlogits are computed per row (redundantly by the four threads, identically);
+//     the C logits are exchanged through the logits staging tile; every thread takes
+//     the row's maximum and sum of exponentials itself and then the loss terms and
+//     dlogits of ITS classes, which meet in the dlogits staging tile;
 //   * every output tile leaves through shared memory: act1, dact1 and dact0 as TMA
 //     stores of swizzled [128 x 32] slabs (dact0 overwrites the act0 slab it was
-//     masked with), logits / dlogits as a copy by the helper warps;
+//     masked with), logits / dlogits as a copy by the row threads while the second
+//     product runs;
 //   * bias gradients: the helper warps add the staged tiles up column by column
-//     in row order and issue one fp32 atomic per column and CTA; the loss is folded
-//     over the grid by the last CTA (ticket) in a fixed order.
+//     in row order and issue one fp32 atomic per column and CTA; the loss leaves as
+//     one partial per CTA with a ticket drawn while the second product runs, and the
+//     CTA that drew the last ticket folds the partials in a fixed order at its end.
 //
 // Roles (20 warps): 0-15 own the rows (warp w: TMEM lanes 32(w%4).., quarter w/4),
 // 16-18 helpers (staging, W1 split, column sums, copy-out), 19 issues the TMA
