@@ -20,8 +20,10 @@ Prints ONE JSON line (rank 0).
 * `e2e`     the same step fed from pinned HOST memory: the H2D copy of every
             batch and the D2H read of every loss are inside the timed region
             (double-buffered on a copy stream, one packed copy per batch).
-* `roofline` the slowest kernel of the step, timed alone over the rotating
-            batches, against the measured HBM / tensor peaks.
+* `roofline` the kernel with the largest share of the step (the split-K
+            weight-gradient GEMM; its layer-1 launch), timed alone over the
+            rotating batches, against the measured HBM peak; `kernels`
+            holds the other two kernels of the critical path beside it.
 * `cpu_baseline` the CPU oracle (reference HostDevice restated, OpenBLAS) on
             the box's host cores, on a bounded sample of the same workload.
 * `dp_check` (N > 1) replicas bit-identical after the timed steps, and three
@@ -503,7 +505,7 @@ def run_gpu(args, rank, local_rank, world):
         g.free()
     st.close()
 
-    # ---- roofline of the slowest kernel, timed alone over the rotating batches
+    # ---- roofline of the kernel with the largest share of the step, timed alone over the rotating batches
     roofline, kernel_table = None, None
     if rank == 0:
         hbm, tflops, _, origin = measured_peaks()
@@ -513,10 +515,20 @@ def run_gpu(args, rank, local_rank, world):
                 lambda X: dev.dispatch(opspec.linear(X, tr.W[0], tr.act[0], B, N0, K0, False, True, K0, K0, N0, 1.0, 0.0, "bias_relu", tr.b[0])),
                 4.0 * (B * K0 + N0 * K0 + B * N0 + N0), 2.0 * B * K0 * N0),
             "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]": (
-                # beta = 1: accumulating into the gradient buffer, the launch the training step makes
-                lambda X: dev.dispatch(opspec.linear(tr.dact[0], X, tr.dW[0], N0, K0, B, True, False, N0, K0, K0, 1.0, 1.0)),
+                # the launch the training step makes: accumulating (beta = 1) with alpha = -lr, its split-K grid sized
+                # for the SM share it has beside the other weight gradients (into the gradient buffer here, so that
+                # timing it does not move the weights)
+                lambda X: dev.dispatch(opspec.linear(tr.dact[0], X, tr.dW[0], N0, K0, B, True, False, N0, K0, K0, -LR, 1.0,
+                                                     sm_budget=(tr._dw_sm_shares().get(0, 0) if tr.tail and tr.L == 3 else 0))),
                 4.0 * (B * N0 + B * K0 + N0 * K0), 2.0 * B * K0 * N0),
         }
+        if tr.tail:
+            H1, H2, CC, LD = DIMS[1], DIMS[2], DIMS[3], tr.ld_out
+            cands["fused tail: layer-2 fwd, layer-3 fwd, softmax-CE, dX3, dX2, bias gradients (not a roofline candidate: a dependent chain)"] = (
+                lambda X: dev.dispatch(opspec.mlp_tail(tr.act[0], tr.W[1], tr.b[1], tr.W[2], tr.b[2], job.resident[0][1], B, H1, H2, CC, LD,
+                                                       float(global_B), tr.act[1], tr.act[2], tr.loss, tr.dact[2], tr.dact[1], tr.dact[0],
+                                                       tr.db[2], tr.db[1], tr.db[0], weights_ready=True)),
+                4.0 * (2 * B * H1 + 2 * B * H2 + 2 * B * LD + B * CC + H2 * H1 + CC * H2), 2.0 * B * (2 * H1 * H2 + 2 * H2 * CC))
         traffic = {}
         if os.path.exists(TRAFFIC_FILE):
             traffic = json.load(open(TRAFFIC_FILE))
@@ -539,16 +551,19 @@ def run_gpu(args, rank, local_rank, world):
             kernel_table[name] = {"us_per_op": us, "launches_per_op": launches_per_run / len(job.resident), "GBps": nbytes / us * 1e-3,
                                   "TFLOPs": flops / us * 1e-6, "bytes": nbytes, "flops": flops}
             g.free()
-        top = max(kernel_table, key=lambda k: kernel_table[k]["us_per_op"])
+        # the roofline kernel is the instance with the largest share of the step in the committed launch list
+        # (profiles/bench_mlp_784-128-64-10_b8192_launch_list.md): the split-K weight-gradient GEMM; the
+        # launch reported is its large one, dW0
+        top = "layer-1 weight-gradient GEMM dY^T.X [128,B]x[B,784]"
         kt = kernel_table[top]
         tr_entry = traffic.get(top, {}) if B == 8192 else {}
         roofline = {"kernel": top, "bound": "hbm", "achieved": kt["GBps"], "peak": hbm, "unit": "GB/s", "frac": kt["GBps"] / hbm,
                     "traffic": tr_entry.get("dram_bytes_per_launch"), "traffic_source": tr_entry.get("source", "no capture for this batch size"),
                     "peak_origin": "of " + origin, "us_per_launch": kt["us_per_op"],
                     "algorithmic_bytes": kt["bytes"], "tensor_TFLOPs_algorithmic": kt["TFLOPs"],
-                    "limiter": "shared-memory pipe: 3xTF32 moves ~710 128-byte wavefronts per 32-deep k-slab (TMA write, hi/lo split, "
-                               "tensor-core reads of B) for 384 cycles of tensor work; DRAM traffic equals the algorithmic bytes "
-                               "(profiles/gemm_tc_fp32x3_mlp_step_gemms_b8192.md)"}
+                    "limiter": "shared-memory pipe: per 32-deep k-slab of a 128x128 tile 3xTF32 moves ~128 KB through it (TMA write, hi/lo "
+                               "split, tensor-core reads of B: ~1000 cycles at 128 B/cycle) for 768 cycles of tensor work; DRAM traffic equals "
+                               "the algorithmic bytes (profiles/gemm_tc_fp32x3_mlp_step_gemms_b8192.md)"}
 
     # ---- CPU baseline (bounded sample), rank 0 at N=1 only
     cpu = None
