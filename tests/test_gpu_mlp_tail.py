@@ -41,9 +41,13 @@ def tail_oracle(act0, W1, b1, W2, b2, T, div):
     return act1, logits, loss, dlog, dact1, dact0, dlog.sum(0), dact1.sum(0), dact0.sum(0)
 
 
+@pytest.mark.parametrize("ready", [False, True], ids=["weights-after-the-wait", "weights-before-the-wait"])
 @pytest.mark.parametrize("rows,C,ld,index,div", [(128, 10, 12, False, 128), (8192, 10, 12, False, 8192), (300, 10, 10, True, 300),
-                                                 (1, 7, 8, False, 64), (1000, 16, 16, True, 65536), (4099, 3, 4, False, 4099)])
-def test_tail_matches_the_separate_ops_of_the_oracle(gpu, rows, C, ld, index, div):
+                                                 (1, 7, 8, False, 64), (1000, 16, 16, True, 65536), (4099, 3, 4, False, 4099),
+                                                 (777, 10, 12, "soft", 777)])
+def test_tail_matches_the_separate_ops_of_the_oracle(gpu, rows, C, ld, index, div, ready):
+    """`index`: u64 class indices, one-hot rows, or ("soft") probability rows with every class non-zero;
+    `ready`: the weights are fetched before / after the kernel's dependency wait."""
     g = rng(rows * 31 + C)
     act0 = np.maximum(g.standard_normal((rows, H1)), 0).astype(np.float32)   # post-ReLU: about half zeros
     W1 = g.uniform(-0.2, 0.2, (H2, H1)).astype(np.float32)
@@ -52,10 +56,13 @@ def test_tail_matches_the_separate_ops_of_the_oracle(gpu, rows, C, ld, index, di
     b2 = g.uniform(-0.1, 0.1, C).astype(np.float32)
     lab = g.integers(0, C, rows)
     T = np.eye(C, dtype=np.float32)[lab]
+    if index == "soft":
+        e = np.exp(g.standard_normal((rows, C))).astype(np.float32)
+        T = (e / e.sum(1, keepdims=True)).astype(np.float32)
     want = tail_oracle(act0, W1, b1, W2, b2, T, div)
     be = GpuBackend(gpu)
     d_act0, d_W1, d_b1, d_W2, d_b2 = be.up(act0), be.up(W1), be.up(b1), be.up(W2), be.up(b2)
-    d_lab = be.up(lab.astype(np.uint64), np.uint64) if index else be.up(T)
+    d_lab = be.up(lab.astype(np.uint64), np.uint64) if index is True else be.up(T)
     sentinel = 7.5  # padding columns of logits / dlogits must not be touched
     d_act1, d_logits, d_dlog = be.up(np.zeros((rows, H2))), be.up(np.full((rows, ld), sentinel)), be.up(np.full((rows, ld), sentinel))
     d_dact1, d_dact0 = be.up(np.zeros((rows, H2))), be.up(np.zeros((rows, H1)))
@@ -63,7 +70,7 @@ def test_tail_matches_the_separate_ops_of_the_oracle(gpu, rows, C, ld, index, di
     d_db2, d_db1, d_db0, d_loss = be.up(np.zeros(C)), be.up(np.zeros(H2)), be.up(db0_init), be.up(np.full(1, -1.0))
     assert gpu.mlp_tail_supported(SINGLE, H1, H2, C)
     gpu.dispatch(opspec.mlp_tail(d_act0, d_W1, d_b1, d_W2, d_b2, d_lab, rows, H1, H2, C, ld, float(div), d_act1, d_logits, d_loss, d_dlog,
-                                 d_dact1, d_dact0, d_db2, d_db1, d_db0))
+                                 d_dact1, d_dact0, d_db2, d_db1, d_db0, weights_ready=ready))
     got_act1 = gpu.to_numpy(d_act1, (rows, H2))
     got_logits, got_dlog = gpu.to_numpy(d_logits, (rows, ld)), gpu.to_numpy(d_dlog, (rows, ld))
     got_dact1, got_dact0 = gpu.to_numpy(d_dact1, (rows, H2)), gpu.to_numpy(d_dact0, (rows, H1))
